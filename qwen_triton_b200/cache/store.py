@@ -1,0 +1,138 @@
+"""Device storage of the cache and its grouping.
+
+Layers whose mixers ask for the same thing (kv heads, head size, all keys or a window of them)
+form a *group* with storage of its own: one key and one value pool
+``[entries, pages, kv_heads, page_tokens, head_dim]`` shared by the group's entries, one page list
+per sequence for the whole group.  Beside the pools each mixer that asks for it has a fixed-size
+state block per slot, ``[num_slots, *shape]``, zeroed when a slot is handed out; the architecture
+built here asks for none, and the plumbing is exercised by a toy mixer in the tests.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..parts.base import KVRequest, StateRequest
+from .book import CacheBook, GroupGeometry
+
+
+@dataclass
+class CacheView:
+    """What one schedule position sees of the cache."""
+
+    group: int | None = None          # index of its kv group (None: no keys/values)
+    k: torch.Tensor | None = None     # [pages, kv_heads, page_tokens, head_dim]
+    v: torch.Tensor | None = None
+    page_tokens: int = 0
+    ring_tokens: int = 0              # 0: position p sits at element p; else at p % ring_tokens
+    writable: bool = True             # False: this call reads an entry that another call writes
+    state: torch.Tensor | None = None  # [num_slots, *shape]
+
+
+@dataclass
+class _Group:
+    request: KVRequest
+    owners: list[int]                 # schedule positions that own an entry, in order
+    ring_tokens: int
+    k: torch.Tensor | None = None
+    v: torch.Tensor | None = None
+
+
+def round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+class SequenceCache:
+    """Slots, paged key/value pools per group, and per-slot state.
+
+    ``requests[i]`` is what schedule position ``i`` asks for (``KVRequest``, ``StateRequest`` or
+    None) and ``cache_of[i]`` the position whose entry it reads instead (or None).
+    """
+
+    def __init__(self, requests, cache_of, *, max_tokens: int, max_seq_len: int, dtype: torch.dtype,
+                 device: torch.device, page_tokens: int = 64, chunk_tokens: int = 256,
+                 num_slots: int | None = None, allocate: bool = True) -> None:
+        self.page_tokens = page_tokens
+        self.dtype = dtype
+        self.device = device
+        self.chunk_tokens = chunk_tokens
+        self.max_seq_len = max_seq_len
+        total_pages = max(1, round_up(max_tokens, page_tokens) // page_tokens)
+        self.num_slots = num_slots if num_slots is not None else total_pages
+        self.groups: list[_Group] = []
+        self._entry_of: dict[int, tuple[int, int]] = {}     # schedule position -> (group, entry)
+        self._state_of: dict[int, torch.Tensor] = {}
+        self._state_requests: dict[int, StateRequest] = {}
+        self._cache_of = list(cache_of)
+        for position, request in enumerate(requests):
+            if self._cache_of[position] is not None or request is None:
+                continue
+            if isinstance(request, StateRequest):
+                self._state_requests[position] = request
+                continue
+            for index, group in enumerate(self.groups):
+                if group.request == request:
+                    break
+            else:
+                ring = 0
+                if request.window:
+                    ring = round_up(request.window + chunk_tokens - 1, page_tokens)
+                self.groups.append(_Group(request, [], ring))
+                index = len(self.groups) - 1
+            self._entry_of[position] = (index, len(self.groups[index].owners))
+            self.groups[index].owners.append(position)
+        geometry = [GroupGeometry(total_pages, g.ring_tokens // page_tokens) for g in self.groups]
+        self.book = CacheBook(self.num_slots, page_tokens, geometry, max_seq_len)
+        self.has_window = any(g.ring_tokens for g in self.groups)
+        if allocate:
+            for group in self.groups:
+                shape = (len(group.owners), total_pages, group.request.kv_heads, page_tokens, group.request.head_dim)
+                group.k = torch.zeros(shape, dtype=dtype, device=device)
+                group.v = torch.zeros(shape, dtype=dtype, device=device)
+            for position, request in self._state_requests.items():
+                self._state_of[position] = torch.zeros((self.num_slots, *request.shape), dtype=request.dtype, device=device)
+
+    # ------------------------------------------------------------------ views
+    def view(self, position: int) -> CacheView:
+        source = self._cache_of[position]
+        owner = position if source is None else source
+        view = CacheView(page_tokens=self.page_tokens, writable=source is None)
+        if owner in self._entry_of:
+            group_index, entry = self._entry_of[owner]
+            group = self.groups[group_index]
+            view.group = group_index
+            view.ring_tokens = group.ring_tokens
+            if group.k is not None:
+                view.k, view.v = group.k[entry], group.v[entry]
+        if owner in self._state_of:
+            view.state = self._state_of[owner]
+        return view
+
+    # ------------------------------------------------------------------ slots
+    def alloc(self) -> int:
+        slot = self.book.alloc()
+        for state in self._state_of.values():
+            state[slot].zero_()
+        return slot
+
+    def free(self, slot: int) -> None:
+        self.book.free(slot)
+
+    def max_blocks(self, group: int) -> int:
+        ring = self.groups[group].ring_tokens
+        return ring // self.page_tokens if ring else -(-self.max_seq_len // self.page_tokens)
+
+    def bytes(self) -> int:
+        total = 0
+        for group in self.groups:
+            if group.k is not None:
+                total += 2 * group.k.numel() * group.k.element_size()
+        for state in self._state_of.values():
+            total += state.numel() * state.element_size()
+        return total
+
+    def token_bytes(self) -> int:
+        """Bytes of keys and values one cached token occupies over all full-attention entries."""
+        size = torch.empty((), dtype=self.dtype).element_size()
+        return sum(2 * len(g.owners) * g.request.kv_heads * g.request.head_dim * size for g in self.groups)

@@ -1,0 +1,110 @@
+// Shared helpers of the sm_100a kernels: element types, loads that widen to float,
+// warp and block reductions, and the error convention of the C entry points.
+//
+// Every entry point is `extern "C" int qt_*(..., void* stream)`: it checks its
+// arguments, launches on `stream`, and returns 0 or a negative code whose text
+// qt_last_error() (in each library) gives.  Nothing allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define QT_OK 0
+#define QT_ERR_ARG -1
+#define QT_ERR_LAUNCH -2
+#define QT_ERR_UNSUPPORTED -3
+
+// element types of activations, weights and caches
+#define QT_F32 0
+#define QT_BF16 1
+
+namespace qt {
+
+static thread_local char g_error[512] = "";
+
+#define QT_FAIL(code, ...)                                   \
+    do {                                                     \
+        snprintf(qt::g_error, sizeof(qt::g_error), __VA_ARGS__); \
+        return (code);                                       \
+    } while (0)
+
+#define QT_REQUIRE(cond, ...)                     \
+    do {                                          \
+        if (!(cond)) QT_FAIL(QT_ERR_ARG, __VA_ARGS__); \
+    } while (0)
+
+#define QT_CHECK_LAUNCH(name)                                                          \
+    do {                                                                               \
+        cudaError_t err__ = cudaGetLastError();                                        \
+        if (err__ != cudaSuccess)                                                      \
+            QT_FAIL(QT_ERR_LAUNCH, "%s: launch failed: %s", name, cudaGetErrorString(err__)); \
+    } while (0)
+
+#define QT_DEFINE_LAST_ERROR(libname)                                   \
+    extern "C" const char* qt_last_error_##libname() { return qt::g_error; }
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Sum of `n_splits` partial results stored `split_stride` elements apart (split-K GEMM output).
+template <typename T>
+__device__ __forceinline__ float load_sum(const T* base, size_t index, int n_splits, size_t split_stride) {
+    float acc = to_float(base[index]);
+    for (int s = 1; s < n_splits; ++s) acc += to_float(base[index + (size_t)s * split_stride]);
+    return acc;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `scratch` holds 32 floats.  All threads get the sum.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = (lane < nwarps) ? scratch[lane] : 0.f;
+    total = warp_sum(total);
+    return total;
+}
+
+// Where position `pos` of a sequence lives in a paged cache.
+//   block_table   this sequence's row of page numbers
+//   ring_tokens   0: position p is element p; else element p % ring_tokens (windowed group)
+// Layout of one cache entry: [pages][kv_heads][page_tokens][head_dim].
+__device__ __forceinline__ size_t cache_offset(const int* block_table, int pos, int ring_tokens, int page_tokens,
+                                               int kv_heads, int kv_head, int head_dim) {
+    const int slot_pos = ring_tokens > 0 ? pos % ring_tokens : pos;
+    const int page = block_table[slot_pos / page_tokens];
+    return (((size_t)page * kv_heads + kv_head) * page_tokens + (slot_pos % page_tokens)) * (size_t)head_dim;
+}
+
+}  // namespace qt
+
+// Calls `body` with `T` bound to the element type named by the runtime code.
+#define QT_DISPATCH_DTYPE(dtype, name, ...)                         \
+    [&]() -> int {                                                  \
+        if ((dtype) == QT_F32) {                                    \
+            using T = float;                                        \
+            __VA_ARGS__                                             \
+        } else if ((dtype) == QT_BF16) {                            \
+            using T = __nv_bfloat16;                                \
+            __VA_ARGS__                                             \
+        }                                                           \
+        QT_FAIL(QT_ERR_ARG, "%s: unknown element type %d", name, (int)(dtype)); \
+    }()

@@ -1,0 +1,112 @@
+// Next-token choice from float logits [rows, vocab]: greedy argmax (ties go to the lowest id) and
+// temperature sampling by inverse CDF in vocabulary order.  The reference only has
+// argmax (luozoupi/Qwen-Triton models/core.py:405).
+#include "common.cuh"
+
+#include <math.h>
+
+using namespace qt;
+
+constexpr int SMP_THREADS = 1024;
+
+// One block per row.
+__global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float x = row[i];
+        if (x > v || (x == v && i < idx)) { v = x; idx = i; }
+    }
+    auto better = [](float av, int ai, float bv, int bi) { return bv > av || (bv == av && bi < ai); };
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+        if (better(v, idx, ov, oi)) { v = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_v[warp] = v; best_i[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        v = best_v[lane]; idx = best_i[lane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+            if (better(v, idx, ov, oi)) { v = ov; idx = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+extern "C" int qt_argmax(const float* logits, int* out, int rows, int vocab, void* stream) {
+    QT_REQUIRE(rows >= 0 && vocab > 0, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
+    if (rows == 0) return QT_OK;
+    argmax_kernel<<<rows, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+    QT_CHECK_LAUNCH("argmax");
+    return QT_OK;
+}
+
+// One block per row: token = first index whose cumulative weight exceeds uniform * total, with
+// weight_i = exp((logit_i - max) / T).  Thread t owns the contiguous ids [t * span, (t + 1) * span).
+__global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                                                            const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
+    __shared__ float scratch[32];
+    __shared__ float sums[SMP_THREADS];
+    __shared__ int chosen;
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const float inv_t = 1.f / temperature[blockIdx.x];
+    const int span = (vocab + blockDim.x - 1) / blockDim.x;
+    const int begin = min(vocab, (int)threadIdx.x * span), end = min(vocab, begin + span);
+
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = scratch[threadIdx.x & 31];   // blockDim.x == 1024: all 32 entries are written
+    mx = warp_max(mx);
+
+    float local = 0.f;
+    for (int i = begin; i < end; ++i) local += expf((row[i] - mx) * inv_t);
+    sums[threadIdx.x] = local;
+    if (threadIdx.x == 0) chosen = vocab - 1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // serial scan over the 1024 partial sums: a fixed order, so the choice is reproducible
+        float total = 0.f;
+        for (int t = 0; t < SMP_THREADS; ++t) total += sums[t];
+        const float target = uniform[blockIdx.x] * total;
+        float running = 0.f;
+        int owner = -1;
+        for (int t = 0; t < SMP_THREADS; ++t) {
+            if (running + sums[t] > target) { owner = t; break; }
+            running += sums[t];
+        }
+        if (owner >= 0) {
+            const int b = min(vocab, owner * span), e = min(vocab, b + span);
+            int pick = e - 1;
+            for (int i = b; i < e; ++i) {
+                running += expf((row[i] - mx) * inv_t);
+                if (running > target) { pick = i; break; }
+            }
+            chosen = pick;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out[blockIdx.x] = chosen;
+}
+
+extern "C" int qt_sample(const float* logits, const float* temperature, const float* uniform, int* out, int rows,
+                         int vocab, void* stream) {
+    QT_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    if (rows == 0) return QT_OK;
+    sample_kernel<<<rows, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, uniform, out, vocab);
+    QT_CHECK_LAUNCH("sample");
+    return QT_OK;
+}
+
+QT_DEFINE_LAST_ERROR(sampling)

@@ -1,0 +1,207 @@
+"""The step function: a model, its cache and its buffers on one GPU.
+
+``Engine.step`` takes, for each sequence of a batch, the next tokens (a whole prompt, a chunk of
+it, or one token) and the places whose logits are wanted; it runs exactly those tokens as one
+packed batch from the cache that earlier steps left, and returns float logits.  Sequences have
+their own lengths, nothing is padded, and the logits at a position do not depend on how the
+tokens were cut into steps or on what else was in the batch, beyond rounding.
+
+The reference's counterpart is ``QwenTritonForCausalLM.forward`` with ``past_key_values`` and
+``logits_to_keep`` (qwen_triton/models/core.py:321-375): a rectangular batch with one shared
+length (qwen_triton/modules/cache.py:21), correct for unequal lengths only in prefill.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache import SequenceCache
+from ..config import load_config
+from ..config.spec import ModelSpec
+from ..parts.base import Runtime, Workspace
+from ..weights import open_checkpoint, random_source
+from .model import CausalLM, expected_tensors
+from .step import StepContext, StepEntry, plan_passes
+
+_DTYPES = {
+    "bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp32": torch.float32, "float32": torch.float32,
+    torch.bfloat16: torch.bfloat16, torch.float32: torch.float32,
+}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    """``bf16``/``bfloat16``/``fp32``/``float32`` (the reference also reads fp16 names,
+    qwen_triton/models/core.py:29-44; half precision is not built here)."""
+    key = dtype.lower() if isinstance(dtype, str) else dtype
+    if key not in _DTYPES:
+        raise ValueError(f"unsupported dtype {dtype!r}: this library runs bfloat16 or float32")
+    return _DTYPES[key]
+
+
+def require_gpu(device: torch.device) -> None:
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("qwen_triton_b200 runs on a CUDA device (sm_100a) only; there is no host path")
+    major, minor = torch.cuda.get_device_capability(device)
+    if major != 10:
+        raise RuntimeError(f"the kernels are built for sm_100a; device {device} is sm_{major}{minor}")
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, source, *, dtype=torch.bfloat16, max_tokens: int = 8192,
+                 max_seq_len: int | None = None, max_step_tokens: int = 4096, device: str | torch.device = "cuda:0",
+                 page_tokens: int = 64, chunk_tokens: int = 256, options: dict | None = None) -> None:
+        self.device = torch.device(device)
+        require_gpu(self.device)
+        torch.cuda.set_device(self.device)
+        self.dtype = parse_dtype(dtype)
+        self.spec = spec
+        max_tokens = max(int(max_tokens), page_tokens)
+        self.max_seq_len = min(int(max_seq_len or spec.max_positions), spec.max_positions,
+                               -(-max_tokens // page_tokens) * page_tokens)
+        self.max_step_tokens = int(max_step_tokens)
+        workspace = Workspace(self.device)
+        self.runtime = Runtime(device=self.device, dtype=self.dtype, max_step_tokens=self.max_step_tokens,
+                               max_positions=self.max_seq_len, workspace=workspace, page_tokens=page_tokens,
+                               options=dict(options or {}))
+        self.model = CausalLM(spec, self.runtime)
+        self.model.load(source)
+        self.cache = SequenceCache(self.model.cache_requests(), [c.cache_of for c in spec.schedule],
+                                   max_tokens=max_tokens, max_seq_len=self.max_seq_len, dtype=self.dtype,
+                                   device=self.device, page_tokens=page_tokens, chunk_tokens=chunk_tokens)
+        workspace.allocate()
+        widths = [self.cache.max_blocks(g) for g in range(len(self.cache.groups))]
+        max_seqs = min(self.max_step_tokens, self.cache.num_slots)
+        self._meta = torch.zeros(StepContext.meta_size(self.max_step_tokens, max_seqs, widths), dtype=torch.int32,
+                                 device=self.device)
+        self._ctx = StepContext(device=self.device, meta=self._meta)
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_pretrained(cls, model_path: str | Path, **kwargs) -> "Engine":
+        """Model folder with config.json and safetensors; the architecture is chosen by config.json."""
+        config = load_config(model_path)
+        spec = config.model_spec()
+        engine = cls(spec, open_checkpoint(model_path, expected_tensors(spec)), **kwargs)
+        engine.config = config
+        return engine
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, **kwargs) -> "Engine":
+        """Seeded random weights drawn on the device (no model folder is written)."""
+        spec = config.model_spec()
+        dtype = parse_dtype(kwargs.get("dtype", torch.bfloat16))
+        device = kwargs.get("device", "cuda:0")
+        engine = cls(spec, random_source(expected_tensors(spec), seed, dtype, device), **kwargs)
+        engine.config = config
+        return engine
+
+    # ------------------------------------------------------------------ properties
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    @property
+    def eos_token_ids(self) -> tuple[int, ...]:
+        return tuple(self.spec.eos_token_ids)
+
+    @property
+    def page_tokens(self) -> int:
+        return self.cache.page_tokens
+
+    @property
+    def total_pages(self) -> int:
+        return self.cache.book.groups[0].num_pages if self.cache.book.groups else self.cache.num_slots
+
+    @property
+    def num_slots(self) -> int:
+        return self.cache.num_slots
+
+    # ------------------------------------------------------------------ sequences
+    def new_sequence(self) -> int:
+        """Take a slot for a sequence that starts at position 0."""
+        return self.cache.alloc()
+
+    def release(self, slot: int) -> None:
+        """Give back the slot and every page the sequence holds."""
+        self.cache.free(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.book.length(slot)
+
+    def can_hold(self, lengths_by_slot: dict[int, int]) -> bool:
+        return self.cache.book.can_hold(lengths_by_slot)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the given tokens; return float logits [sum of wanted places, vocab] in the order of
+        the entries and, within an entry, of its ``want`` list."""
+        entries = list(entries)
+        book = self.cache.book
+        seen: set[int] = set()
+        targets: dict[int, int] = {}
+        for entry in entries:
+            if entry.slot in seen:
+                raise ValueError(f"slot {entry.slot} appears twice in one step")
+            seen.add(entry.slot)
+            if not book.is_live(entry.slot):
+                raise ValueError(f"slot {entry.slot} is not in use")
+            if not entry.tokens:
+                raise ValueError(f"slot {entry.slot}: a step entry needs at least one token")
+            low, high = min(entry.tokens), max(entry.tokens)
+            if low < 0 or high >= self.spec.vocab_size:
+                raise ValueError(f"slot {entry.slot}: token id {low if low < 0 else high} is outside 0..{self.spec.vocab_size - 1}")
+            for place in entry.want:
+                if not 0 <= place < len(entry.tokens):
+                    raise ValueError(f"slot {entry.slot}: wanted place {place} is outside its {len(entry.tokens)} tokens")
+            targets[entry.slot] = book.length(entry.slot) + len(entry.tokens)
+            if targets[entry.slot] > self.max_seq_len:
+                raise ValueError(f"slot {entry.slot}: {targets[entry.slot]} tokens exceed max_seq_len={self.max_seq_len}")
+        if not book.can_hold(targets):
+            raise RuntimeError("the cache cannot hold this step: too many tokens are live (raise max_tokens)")
+
+        n_want = sum(len(e.want) for e in entries)
+        logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        want_base = np.cumsum([0] + [len(e.want) for e in entries])
+        chunk_limit = self.cache.chunk_tokens if self.cache.has_window else None
+        passes = plan_passes([len(e.tokens) for e in entries], self.max_step_tokens, chunk_limit)
+        for pieces in passes:
+            slots, tokens, past, rows, final_rows, row0 = [], [], [], [], [], 0
+            for piece in pieces:
+                entry = entries[piece.entry]
+                slots.append(entry.slot)
+                tokens.append(entry.tokens[piece.begin:piece.end])
+                past.append(book.length(entry.slot))
+                for k, place in enumerate(entry.want):
+                    if piece.begin <= place < piece.end:
+                        rows.append(row0 + place - piece.begin)
+                        final_rows.append(int(want_base[piece.entry]) + k)
+                row0 += piece.end - piece.begin
+                book.extend(entry.slot, past[-1] + piece.end - piece.begin)
+            tables = []
+            for group in range(len(self.cache.groups)):
+                width = max(1, max(len(book.pages(s, group)) for s in slots))
+                table = np.zeros((len(slots), width), dtype=np.int32)
+                for i, s in enumerate(slots):
+                    pages = book.pages(s, group)
+                    table[i, :len(pages)] = pages
+                tables.append(table)
+            self._ctx.fill(slots, tokens, past, rows, tables)
+            direct = len(passes) == 1 or final_rows == list(range(final_rows[0], final_rows[0] + len(rows))) if rows else True
+            if not rows:
+                self.model.forward(self._ctx, self.cache, None)
+            elif direct:
+                self.model.forward(self._ctx, self.cache, logits[final_rows[0]:final_rows[0] + len(rows)])
+            else:
+                part = torch.empty((len(rows), self.spec.vocab_size), dtype=torch.float32, device=self.device)
+                self.model.forward(self._ctx, self.cache, part)
+                logits.index_copy_(0, torch.tensor(final_rows, device=self.device), part)
+        self.steps_run += 1
+        return logits
+
+    def memory_report(self) -> dict[str, int]:
+        return {"weights": self.model.weight_bytes(), "cache": self.cache.bytes(),
+                "workspace": self.runtime.workspace.bytes()}

@@ -1,0 +1,295 @@
+"""Python entry to the CUDA kernels: argument checks, then a ctypes call on the current stream.
+
+Every function works on CUDA tensors only and raises if given anything else;
+there is no host implementation behind them.  ``GemmOut`` is how a matrix
+product hands its result to the next kernel: either the finished matrix or
+split-K partial sums that the consumer adds up in float.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _build
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+_c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+_SIGNATURES = {
+    "elementwise": {
+        "qt_embedding": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_add_rmsnorm": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int,
+                           _c_int, _c_ptr],
+        "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                                  _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+    },
+    "attention": {
+        "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+        "qt_attention_decode": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
+                                _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
+    },
+    "gemm_simt": {
+        "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    },
+    "sampling": {
+        "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_sample": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    },
+}
+_BOUND: dict[str, ctypes._CFuncPtr] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _fn(library: str, name: str):
+    fn = _BOUND.get(name)
+    if fn is None:
+        lib = _build.load_library(library)
+        fn = getattr(lib, name)
+        fn.argtypes = _SIGNATURES[library][name]
+        fn.restype = _c_int
+        _BOUND[name] = fn
+    return fn
+
+
+def _call(library: str, name: str, *args) -> None:
+    code = _fn(library, name)(*args)
+    if code != 0:
+        raise KernelError(f"{name} failed ({code}): {_build.last_error(library)}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _need(tensor: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no host path)")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if shape is not None and tuple(tensor.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(tensor.shape)}")
+
+
+def _code(tensor: torch.Tensor, name: str) -> int:
+    if tensor.dtype not in _CODES:
+        raise KernelError(f"{name}: element type {tensor.dtype} is neither float32 nor bfloat16")
+    return _CODES[tensor.dtype]
+
+
+@dataclass
+class GemmOut:
+    """Result of a matrix product: ``tensor`` is [splits, M, N]; the value is the sum over splits.
+
+    Rows and columns are dense (stride N, 1); the stride between splits may be larger than M * N
+    when the tensor is a view of a larger buffer.
+    """
+
+    tensor: torch.Tensor
+
+    def __post_init__(self) -> None:
+        t = self.tensor
+        if t.dim() != 3 or t.stride(2) != 1 or t.stride(1) != t.shape[2]:
+            raise KernelError(f"GemmOut needs a [splits, M, N] tensor with dense rows, got {tuple(t.shape)} / {t.stride()}")
+
+    @property
+    def n_splits(self) -> int:
+        return self.tensor.shape[0]
+
+    @property
+    def split_stride(self) -> int:
+        return self.tensor.stride(0) if self.tensor.shape[0] > 1 else 0
+
+    @property
+    def rows(self) -> int:
+        return self.tensor.shape[1]
+
+    @property
+    def cols(self) -> int:
+        return self.tensor.shape[2]
+
+    def value(self) -> torch.Tensor:
+        """The finished matrix in float (for tests and host-side use)."""
+        return self.tensor.float().sum(dim=0)
+
+
+# ----------------------------------------------------------------------------- elementwise
+def embedding(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+    """residual[t] = table[ids[t]] in float.  ids: int32 [T]."""
+    tokens, hidden = residual.shape
+    _need(residual, "residual", torch.float32)
+    _need(table, "table")
+    _need(ids, "ids", torch.int32, (tokens,))
+    if table.shape[1] != hidden:
+        raise KernelError(f"embedding: table width {table.shape[1]} != stream width {hidden}")
+    _call("elementwise", "qt_embedding", _ptr(residual), _ptr(table), _ptr(ids), tokens, hidden, table.shape[0],
+          _code(table, "table"), _stream())
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: GemmOut | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """stream += delta; out = rmsnorm(stream) * weight.
+
+    Without ``rows`` every row of ``residual`` [T, H] is updated in place and normed into ``out`` [T, H].
+    With ``rows`` (int32 [K]) only those rows are normed into ``out`` [K, H] and the stream is left as it is.
+    """
+    hidden = residual.shape[1]
+    _need(residual, "residual", torch.float32)
+    _need(weight, "weight", torch.float32, (hidden,))
+    n_rows = residual.shape[0] if rows is None else rows.shape[0]
+    _need(out, "out", shape=(n_rows, hidden))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if delta is not None:
+        if not delta.tensor.is_cuda or (delta.rows, delta.cols) != tuple(residual.shape):
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.tensor.shape)} does not match the stream {tuple(residual.shape)}")
+    _call("elementwise", "qt_add_rmsnorm", _ptr(residual), _ptr(delta.tensor) if delta else None,
+          _code(delta.tensor, "delta") if delta else F32, delta.n_splits if delta else 1,
+          delta.split_stride if delta else 0, _ptr(weight), float(eps), _ptr(out), _code(out, "out"), _ptr(rows),
+          n_rows, hidden, _stream())
+
+
+def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+                       token_seq: torch.Tensor, token_pos: torch.Tensor, block_table: torch.Tensor | None,
+                       q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                       cos_sin: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
+                       page_tokens: int, ring_tokens: int, write_kv: bool = True, kv_in_proj: bool = True) -> None:
+    """Per-head q/k RMSNorm, rotation and the cache write, from the fused projection output.
+
+    qkv [*, T, (nq + 2 nkv) d]; q_out [T, nq, d]; caches [pages, nkv, page_tokens, d]; cos_sin float [P, rd].
+    """
+    tokens = qkv.rows
+    width = (num_heads + (2 * num_kv_heads if kv_in_proj else 0)) * head_dim
+    if qkv.cols != width:
+        raise KernelError(f"qk_norm_rope_write: projection width {qkv.cols} != (nq + 2 nkv) d = {width}")
+    _need(q_out, "q_out", shape=(tokens, num_heads, head_dim))
+    _need(token_seq, "token_seq", torch.int32, (tokens,))
+    _need(token_pos, "token_pos", torch.int32, (tokens,))
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _need(w, name, torch.float32, (head_dim,))
+    rotary_dim, max_pos = 0, 0
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        max_pos, rotary_dim = cos_sin.shape
+    max_blocks = 0
+    if write_kv:
+        _need(block_table, "block_table", torch.int32)
+        max_blocks = block_table.shape[1]
+        for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
+            _need(cache, name, q_out.dtype)
+            if tuple(cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
+                raise KernelError(f"{name}: shape {tuple(cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
+    _call("elementwise", "qt_qk_norm_rope_write", _ptr(qkv.tensor), _code(qkv.tensor, "qkv"), qkv.n_splits,
+          qkv.split_stride, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _code(q_out, "q_out"), _ptr(token_seq),
+          _ptr(token_pos), _ptr(block_table), max_blocks, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin),
+          rotary_dim, max_pos, tokens, num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens,
+          1 if write_kv else 0, 1 if kv_in_proj else 0, _stream())
+
+
+def swiglu(gate_up: GemmOut, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    tokens, inter = out.shape
+    _need(out, "out")
+    if (gate_up.rows, gate_up.cols) != (tokens, 2 * inter):
+        raise KernelError(f"swiglu: input {tuple(gate_up.tensor.shape)} does not match output {tuple(out.shape)}")
+    _call("elementwise", "qt_swiglu", _ptr(gate_up.tensor), _code(gate_up.tensor, "gate_up"), gate_up.n_splits,
+          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, _stream())
+
+
+# ----------------------------------------------------------------------------- attention
+def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens):
+    _need(q, "q")
+    tokens, num_heads, head_dim = q.shape
+    _need(out, "out", q.dtype, q.shape)
+    _need(k_cache, "k_cache", q.dtype)
+    _need(v_cache, "v_cache", q.dtype, k_cache.shape)
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
+        raise KernelError(f"cache shape {tuple(k_cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
+    _need(block_table, "block_table", torch.int32)
+    return tokens, num_heads, head_dim
+
+
+def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                      block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
+                      num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float) -> None:
+    """Causal attention of packed sequences over the cache (which already holds this step's keys)."""
+    _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
+    n_seqs = seq_past.shape[0]
+    _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
+    _need(seq_past, "seq_past", torch.int32)
+    if block_table.shape[0] < n_seqs:
+        raise KernelError("attention_prefill: block table has fewer rows than sequences")
+    _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
+          _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
+          num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                     block_table: torch.Tensor, seq_len: torch.Tensor, num_kv_heads: int, page_tokens: int,
+                     ring_tokens: int, window: int | None, scale: float, n_splits: int,
+                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None) -> None:
+    """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
+
+    With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
+    results pass through ``part_acc`` (float, >= B nq splits d) and ``part_ml`` (float, >= B nq splits 2).
+    """
+    n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
+    _need(seq_len, "seq_len", torch.int32, (n_seqs,))
+    if n_splits > 1:
+        _need(part_acc, "part_acc", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_acc.numel() < n_seqs * num_heads * n_splits * head_dim or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
+            raise KernelError("attention_decode: scratch is too small for this batch and split count")
+    _call("attention", "qt_attention_decode", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
+          _ptr(block_table), block_table.shape[1], _ptr(seq_len), n_seqs, num_heads, num_kv_heads, head_dim,
+          page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits), _ptr(part_acc), _ptr(part_ml),
+          _stream())
+
+
+# ----------------------------------------------------------------------------- matrix product
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
+    """out = a [M, K] @ w [N, K]^T on the FMA pipe (float accumulation, any sizes)."""
+    _need(a, "a")
+    _need(w, "w", a.dtype)
+    if a.shape[1] != w.shape[1] or out.n_splits != 1 or (out.rows, out.cols) != (a.shape[0], w.shape[0]):
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.tensor.shape)} do not fit")
+    _call("gemm_simt", "qt_gemm_simt", _ptr(a), _ptr(w), _code(a, "a"), _ptr(out.tensor), _code(out.tensor, "out"),
+          a.shape[0], w.shape[0], a.shape[1], _stream())
+
+
+# ----------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits, "logits", torch.float32)
+    _need(out, "out", torch.int32, (logits.shape[0],))
+    _call("sampling", "qt_argmax", _ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream())
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:
+    rows = logits.shape[0]
+    _need(logits, "logits", torch.float32)
+    _need(temperature, "temperature", torch.float32, (rows,))
+    _need(uniform, "uniform", torch.float32, (rows,))
+    _need(out, "out", torch.int32, (rows,))
+    _call("sampling", "qt_sample", _ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), rows, logits.shape[1],
+          _stream())
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
+    """out = a @ w^T with the kernel that fits the element type and shape (a static choice)."""
+    gemm_simt(a, w, out)

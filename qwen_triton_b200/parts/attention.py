@@ -1,0 +1,126 @@
+"""Softmax attention over the paged cache with grouped kv heads, optional per-head q/k RMSNorm,
+a position encoding part and an optional window.
+
+Order as in the reference (qwen_triton/modules/attention.py:53-73,125-128): project, norm q and k
+per head over head_dim *before* rotation, rotate, write k/v to the cache, attend, project out.
+The three projections run as one product over the row-concatenated weight [q; k; v].
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import kernels
+from ..ops.kernels import GemmOut
+from ..weights.tensors import TensorSpec
+from .base import KVRequest, Runtime, part_class, register_mixer, to_device
+from .linear import Linear
+
+_DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight for the one-token kernel
+_MAX_SPLIT_PAIRS = 640              # (sequence, split) pairs the scratch holds
+_MIN_KEYS_PER_SPLIT = 128
+
+
+@register_mixer("attention")
+class Attention:
+    def __init__(self, params, prefix: str, runtime: Runtime) -> None:
+        self.prefix = prefix
+        self.runtime = runtime
+        self.hidden = int(params["hidden_size"])
+        self.nq = int(params["num_heads"])
+        self.nkv = int(params["num_kv_heads"])
+        self.d = int(params["head_dim"])
+        self.scale = float(params.get("scale", self.d ** -0.5))
+        self.window = params.get("window")
+        self.own_kv = bool(params.get("own_kv", True))
+        self.qk_norm = bool(params.get("qk_norm", False))
+        self.eps = float(params.get("qk_norm_eps", 1e-6))
+        self.names = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+        if self.nq % self.nkv:
+            raise ValueError(f"{prefix}: {self.nq} query heads are not a multiple of {self.nkv} kv heads")
+        if self.d > 256:
+            raise ValueError(f"{prefix}: head_dim={self.d} is beyond what the attention kernels take (256)")
+        position_spec = params["position"]
+        self.position = part_class("position", position_spec)(position_spec.params, runtime)
+        self.cos_sin: torch.Tensor | None = None
+        self.q_weight = self.k_weight = None
+        proj_rows = (self.nq + (2 * self.nkv if self.own_kv else 0)) * self.d
+        self.qkv = Linear("attn.qkv", proj_rows, self.hidden, runtime)
+        self.o = Linear("attn.o", self.hidden, self.nq * self.d, runtime)
+        ws = runtime.workspace
+        ws.declare("attn.q", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
+        ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
+        ws.declare("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.d, torch.float32)
+        ws.declare("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2, torch.float32)
+
+    # ------------------------------------------------------------------ weights
+    @classmethod
+    def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
+        hidden, nq, nkv, d = (int(params[k]) for k in ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
+        n = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
+        own_kv = bool(params.get("own_kv", True))
+        out = {f"{prefix}.{n['q']}.weight": TensorSpec((nq * d, hidden)),
+               f"{prefix}.{n['o']}.weight": TensorSpec((hidden, nq * d))}
+        if own_kv:
+            out[f"{prefix}.{n['k']}.weight"] = TensorSpec((nkv * d, hidden))
+            out[f"{prefix}.{n['v']}.weight"] = TensorSpec((nkv * d, hidden))
+        if params.get("qk_norm", False):
+            out[f"{prefix}.{n['q_norm']}.weight"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
+            if own_kv:
+                out[f"{prefix}.{n['k_norm']}.weight"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
+        return out
+
+    def load(self, source) -> None:
+        n, p = self.names, self.prefix
+        rows = [source(f"{p}.{n['q']}.weight")]
+        if self.own_kv:
+            rows += [source(f"{p}.{n['k']}.weight"), source(f"{p}.{n['v']}.weight")]
+        self.qkv.set_weight(torch.cat([r.to(self.runtime.dtype) for r in rows], dim=0))
+        self.o.set_weight(source(f"{p}.{n['o']}.weight"))
+        if self.qk_norm:
+            self.q_weight = to_device(source(f"{p}.{n['q_norm']}.weight"), torch.float32, self.runtime.device)
+            if self.own_kv:
+                self.k_weight = to_device(source(f"{p}.{n['k_norm']}.weight"), torch.float32, self.runtime.device)
+        tables = self.runtime.options.setdefault("position_tables", {})
+        key = self.position.key() + (self.runtime.max_positions,)
+        if key not in tables:
+            tables[key] = self.position.table(self.runtime.max_positions)
+        self.cos_sin = tables[key]
+
+    # ------------------------------------------------------------------ cache
+    def cache_request(self) -> KVRequest | None:
+        return KVRequest(self.nkv, self.d, self.window)
+
+    # ------------------------------------------------------------------ run
+    def _splits(self, ctx) -> int:
+        span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
+        heads_per_block = 8 if self.nq // self.nkv > 4 else max(1, self.nq // self.nkv)
+        blocks = ctx.n_seqs * self.nkv * math.ceil((self.nq // self.nkv) / heads_per_block)
+        wanted = max(1, math.ceil(_DECODE_TARGET_BLOCKS / blocks))
+        by_length = max(1, span // _MIN_KEYS_PER_SPLIT)
+        by_scratch = max(1, _MAX_SPLIT_PAIRS // ctx.n_seqs)
+        return max(1, min(wanted, by_length, by_scratch, 64))
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> GemmOut:
+        tokens = x.shape[0]
+        ws = self.runtime.workspace
+        qkv = self.qkv(x)
+        q = ws.view("attn.q", tokens, self.nq, self.d)
+        out = ws.view("attn.ctx", tokens, self.nq, self.d)
+        table = ctx.block_table(cache.group)
+        write = cache.writable and self.own_kv
+        kernels.qk_norm_rope_write(
+            qkv, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
+            table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
+            cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv)
+        if ctx.is_decode:
+            n_splits = self._splits(ctx)
+            kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,
+                                     cache.ring_tokens, self.window, self.scale, n_splits,
+                                     ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.d),
+                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2))
+        else:
+            kernels.attention_prefill(q, cache.k, cache.v, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len,
+                                      self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale)
+        return self.o(out.view(tokens, self.nq * self.d))

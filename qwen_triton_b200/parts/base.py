@@ -1,0 +1,156 @@
+"""What every part shares: the registries, the runtime it is built in, and buffers.
+
+A part is chosen by the ``kind`` of a :class:`~qwen_triton_b200.config.PartSpec`
+and built with that spec's parameters; it never sees the model it is in.
+
+Interfaces (what a new part must offer):
+
+* every part:  ``expected_tensors(params, prefix) -> {name: TensorSpec}`` (classmethod; no device),
+  ``__init__(params, prefix, runtime)``, ``load(source)`` with ``source(name) -> CPU tensor``.
+* norm:        ``apply(stream, out=None, rows=None) -> Tensor``: folds the pending delta into the
+  residual stream and returns the normed rows in the activation dtype.
+* position:    ``table(max_positions) -> float32 [P, rotary_dim]`` (cos | sin), or ``None`` for no encoding.
+* mixer:       ``cache_request() -> KVRequest | StateRequest | None`` and
+  ``forward(x, ctx, cache) -> GemmOut`` where ``cache`` is the view of the cache entry this call
+  uses (``cache.writable`` tells whether it owns it).
+* feed-forward: ``forward(x, ctx) -> GemmOut``.
+* block:       ``forward(stream, ctx, cache) -> None``: arranges norm, mixer and feed-forward
+  around the residual stream.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Mapping
+
+import torch
+
+from ..config.spec import PartSpec
+from ..ops.kernels import GemmOut
+
+_REGISTRIES: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+                                           "embedding": {}, "head": {}}
+
+
+def _register(family: str, kind: str, cls: type | None = None):
+    def put(c: type) -> type:
+        existing = _REGISTRIES[family].get(kind)
+        if existing is not None and existing is not c:
+            raise ValueError(f"{family} kind {kind!r} is already registered")
+        _REGISTRIES[family][kind] = c
+        return c
+
+    return put if cls is None else put(cls)
+
+
+def register_norm(kind: str, cls: type | None = None): return _register("norm", kind, cls)
+def register_position(kind: str, cls: type | None = None): return _register("position", kind, cls)
+def register_mixer(kind: str, cls: type | None = None): return _register("mixer", kind, cls)
+def register_feed_forward(kind: str, cls: type | None = None): return _register("feed_forward", kind, cls)
+def register_block(kind: str, cls: type | None = None): return _register("block", kind, cls)
+def register_embedding(kind: str, cls: type | None = None): return _register("embedding", kind, cls)
+def register_head(kind: str, cls: type | None = None): return _register("head", kind, cls)
+
+
+def part_class(family: str, spec: PartSpec) -> type:
+    try:
+        return _REGISTRIES[family][spec.kind]
+    except KeyError:
+        raise KeyError(f"no {family} of kind {spec.kind!r}; registered: {sorted(_REGISTRIES[family])}") from None
+
+
+# ----------------------------------------------------------------------------- what a mixer keeps per sequence
+@dataclass(frozen=True)
+class KVRequest:
+    """Keys and values per token: all of them (``window`` None) or the last ``window``."""
+
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """A fixed-size block per sequence, zeroed when the sequence starts."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+# ----------------------------------------------------------------------------- buffers
+class Workspace:
+    """Named device buffers shared by all layers; sized once, before the first step.
+
+    Parts ``declare`` what they need when they are built; ``allocate`` makes one buffer per name
+    (the largest request wins); ``view`` hands out the leading elements in the wanted shape.
+    No step allocates device memory afterwards.
+    """
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self._need: dict[str, tuple[int, torch.dtype]] = {}
+        self._buffers: dict[str, torch.Tensor] = {}
+
+    def declare(self, name: str, numel: int, dtype: torch.dtype) -> None:
+        old = self._need.get(name)
+        if old is not None and old[1] != dtype:
+            raise ValueError(f"workspace buffer {name!r} requested as {old[1]} and {dtype}")
+        self._need[name] = (max(int(numel), old[0] if old else 0), dtype)
+
+    def allocate(self) -> None:
+        for name, (numel, dtype) in self._need.items():
+            current = self._buffers.get(name)
+            if current is None or current.numel() < numel:
+                self._buffers[name] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+
+    def view(self, name: str, *shape: int) -> torch.Tensor:
+        count = 1
+        for dim in shape:
+            count *= dim
+        buffer = self._buffers[name]
+        if count > buffer.numel():
+            raise ValueError(f"workspace buffer {name!r} holds {buffer.numel()} elements, {count} wanted")
+        return buffer[:count].view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())
+
+
+@dataclass
+class Runtime:
+    """Where and how parts are built: device, activation dtype, token limit per step, buffers."""
+
+    device: torch.device
+    dtype: torch.dtype                      # activations, matrices and caches: bfloat16 or float32
+    max_step_tokens: int
+    max_positions: int
+    workspace: Workspace
+    page_tokens: int = 64
+    options: dict[str, Any] = field(default_factory=dict)
+
+
+class ResidualStream:
+    """The float residual stream [T, H] with at most one pending addition.
+
+    A part's output is not added at once: it is kept as ``pending`` and folded in by the next norm
+    kernel, which reads the stream anyway.
+    """
+
+    def __init__(self, residual: torch.Tensor) -> None:
+        self.residual = residual
+        self.pending: GemmOut | None = None
+
+    def add(self, delta: GemmOut) -> None:
+        if self.pending is not None:
+            raise RuntimeError("the residual stream already has a pending addition; apply a norm first")
+        self.pending = delta
+
+
+TensorSource = Callable[[str], torch.Tensor]
+
+
+def to_device(tensor: torch.Tensor, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    return tensor.to(device=device, dtype=dtype).contiguous()
+
+
+def params_of(spec: PartSpec) -> Mapping[str, Any]:
+    return spec.params

@@ -1,0 +1,48 @@
+"""Arrangements of norm, mixer and feed-forward around the residual stream.
+
+``pre_norm``: h += mixer(norm(h)); h += feed_forward(norm(h)) (qwen_triton/models/core.py:126-152).
+Each addition is left pending on the stream and folded in by the next norm kernel.
+"""
+from __future__ import annotations
+
+from ..config.spec import LayerSpec
+from ..weights.tensors import TensorSpec
+from .base import ResidualStream, Runtime, part_class, register_block
+
+
+@register_block("pre_norm")
+class PreNormBlock:
+    def __init__(self, layer: LayerSpec, runtime: Runtime) -> None:
+        names = self._names(layer)
+        self.mixer_norm = part_class("norm", layer.norm)(layer.norm.params, names["mixer_norm"], runtime)
+        self.feed_forward_norm = part_class("norm", layer.norm)(layer.norm.params, names["feed_forward_norm"], runtime)
+        self.mixer = part_class("mixer", layer.mixer)(layer.mixer.params, names["mixer"], runtime)
+        self.feed_forward = part_class("feed_forward", layer.feed_forward)(layer.feed_forward.params,
+                                                                           names["feed_forward"], runtime)
+
+    @staticmethod
+    def _names(layer: LayerSpec) -> dict[str, str]:
+        p = layer.block.params
+        return {key: f"{layer.prefix}.{p.get(key, key)}" for key in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")}
+
+    @classmethod
+    def expected_tensors(cls, layer: LayerSpec) -> dict[str, TensorSpec]:
+        names = cls._names(layer)
+        out: dict[str, TensorSpec] = {}
+        norm_cls = part_class("norm", layer.norm)
+        out.update(norm_cls.expected_tensors(layer.norm.params, names["mixer_norm"]))
+        out.update(norm_cls.expected_tensors(layer.norm.params, names["feed_forward_norm"]))
+        out.update(part_class("mixer", layer.mixer).expected_tensors(layer.mixer.params, names["mixer"]))
+        out.update(part_class("feed_forward", layer.feed_forward).expected_tensors(layer.feed_forward.params,
+                                                                                   names["feed_forward"]))
+        return out
+
+    def load(self, source) -> None:
+        for part in (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward):
+            part.load(source)
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        x = self.mixer_norm.apply(stream)
+        stream.add(self.mixer.forward(x, ctx, cache))
+        x = self.feed_forward_norm.apply(stream)
+        stream.add(self.feed_forward.forward(x, ctx))

@@ -1,0 +1,50 @@
+"""Dense gated feed-forward: down(act(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:10-22).
+
+gate and up run as one product over the row-concatenated weight [gate; up].
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..ops.kernels import GemmOut
+from ..weights.tensors import TensorSpec
+from .base import Runtime, register_feed_forward
+from .linear import Linear
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP:
+    def __init__(self, params, prefix: str, runtime: Runtime) -> None:
+        self.prefix = prefix
+        self.runtime = runtime
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        activation = params.get("activation", "silu")
+        if activation != "silu":
+            raise ValueError(f"{prefix}: the gated feed-forward kernel computes SiLU, not {activation!r}")
+        self.names = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
+        self.gate_up = Linear("mlp.gate_up", 2 * self.inter, self.hidden, runtime)
+        self.down = Linear("mlp.down", self.hidden, self.inter, runtime)
+        runtime.workspace.declare("mlp.act", runtime.max_step_tokens * self.inter, runtime.dtype)
+
+    @classmethod
+    def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
+        hidden, inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        n = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
+        return {f"{prefix}.{n['gate']}.weight": TensorSpec((inter, hidden)),
+                f"{prefix}.{n['up']}.weight": TensorSpec((inter, hidden)),
+                f"{prefix}.{n['down']}.weight": TensorSpec((hidden, inter))}
+
+    def load(self, source) -> None:
+        n, p = self.names, self.prefix
+        gate, up = source(f"{p}.{n['gate']}.weight"), source(f"{p}.{n['up']}.weight")
+        self.gate_up.set_weight(torch.cat((gate.to(self.runtime.dtype), up.to(self.runtime.dtype)), dim=0))
+        self.down.set_weight(source(f"{p}.{n['down']}.weight"))
+
+    def forward(self, x: torch.Tensor, ctx) -> GemmOut:
+        tokens = x.shape[0]
+        gate_up = self.gate_up(x)
+        act = self.runtime.workspace.view("mlp.act", tokens, self.inter)
+        kernels.swiglu(gate_up, act)
+        return self.down(act)

@@ -1,0 +1,3 @@
+from .sampler import Sampler, SamplingParams, uniform_for
+
+__all__ = ["Sampler", "SamplingParams", "uniform_for"]
