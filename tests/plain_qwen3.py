@@ -207,3 +207,16 @@ def sample_temperature(logits: torch.Tensor, temperature: float, uniform: float)
     target = uniform * float(cumulative[-1])
     index = int(torch.searchsorted(cumulative, torch.tensor(target, dtype=torch.float64), right=True))
     return min(index, logits.numel() - 1)
+
+
+def choice_is_consistent(logits: torch.Tensor, temperature: float, uniform: float, token: int,
+                         slack: float = 1e-4) -> bool:
+    """Whether ``token`` is the inverse-CDF choice for ``uniform`` up to float32 rounding of the
+    cumulative weights: the target mass lies in the token's interval widened by ``slack`` of the total."""
+    scaled = logits.double() / temperature
+    weights = torch.exp(scaled - scaled.max())
+    cumulative = torch.cumsum(weights, dim=0)
+    total = float(cumulative[-1])
+    target = uniform * total
+    lower = float(cumulative[token - 1]) if token > 0 else 0.0
+    return lower - slack * total <= target <= float(cumulative[token]) + slack * total

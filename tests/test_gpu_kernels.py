@@ -1,0 +1,322 @@
+"""Each CUDA kernel alone against a plain float32 PyTorch statement of the same op, at sizes other
+than the engine's tiny configurations (odd widths, head sizes in steps of 16, many groups, shuffled
+pages), and with inputs made so that a fault shows: one far key that dominates, a key just outside
+the window, stale data in reused pages."""
+import math
+
+import pytest
+import torch
+
+from qwen_triton_b200.ops import kernels
+from qwen_triton_b200.ops.kernels import GemmOut
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# float32 1e-4/1e-4 and bfloat16 2e-2/2e-2: the reference's kernel bars (tests/test_kernels.py:28,150)
+TOL = {torch.float32: dict(atol=1e-4, rtol=1e-4), torch.bfloat16: dict(atol=2e-2, rtol=2e-2)}
+DTYPES = [torch.float32, torch.bfloat16]
+PAGE = 64
+
+
+def gen(seed=0):
+    return torch.Generator(device="cpu").manual_seed(seed)
+
+
+def rand(*shape, seed=0, scale=1.0, dtype=torch.float32):
+    return (torch.randn(*shape, generator=gen(seed)) * scale).to(dtype).to(DEV)
+
+
+def close(actual, expected, dtype, what=""):
+    torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), **TOL[dtype], msg=lambda m: f"{what}: {m}")
+
+
+# ----------------------------------------------------------------------------- paged cache helpers
+def paged(dense_k, dense_v, lengths, dtype, ring_tokens=0, seed=0, garbage=True):
+    """Scatter per-sequence dense keys/values [len, nkv, d] into shuffled pages.  Unused room is filled
+    with large garbage so that any read outside a sequence's valid range shows."""
+    nkv, d = dense_k[0].shape[1:]
+    per_seq = [min(math.ceil(n / PAGE), ring_tokens // PAGE) if ring_tokens else math.ceil(n / PAGE) for n in lengths]
+    total = sum(per_seq) + 3
+    order = torch.randperm(total, generator=gen(seed)).tolist()
+    k_cache = torch.full((total, nkv, PAGE, d), 1e4 if garbage else 0.0)
+    v_cache = torch.full((total, nkv, PAGE, d), -1e4 if garbage else 0.0)
+    width = max(per_seq)
+    table = torch.zeros((len(lengths), width), dtype=torch.int32)
+    cursor = 0
+    for b, n in enumerate(lengths):
+        pages = order[cursor:cursor + per_seq[b]]
+        cursor += per_seq[b]
+        table[b, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        first = max(0, n - ring_tokens) if ring_tokens else 0
+        for pos in range(first, n):
+            idx = pos % ring_tokens if ring_tokens else pos
+            k_cache[pages[idx // PAGE], :, idx % PAGE] = dense_k[b][pos]
+            v_cache[pages[idx // PAGE], :, idx % PAGE] = dense_v[b][pos]
+    return k_cache.to(dtype).to(DEV), v_cache.to(dtype).to(DEV), table.to(DEV)
+
+
+def attention_reference(q, k, v, positions, scale, window):
+    """q [n, nq, d] at absolute ``positions``; k/v [len, nkv, d] of the same sequence."""
+    groups = q.shape[1] // k.shape[1]
+    k, v = k.repeat_interleave(groups, dim=1), v.repeat_interleave(groups, dim=1)
+    scores = torch.einsum("qhd,khd->hqk", q, k) * scale
+    keys = torch.arange(k.shape[0])
+    visible = keys[None, :] <= positions[:, None]
+    if window:
+        visible &= keys[None, :] > positions[:, None] - window
+    scores = scores.masked_fill(~visible[None], float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), v)
+
+
+# ----------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    table = rand(77, 200, seed=1, dtype=dtype)
+    ids = torch.tensor([0, 76, 5, 5, 33], dtype=torch.int32, device=DEV)
+    out = torch.full((5, 200), 9.0, device=DEV)
+    kernels.embedding(out, table, ids)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden, splits", [(200, 1), (96, 3), (4100, 2)])
+def test_add_rmsnorm(dtype, hidden, splits):
+    rows, eps = 7, 3e-6
+    residual = rand(rows, hidden, seed=2)
+    delta_dtype = torch.float32 if splits > 1 else dtype
+    delta = rand(splits, rows, hidden, seed=3, dtype=delta_dtype)
+    weight = 1.0 + rand(hidden, seed=4, scale=0.1)
+    expected_stream = residual + delta.float().sum(0)
+    expected = expected_stream * torch.rsqrt(expected_stream.pow(2).mean(-1, keepdim=True) + eps) * weight
+    stream = residual.clone()
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(stream, GemmOut(delta), weight, eps, out)
+    close(stream, expected_stream, torch.float32, "stream")
+    close(out, expected, dtype, "normed")
+    # listed rows only: the stream stays as it was
+    stream = residual.clone()
+    picked = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(stream, GemmOut(delta), weight, eps, out, rows=picked)
+    assert torch.equal(stream, residual)
+    close(out, expected[picked.long()], dtype, "listed rows")
+    # no pending delta
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    kernels.add_rmsnorm(stream, None, weight, eps, out)
+    close(out, residual * torch.rsqrt(residual.pow(2).mean(-1, keepdim=True) + eps) * weight, dtype, "no delta")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq, nkv, d, rotary, ring, splits", [(3, 3, 80, 40, 0, 1), (8, 2, 16, 16, 128, 2), (5, 1, 128, 128, 0, 1)])
+def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits):
+    import plain_qwen3 as plain
+    lengths, past = [70, 3, 100], [130, 0, 20]          # tokens in this step and tokens before it, per sequence
+    tokens = sum(lengths)
+    eps = 1e-5
+    in_dtype = torch.float32 if splits > 1 else dtype
+    qkv = rand(splits, tokens, (nq + 2 * nkv) * d, seed=5, dtype=in_dtype)
+    qw, kw = 1.0 + rand(d, seed=6, scale=0.2), 1.0 + rand(d, seed=7, scale=0.2)
+    max_pos = 400
+    cos, sin = plain.rope_tables(torch.arange(max_pos), rotary, 50000.0, torch.float32)
+    cos_sin = torch.cat((cos, sin), dim=-1).contiguous().to(DEV)
+    token_seq = torch.repeat_interleave(torch.arange(3), torch.tensor(lengths)).int().to(DEV)
+    token_pos = torch.cat([torch.arange(p, p + n) for p, n in zip(past, lengths)]).int().to(DEV)
+    totals = [p + n for p, n in zip(past, lengths)]
+    zeros = [torch.zeros(t, nkv, d) for t in totals]
+    k_cache, v_cache, table = paged(zeros, zeros, totals, dtype, ring_tokens=ring, seed=8, garbage=False)
+    q_out = torch.empty(tokens, nq, d, dtype=dtype, device=DEV)
+    kernels.qk_norm_rope_write(GemmOut(qkv), q_out, k_cache, v_cache, token_seq, token_pos, table, qw, kw, eps, cos_sin,
+                               nq, nkv, d, PAGE, ring)
+    x = qkv.float().sum(0).cpu().view(tokens, nq + 2 * nkv, d)
+    pos = token_pos.cpu().long()
+    q_ref = plain.apply_rope(plain.rms_norm(x[:, :nq], qw.cpu(), eps), cos[pos], sin[pos])
+    k_ref = plain.apply_rope(plain.rms_norm(x[:, nq:nq + nkv], kw.cpu(), eps), cos[pos], sin[pos])
+    v_ref = x[:, nq + nkv:]
+    close(q_out, q_ref, dtype, "q")
+    table_host, k_host, v_host = table.cpu(), k_cache.float().cpu(), v_cache.float().cpu()
+    for t in range(tokens):
+        b, p = int(token_seq[t]), int(pos[t])
+        if ring and p < totals[b] - ring:
+            continue                                      # overwritten by a later token of the ring
+        idx = p % ring if ring else p
+        page = int(table_host[b, idx // PAGE])
+        close(k_host[page, :, idx % PAGE], k_ref[t], dtype, f"k of token {t}")
+        close(v_host[page, :, idx % PAGE], v_ref[t], dtype, f"v of token {t}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    tokens, inter = 5, 336
+    for splits in (1, 3):
+        in_dtype = torch.float32 if splits > 1 else dtype
+        gate_up = rand(splits, tokens, 2 * inter, seed=9, scale=2.0, dtype=in_dtype)
+        out = torch.empty(tokens, inter, dtype=dtype, device=DEV)
+        kernels.swiglu(GemmOut(gate_up), out)
+        total = gate_up.float().sum(0)
+        close(out, torch.nn.functional.silu(total[:, :inter]) * total[:, inter:], dtype, f"splits={splits}")
+
+
+# ----------------------------------------------------------------------------- matrix product
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m, n, k", [(1, 503, 96), (37, 130, 257), (64, 64, 16), (129, 70, 1000)])
+def test_gemm_simt(dtype, m, n, k):
+    a, w = rand(m, k, seed=10, dtype=dtype), rand(n, k, seed=11, scale=0.1, dtype=dtype)
+    expected = a.double() @ w.double().T
+    for out_dtype in {dtype, torch.float32}:
+        out = torch.empty(1, m, n, dtype=out_dtype, device=DEV)
+        kernels.gemm_simt(a, w, GemmOut(out))
+        close(out[0], expected, out_dtype, f"{m}x{n}x{k}")
+
+
+def test_gemm_float32_is_true_float32():
+    """Inputs that a reduced-precision matrix mode would round away: 1 + 2^-12 squared keeps the 2^-11 term."""
+    a = torch.full((4, 64), 1.0 + 2.0 ** -12, device=DEV)
+    w = torch.full((3, 64), 1.0 + 2.0 ** -12, device=DEV)
+    out = torch.empty(1, 4, 3, device=DEV)
+    kernels.gemm_simt(a, w, GemmOut(out))
+    exact = 64 * (1.0 + 2.0 ** -12) ** 2
+    assert abs(float(out[0, 0, 0]) - exact) < 1e-4 and abs(exact - 64.0) > 0.03
+
+
+# ----------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq, nkv, d, window, ring", [(6, 2, 80, None, 0), (4, 4, 16, 40, 128), (8, 1, 128, None, 0), (2, 1, 256, 100, 0)])
+def test_attention_prefill(dtype, nq, nkv, d, window, ring):
+    q_lens, past = [50, 1, 33], [100, 0, 7]
+    if ring:
+        q_lens = [min(n, ring - window + 1) for n in q_lens]       # a step never outruns the ring
+    totals = [p + n for p, n in zip(past, q_lens)]
+    k = [rand(t, nkv, d, seed=20 + i, dtype=dtype).float().cpu() for i, t in enumerate(totals)]
+    v = [rand(t, nkv, d, seed=30 + i, dtype=dtype).float().cpu() for i, t in enumerate(totals)]
+    k_cache, v_cache, table = paged(k, v, totals, dtype, ring_tokens=ring, seed=1)
+    q = rand(sum(q_lens), nq, d, seed=40, dtype=dtype)
+    out = torch.empty_like(q)
+    seq_start = torch.tensor([0, *torch.tensor(q_lens).cumsum(0).tolist()], dtype=torch.int32, device=DEV)
+    seq_past = torch.tensor(past, dtype=torch.int32, device=DEV)
+    scale = d ** -0.5
+    kernels.attention_prefill(q, k_cache, v_cache, out, table, seq_start, seq_past, max(q_lens), nkv, PAGE, ring, window, scale)
+    start = 0
+    for b, n in enumerate(q_lens):
+        ref = attention_reference(q[start:start + n].float().cpu(), k[b], v[b], torch.arange(past[b], past[b] + n), scale, window)
+        close(out[start:start + n], ref, dtype, f"sequence {b}")
+        start += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq, nkv, d, window, ring, splits", [
+    (6, 2, 80, None, 0, 1), (6, 2, 80, None, 0, 5), (4, 4, 16, 40, 128, 2), (16, 1, 128, None, 0, 3),
+    (32, 8, 128, None, 0, 4), (5, 5, 112, 300, 0, 7), (10, 2, 48, None, 0, 64)])
+def test_attention_decode(dtype, nq, nkv, d, window, ring, splits):
+    lengths = [700, 1, 65, 129]
+    k = [rand(t, nkv, d, seed=50 + i, dtype=dtype).float().cpu() for i, t in enumerate(lengths)]
+    v = [rand(t, nkv, d, seed=60 + i, dtype=dtype).float().cpu() for i, t in enumerate(lengths)]
+    k_cache, v_cache, table = paged(k, v, lengths, dtype, ring_tokens=ring, seed=2)
+    q = rand(len(lengths), nq, d, seed=70, dtype=dtype)
+    out = torch.empty_like(q)
+    seq_len = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    part_acc = torch.full((len(lengths) * nq * splits * d,), float("nan"), device=DEV)
+    part_ml = torch.full((len(lengths) * nq * splits * 2,), float("nan"), device=DEV)
+    scale = d ** -0.5
+    kernels.attention_decode(q, k_cache, v_cache, out, table, seq_len, nkv, PAGE, ring, window, scale, splits, part_acc, part_ml)
+    for b, n in enumerate(lengths):
+        ref = attention_reference(q[b:b + 1].float().cpu(), k[b], v[b], torch.tensor([n - 1]), scale, window)
+        close(out[b:b + 1], ref, dtype, f"sequence {b}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mode", ["decode", "prefill"])
+def test_one_far_key_among_hundreds_wins(dtype, mode):
+    """Key 3 of 700 gets a score far above the rest; the output must be its value row."""
+    nq, nkv, d, n = 4, 2, 64, 700
+    k = torch.randn(n, nkv, d, generator=gen(80)) * 0.1
+    v = torch.randn(n, nkv, d, generator=gen(81))
+    query = torch.randn(1, nq, d, generator=gen(82)) * 0.1
+    for h in range(nq):
+        k[3, h // 2] = 0.0
+    k[3, :, 0] = 40.0
+    query[0, :, 0] = 40.0
+    k, v = k.to(dtype).float(), v.to(dtype).float()
+    k_cache, v_cache, table = paged([k], [v], [n], dtype, seed=3)
+    q = query.to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    if mode == "decode":
+        kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
+                                 None, 1.0, 4, torch.empty(nq * 4 * d, device=DEV), torch.empty(nq * 4 * 2, device=DEV))
+    else:
+        kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                  torch.tensor([n - 1], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, None, 1.0)
+    expected = v[3].repeat_interleave(2, dim=0)[None]
+    close(out, expected, dtype, "far key")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mode", ["decode", "prefill"])
+def test_window_edge(dtype, mode):
+    """The key just outside the window carries a huge score and a huge value: it must not be seen; the
+    key just inside carries the second-largest score: it must dominate."""
+    nq, nkv, d, n, window = 2, 1, 32, 200, 37
+    k = torch.randn(n, nkv, d, generator=gen(90)) * 0.05
+    v = torch.randn(n, nkv, d, generator=gen(91))
+    last = n - 1
+    outside, inside = last - window, last - window + 1
+    k[outside, :, 1] = 60.0
+    v[outside] = 1000.0
+    k[inside, :, 1] = 30.0
+    query = torch.zeros(1, nq, d)
+    query[0, :, 1] = 30.0
+    k, v = k.to(dtype).float(), v.to(dtype).float()
+    k_cache, v_cache, table = paged([k], [v], [n], dtype, seed=4)
+    q = query.to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    if mode == "decode":
+        kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
+                                 window, 1.0, 3, torch.empty(nq * 3 * d, device=DEV), torch.empty(nq * 3 * 2, device=DEV))
+    else:
+        kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                  torch.tensor([last], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, window, 1.0)
+    close(out, v[inside].expand(1, nq, d), dtype, "window edge")
+
+
+# ----------------------------------------------------------------------------- sampling
+def test_argmax_ties_go_to_the_lowest_id():
+    logits = rand(5, 1500, seed=100)
+    logits[0, 700] = logits[0, 1400] = 50.0
+    logits[1, 0] = 50.0
+    logits[2, 1499] = 50.0
+    logits[3] = -float("inf")
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    kernels.argmax(logits, out)
+    assert out.tolist() == [700, 0, 1499, 0, int(logits[4].argmax())]
+
+
+def test_sample_follows_the_inverse_cdf():
+    import plain_qwen3 as plain
+    rows, vocab = 64, 5003
+    logits = rand(rows, vocab, seed=101, scale=3.0)
+    temps = torch.full((rows,), 0.8, device=DEV)
+    uniforms = torch.rand(rows, generator=gen(102))
+    uniforms[0] = 0.0
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    kernels.sample(logits, temps, uniforms.to(DEV), out)
+    host = logits.cpu()
+    for r in range(rows):
+        assert plain.choice_is_consistent(host[r], 0.8, float(uniforms[r]), int(out[r])), r
+    assert int(out[0]) == 0
+    # the empirical distribution of many draws follows softmax(logits / T)
+    small = rand(1, 7, seed=103).repeat(4000, 1).contiguous()
+    draws = torch.empty(4000, dtype=torch.int32, device=DEV)
+    kernels.sample(small, torch.full((4000,), 1.3, device=DEV), torch.rand(4000, generator=gen(104)).to(DEV), draws)
+    freq = torch.bincount(draws.cpu().long(), minlength=7).float() / 4000
+    assert (freq - torch.softmax(small[0].cpu() / 1.3, 0)).abs().max() < 0.03
+
+
+def test_kernels_refuse_what_they_cannot_run():
+    with pytest.raises(kernels.KernelError, match="CUDA tensor"):
+        kernels.argmax(torch.zeros(1, 4), torch.zeros(1, dtype=torch.int32))
+    q = torch.zeros(1, 2, 272, device=DEV)
+    cache = torch.zeros(1, 1, PAGE, 272, device=DEV)
+    with pytest.raises(kernels.KernelError, match="head_dim"):
+        kernels.attention_decode(q, cache, cache, torch.empty_like(q), torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                 torch.ones(1, dtype=torch.int32, device=DEV), 1, PAGE, 0, None, 1.0, 1, None, None)
+    with pytest.raises(kernels.KernelError, match="do not fit"):
+        kernels.gemm_simt(torch.zeros(2, 8, device=DEV), torch.zeros(4, 8, device=DEV), GemmOut(torch.zeros(2, 2, 4, device=DEV)))

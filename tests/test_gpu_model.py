@@ -1,0 +1,208 @@
+"""The engine against the plain implementation, in float32 and bfloat16, under every way of cutting
+the work: whole, last 32 tokens one by one, unequal batches whose slots are used again, long
+decoding, the first tokens, and generation through the entry point."""
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from gpu_util import PRESETS, assert_close, make_engine, model_folder, oracle, plain_logits, random_tokens, run_whole
+from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset
+
+pytestmark = pytest.mark.gpu
+DTYPES = ("fp32", "bf16")
+LENGTHS = {"tiny-a": (5, 9, 17, 70), "tiny-b": (1, 7, 12, 31, 97), "tiny-c": (3, 26, 49, 130)}
+
+
+@pytest.fixture(scope="module", params=[(p, d) for p in PRESETS for d in DTYPES], ids=lambda v: f"{v[0]}-{v[1]}")
+def case(request):
+    preset, dtype = request.param
+    # a small chunk limit makes the windowed configuration wrap its ring within the test lengths
+    engine = make_engine(preset, dtype, max_tokens=1024, chunk_tokens=16)
+    yield preset, dtype, engine
+    assert engine.cache.book.live_slots() == []
+    engine.cache.book.check()
+
+
+def requests_of(preset):
+    return [random_tokens(preset, n, seed) for seed, n in enumerate(LENGTHS[preset])]
+
+
+def test_each_request_alone_and_whole(case):
+    preset, dtype, engine = case
+    for tokens in requests_of(preset):
+        assert_close(run_whole(engine, tokens), plain_logits(preset, dtype, tokens), dtype, f"whole, {len(tokens)} tokens")
+
+
+def test_last_32_tokens_one_by_one(case):
+    preset, dtype, engine = case
+    for tokens in requests_of(preset):
+        if len(tokens) <= 33:
+            continue
+        head = len(tokens) - 32
+        slot = engine.new_sequence()
+        rows = [engine.step([StepEntry(slot, tokens[:head], list(range(head)))])]
+        for token in tokens[head:]:
+            rows.append(engine.step([StepEntry(slot, [token], [0])]))
+        engine.release(slot)
+        assert_close(torch.cat(rows), plain_logits(preset, dtype, tokens), dtype, f"tail32, {len(tokens)} tokens")
+
+
+def test_unequal_batches_one_after_another(case):
+    """Batches of unequal lengths; prompts in one step, then one token each; shorter requests end
+    earlier; the cache is small enough that later batches get the slots and pages of earlier ones."""
+    preset, dtype, _ = case
+    engine = make_engine(preset, dtype, max_tokens=320, chunk_tokens=16)
+    requests = requests_of(preset) + [random_tokens(preset, n, 50 + n) for n in (2, 40, 11, 64, 65)]
+    collected = {i: [] for i in range(len(requests))}
+    used_slots = []
+    for start in range(0, len(requests), 3):
+        batch = list(range(start, min(start + 3, len(requests))))
+        slots = {i: engine.new_sequence() for i in batch}
+        used_slots += list(slots.values())
+        prompt = {i: max(1, len(requests[i]) // 2) for i in batch}
+        logits = engine.step([StepEntry(slots[i], requests[i][:prompt[i]], list(range(prompt[i]))) for i in batch])
+        offset = 0
+        for i in batch:
+            collected[i].append(logits[offset:offset + prompt[i]])
+            offset += prompt[i]
+        position = dict(prompt)
+        active = [i for i in batch if position[i] < len(requests[i])]
+        for i in batch:
+            if i not in active:
+                engine.release(slots[i])
+        while active:
+            logits = engine.step([StepEntry(slots[i], [requests[i][position[i]]], [0]) for i in active])
+            for row, i in enumerate(active):
+                collected[i].append(logits[row:row + 1])
+                position[i] += 1
+            for i in [i for i in active if position[i] == len(requests[i])]:
+                engine.release(slots[i])                       # shorter requests end earlier
+            active = [i for i in active if position[i] < len(requests[i])]
+        engine.cache.book.check()
+    assert len(set(used_slots)) < len(used_slots)              # slots were used again
+    for i, tokens in enumerate(requests):
+        assert_close(torch.cat(collected[i]), plain_logits(preset, dtype, tokens), dtype, f"batched, request {i} ({len(tokens)} tokens)")
+
+
+def test_long_decoding(case):
+    preset, dtype, engine = case
+    tokens = random_tokens(preset, 300, 77)
+    slot = engine.new_sequence()
+    rows = [engine.step([StepEntry(slot, tokens[:3], [0, 1, 2])])]
+    for token in tokens[3:]:
+        rows.append(engine.step([StepEntry(slot, [token], [0])]))
+    engine.release(slot)
+    assert_close(torch.cat(rows), plain_logits(preset, dtype, tokens), dtype, "long decoding")
+
+
+def test_first_tokens_of_a_sequence(case):
+    preset, dtype, engine = case
+    tokens = random_tokens(preset, 4, 5)
+    slot = engine.new_sequence()
+    rows = [engine.step([StepEntry(slot, [t], [0])]) for t in tokens]       # the very first token is a step of its own
+    engine.release(slot)
+    assert_close(torch.cat(rows), plain_logits(preset, dtype, tokens), dtype, "first tokens")
+
+
+def test_chunks_of_a_prompt(case):
+    """A prompt cut into steps of several tokens (continuation chunks with a past)."""
+    preset, dtype, engine = case
+    tokens = random_tokens(preset, 75, 9)
+    slot = engine.new_sequence()
+    rows, start = [], 0
+    for size in (7, 1, 30, 20, 17):
+        rows.append(engine.step([StepEntry(slot, tokens[start:start + size], list(range(size)))]))
+        start += size
+    engine.release(slot)
+    assert_close(torch.cat(rows), plain_logits(preset, dtype, tokens), dtype, "chunked prompt")
+
+
+def test_passes_inside_one_step_change_nothing(case):
+    """A step larger than the per-pass token limit is cut inside the engine; wanted places keep their order."""
+    preset, dtype, _ = case
+    engine = make_engine(preset, dtype, max_tokens=1024, max_step_tokens=24, chunk_tokens=16)
+    requests = [random_tokens(preset, n, 30 + n) for n in (40, 5, 33)]
+    slots = [engine.new_sequence() for _ in requests]
+    wants = [[39, 0, 17], [4], list(range(33))]
+    logits = engine.step([StepEntry(s, r, w) for s, r, w in zip(slots, requests, wants)])
+    for slot in slots:
+        engine.release(slot)
+    expected = torch.cat([plain_logits(preset, dtype, r)[w] for r, w in zip(requests, wants)])
+    assert_close(logits, expected, dtype, "passes inside a step")
+
+
+def test_greedy_generation_through_the_entry_point(case):
+    preset, dtype, _ = case
+    raw, weights = oracle(preset, dtype)
+    model = QwenB200ForCausalLM.from_pretrained_hf(model_folder(preset, dtype), dtype=dtype, max_tokens=1024)
+    prompts = [r[:max(1, len(r) // 2)] for r in requests_of(preset)][:3]
+    steps = 8
+    results = model.generate(prompts, max_new_tokens=steps, ignore_eos=True)
+    for prompt, result in zip(prompts, results):
+        assert len(result.tokens) == steps and result.finish_reason == "length"
+        if dtype == "fp32":
+            assert result.tokens == plain.greedy_generate(raw, weights, prompt, steps)
+        else:
+            # bfloat16 may pick another token where two logits are closer than its rounding: every chosen
+            # token must be within tolerance of the oracle's best at that place, given the engine's own prefix
+            sequence = list(prompt)
+            for token in result.tokens:
+                row = plain.forward(raw, weights, sequence)[-1]
+                assert float(row.max() - row[token]) <= 4e-2, (sequence, token)
+                sequence.append(token)
+    rect = torch.tensor([requests_of(preset)[-1][:6], requests_of(preset)[-1][6:12]])
+    out = model.greedy_generate(rect, max_new_tokens=3)
+    assert out.shape == (2, 9) and torch.equal(out[:, :6], rect)
+    kept = model.forward(rect, logits_to_keep=1).logits
+    assert kept.shape == (2, 1, load_preset(preset).vocab_size)
+    assert_close(kept[0, 0], plain_logits(preset, dtype, rect[0].tolist())[-1], dtype, "logits_to_keep=1")
+
+
+def test_temperature_sampling_with_a_fixed_seed():
+    """Four prompts of lengths 1/7/12/31, ten steps at temperature 0.8 (float32): the tokens are the
+    oracle's inverse-CDF choice with the same uniform numbers (up to float32 rounding of the cumulative weights), and do not depend on the batch."""
+    preset, dtype = "tiny-b", "fp32"
+    raw, weights = oracle(preset, dtype)
+    model = QwenB200ForCausalLM.from_pretrained_hf(model_folder(preset, dtype), dtype=dtype, max_tokens=1024)
+    prompts = [random_tokens(preset, n, 200 + n) for n in (1, 7, 12, 31)]
+    results = model.generate(prompts, max_new_tokens=10, temperature=0.8, seed=11, ignore_eos=True)
+    for index, (prompt, result) in enumerate(zip(prompts, results)):
+        sequence = list(prompt)
+        for step, token in enumerate(result.tokens):
+            row = plain.forward(raw, weights, sequence)[-1]
+            assert plain.choice_is_consistent(row, 0.8, plain.uniform_for(11, index, step), token), (index, step)
+            sequence.append(token)
+    again = model.generate(prompts, max_new_tokens=10, temperature=0.8, seed=11, ignore_eos=True, max_batch_size=2)
+    assert [r.tokens for r in again] == [r.tokens for r in results]
+    assert [r.tokens for r in model.generate(prompts, max_new_tokens=10, temperature=0.8, seed=12, ignore_eos=True)] != \
+        [r.tokens for r in results]
+
+
+def test_stop_token_ends_a_sequence_early():
+    preset, dtype = "tiny-a", "fp32"
+    raw, weights = oracle(preset, dtype)
+    model = QwenB200ForCausalLM.from_pretrained_hf(model_folder(preset, dtype), dtype=dtype, max_tokens=1024)
+    prompts = [random_tokens(preset, n, 300 + n) for n in (5, 9, 17)]
+    free_run = [plain.greedy_generate(raw, weights, p, 8) for p in prompts]
+    stop = free_run[1][2]
+    results = model.generate(prompts, max_new_tokens=8, stop_token_ids=[stop], ignore_eos=True)
+    for expected, result in zip(free_run, results):
+        cut = expected.index(stop) + 1 if stop in expected else len(expected)
+        assert result.tokens == expected[:cut]
+        assert result.finish_reason == ("stop" if stop in expected else "length")
+    assert model.engine.cache.book.live_slots() == []
+
+
+def test_errors_are_loud(case):
+    preset, dtype, engine = case
+    slot = engine.new_sequence()
+    with pytest.raises(ValueError, match="outside"):
+        engine.step([StepEntry(slot, [load_preset(preset).vocab_size], [0])])
+    with pytest.raises(ValueError, match="wanted place"):
+        engine.step([StepEntry(slot, [1, 2], [2])])
+    with pytest.raises(ValueError, match="twice"):
+        engine.step([StepEntry(slot, [1], []), StepEntry(slot, [2], [])])
+    engine.release(slot)
+    with pytest.raises(ValueError, match="not in use"):
+        engine.step([StepEntry(slot, [1], [0])])
+    assert engine.length is not None

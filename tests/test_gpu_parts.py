@@ -1,0 +1,307 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with state of
+its own that is registered, built and stepped without touching the library's files."""
+import tempfile
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from gpu_util import TOL, assert_close
+from qwen_triton_b200 import Engine, StepEntry, register_architecture
+from qwen_triton_b200.cache import SequenceCache
+from qwen_triton_b200.config import LayerCall, LayerSpec, ModelSpec, PartSpec
+from qwen_triton_b200.engine.step import StepContext
+from qwen_triton_b200.ops.kernels import GemmOut
+from qwen_triton_b200.parts import (ResidualStream, Runtime, StateRequest, Workspace, part_class, register_mixer)
+from qwen_triton_b200.weights import write_safetensors
+from qwen_triton_b200.weights.tensors import TensorSpec
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = {"fp32": torch.float32, "bf16": torch.bfloat16}
+
+
+def runtime(dtype, max_tokens=256, max_positions=512):
+    return Runtime(device=DEV, dtype=DTYPES[dtype], max_step_tokens=max_tokens, max_positions=max_positions,
+                   workspace=Workspace(DEV))
+
+
+def weights_for(expected, dtype, seed=0):
+    out = {}
+    for index, (name, spec) in enumerate(sorted(expected.items())):
+        g = torch.Generator().manual_seed(seed * 100 + index)
+        values = torch.randn(spec.shape, generator=g) * (0.2 if spec.role == "vector" else 0.08) + spec.init_mean
+        out[name] = values.to(DTYPES[dtype])
+    return out
+
+
+def context(rt, cache, lengths, past=None):
+    past = past or [0] * len(lengths)
+    slots = [cache.alloc() for _ in lengths]
+    for slot, n, p in zip(slots, lengths, past):
+        cache.book.extend(slot, p + n)
+    import numpy as np
+    tables = []
+    for g in range(len(cache.groups)):
+        width = max(len(cache.book.pages(s, g)) for s in slots)
+        table = np.zeros((len(slots), width), dtype=np.int32)
+        for i, s in enumerate(slots):
+            table[i, :len(cache.book.pages(s, g))] = cache.book.pages(s, g)
+        tables.append(table)
+    meta = torch.zeros(StepContext.meta_size(sum(lengths), len(lengths), [t.shape[1] for t in tables]), dtype=torch.int32, device=DEV)
+    ctx = StepContext(device=DEV, meta=meta)
+    ctx.fill(slots, [[0] * n for n in lengths], past, [], tables)
+    return ctx, slots
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_norm_part(dtype):
+    rt = runtime(dtype)
+    norm = part_class("norm", PartSpec("rmsnorm"))({"size": 200, "eps": 2e-5}, "n", rt)
+    expected = norm.expected_tensors({"size": 200, "eps": 2e-5}, "n")
+    assert list(expected) == ["n.weight"] and expected["n.weight"].role == "vector"
+    w = weights_for(expected, dtype)
+    norm.load(w.__getitem__)
+    rt.workspace.allocate()
+    x = torch.randn(9, 200, generator=torch.Generator().manual_seed(1))
+    delta = (torch.randn(9, 200, generator=torch.Generator().manual_seed(2))).to(DTYPES[dtype])
+    stream = ResidualStream(x.to(DEV).clone())
+    stream.add(GemmOut(delta.to(DEV)[None]))
+    out = norm.apply(stream)
+    assert stream.pending is None
+    want = plain.rms_norm(x + delta.float(), w["n.weight"].float(), 2e-5)
+    assert_close(out, want, dtype, "norm part")
+    assert norm.weight.dtype == torch.float32                    # vectors are kept in 32-bit
+
+
+def test_position_part_matches_the_formula():
+    rt = runtime("fp32")
+    rope = part_class("position", PartSpec("rope"))({"theta": 1e6, "rotary_dim": 24, "head_dim": 32}, rt)
+    table = rope.table(300).cpu()
+    cos, sin = plain.rope_tables(torch.arange(300), 24, 1e6, torch.float32)
+    assert table.dtype == torch.float32 and torch.equal(table, torch.cat((cos, sin), -1))
+    assert part_class("position", PartSpec("none"))({}, rt).table(10) is None
+    with pytest.raises(ValueError):
+        part_class("position", PartSpec("rope"))({"theta": 1e4, "rotary_dim": 34, "head_dim": 32}, rt)
+
+
+ATTN = {"hidden_size": 72, "num_heads": 6, "num_kv_heads": 2, "head_dim": 48, "qk_norm": True, "qk_norm_eps": 1e-5,
+        "position": PartSpec("rope", {"theta": 7e4, "rotary_dim": 48, "head_dim": 48}),
+        "q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm"}
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("window", [None, 10])
+def test_attention_part(dtype, window):
+    rt = runtime(dtype)
+    params = {**ATTN, "window": window}
+    mixer = part_class("mixer", PartSpec("attention"))(params, "a", rt)
+    w = weights_for(mixer.expected_tensors(params, "a"), dtype, seed=3)
+    mixer.load(w.__getitem__)
+    rt.workspace.allocate()
+    cache = SequenceCache([mixer.cache_request()], [None], max_tokens=512, max_seq_len=512, dtype=DTYPES[dtype], device=DEV,
+                          chunk_tokens=64)
+    lengths = [40, 7]
+    ctx, _ = context(rt, cache, lengths)
+    x = (torch.randn(sum(lengths), 72, generator=torch.Generator().manual_seed(4)) * 0.5).to(DTYPES[dtype])
+    out = mixer.forward(x.to(DEV), ctx, cache.view(0)).value()
+    cfg = {"heads": 6, "kv_heads": 2, "head_dim": 48, "eps": 1e-5, "rotary_dim": 48, "theta": 7e4}
+    wf = {k: v.float() for k, v in w.items()}
+    start = 0
+    for n in lengths:
+        want = plain.attention_layer(x[start:start + n].float(), wf, "a", cfg, window)
+        assert_close(out[start:start + n], want, dtype, f"attention part, window={window}")
+        start += n
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_feed_forward_part(dtype):
+    rt = runtime(dtype)
+    params = {"hidden_size": 72, "intermediate_size": 200, "activation": "silu", "gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
+    ff = part_class("feed_forward", PartSpec("gated_mlp"))(params, "m", rt)
+    w = weights_for(ff.expected_tensors(params, "m"), dtype, seed=5)
+    ff.load(w.__getitem__)
+    rt.workspace.allocate()
+    x = (torch.randn(11, 72, generator=torch.Generator().manual_seed(6))).to(DTYPES[dtype])
+    out = ff.forward(x.to(DEV), None).value()
+    assert_close(out, plain.gated_mlp(x.float(), {k: v.float() for k, v in w.items()}, "m"), dtype, "feed-forward part")
+    with pytest.raises(ValueError, match="SiLU"):
+        part_class("feed_forward", PartSpec("gated_mlp"))({**params, "activation": "gelu"}, "m", rt)
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_block_part(dtype):
+    rt = runtime(dtype)
+    layer = LayerSpec(prefix="model.layers.0",
+                      block=PartSpec("pre_norm", {"mixer": "self_attn", "feed_forward": "mlp", "mixer_norm": "input_layernorm",
+                                                  "feed_forward_norm": "post_attention_layernorm"}),
+                      mixer=PartSpec("attention", {**ATTN, "window": None}),
+                      feed_forward=PartSpec("gated_mlp", {"hidden_size": 72, "intermediate_size": 136, "activation": "silu"}),
+                      norm=PartSpec("rmsnorm", {"size": 72, "eps": 1e-5}))
+    block = part_class("block", layer.block)(layer, rt)
+    w = weights_for(block.expected_tensors(layer), dtype, seed=7)
+    assert len(w) == 11
+    block.load(w.__getitem__)
+    rt.workspace.declare("residual", 256 * 72, torch.float32)
+    rt.workspace.allocate()
+    cache = SequenceCache([block.mixer.cache_request()], [None], max_tokens=512, max_seq_len=512, dtype=DTYPES[dtype], device=DEV)
+    ctx, _ = context(rt, cache, [23])
+    x = torch.randn(23, 72, generator=torch.Generator().manual_seed(8)).to(DTYPES[dtype]).float()
+    stream = ResidualStream(x.to(DEV).clone())
+    block.forward(stream, ctx, cache.view(0))
+    got = stream.residual + stream.pending.value()
+    cfg = {"heads": 6, "kv_heads": 2, "head_dim": 48, "eps": 1e-5, "rotary_dim": 48, "theta": 7e4, "window": None,
+           "layer_types": ["full_attention"]}
+    want = plain.decoder_layer(x, {k: v.float() for k, v in w.items()}, 0, cfg)
+    assert_close(got, want, dtype, "block part")
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state of its own
+class ToyDecayMixer:
+    """s_t = decay * s_{t-1} + x_t W per sequence, output s_t: a recurrent mixer whose only memory is a
+    fixed-size state block per sequence.  Written with plain tensor operations; it exists to show that
+    the library's registries, cache and step function carry a mixer they have never seen."""
+
+    def __init__(self, params, prefix, runtime):
+        self.prefix, self.runtime = prefix, runtime
+        self.hidden, self.decay = int(params["hidden_size"]), float(params["decay"])
+        self.weight = None
+
+    @classmethod
+    def expected_tensors(cls, params, prefix):
+        return {f"{prefix}.mix.weight": TensorSpec((int(params["hidden_size"]),) * 2, init_std=0.1)}
+
+    def load(self, source):
+        self.weight = source(f"{self.prefix}.mix.weight").to(self.runtime.device, torch.float32)
+
+    def cache_request(self):
+        return StateRequest((self.hidden,), torch.float32)
+
+    def forward(self, x, ctx, cache):
+        projected = x.float() @ self.weight.T
+        out = torch.empty_like(projected)
+        starts, slots = ctx.seq_start.tolist(), ctx.slots.tolist()
+        for b, slot in enumerate(slots):
+            state = cache.state[slot]
+            for t in range(starts[b], starts[b + 1]):
+                state = self.decay * state + projected[t]
+                out[t] = state
+            cache.state[slot] = state
+        return GemmOut(out.to(self.runtime.dtype)[None].contiguous())
+
+
+class ToyConfig:
+    def __init__(self, raw):
+        self.raw = dict(raw)
+
+    @classmethod
+    def from_hf_config(cls, raw):
+        return cls(raw)
+
+    def to_hf_dict(self):
+        return dict(self.raw)
+
+    def model_spec(self):
+        r = self.raw
+        hidden = r["hidden_size"]
+        norm = PartSpec("rmsnorm", {"size": hidden, "eps": r["eps"]})
+        block = PartSpec("pre_norm", {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "norm1", "feed_forward_norm": "norm2"})
+        ff = PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": r["inter"], "activation": "silu"})
+        toy = PartSpec("toy_decay", {"hidden_size": hidden, "decay": r["decay"]})
+        attn = PartSpec("attention", {"hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "window": None,
+                                      "qk_norm": False, "position": PartSpec("none")})
+        layers = (LayerSpec("blocks.0", block, toy, ff, norm), LayerSpec("blocks.1", block, attn, ff, norm))
+        # layer 0 runs twice (two state entries), and the last call reads the keys the attention call before it wrote
+        schedule = (LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache_of=1))
+        return ModelSpec(architecture="ToyForCausalLM", vocab_size=r["vocab"], hidden_size=hidden,
+                         embedding=PartSpec("token_embedding", {"name": "embed.weight"}), layers=layers, schedule=schedule,
+                         final_norm=PartSpec("rmsnorm", {"size": hidden, "eps": r["eps"], "name": "final"}),
+                         head=PartSpec("linear_head", {"name": "head.weight", "tied_to": "embed.weight"}), max_positions=256)
+
+
+def toy_oracle(raw, w, tokens):
+    """The toy model in plain float32, whole sequence."""
+    hidden, eps = raw["hidden_size"], raw["eps"]
+    x = w["embed.weight"][torch.tensor(tokens)]
+    n = len(tokens)
+
+    def ff(h, p):
+        return plain.gated_mlp(h, {k.replace(f"{p}.ff.", "m.", 1): v for k, v in w.items() if k.startswith(f"{p}.ff.")}, "m")
+
+    def toy(h, p):
+        proj = h @ w[f"{p}.mixer.mix.weight"].T
+        state, out = torch.zeros(hidden), []
+        for t in range(n):
+            state = raw["decay"] * state + proj[t]
+            out.append(state)
+        return torch.stack(out)
+
+    def attn(h, p):
+        q = (h @ w[f"{p}.mixer.q_proj.weight"].T).view(n, 2, 16)
+        k = (h @ w[f"{p}.mixer.k_proj.weight"].T).view(n, 1, 16)
+        v = (h @ w[f"{p}.mixer.v_proj.weight"].T).view(n, 1, 16)
+        return plain.attention_scores(q, k, v, 16 ** -0.5, None).reshape(n, 32) @ w[f"{p}.mixer.o_proj.weight"].T, k, v
+
+    kept = None
+    for position, (layer, mix) in enumerate([("blocks.0", "toy"), ("blocks.1", "attn"), ("blocks.0", "toy"), ("blocks.1", "shared")]):
+        h = plain.rms_norm(x, w[f"{layer}.norm1.weight"], eps)
+        if mix == "toy":
+            x = x + toy(h, layer)
+        elif mix == "attn":
+            delta, k, v = attn(h, layer)
+            kept = (k, v)
+            x = x + delta
+        else:                                                  # queries of this call over the keys and values of the earlier call
+            q = (h @ w[f"{layer}.mixer.q_proj.weight"].T).view(n, 2, 16)
+            x = x + plain.attention_scores(q, kept[0], kept[1], 16 ** -0.5, None).reshape(n, 32) @ w[f"{layer}.mixer.o_proj.weight"].T
+        x = x + ff(plain.rms_norm(x, w[f"{layer}.norm2.weight"], eps), layer)
+    return plain.rms_norm(x, w["final.weight"], eps) @ w["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    register_mixer("toy_decay", ToyDecayMixer)
+    register_architecture("ToyForCausalLM", ToyConfig)
+    raw = {"architectures": ["ToyForCausalLM"], "hidden_size": 40, "inter": 56, "vocab": 97, "eps": 1e-5, "decay": 0.8}
+    from qwen_triton_b200.config import config_from_dict
+    from qwen_triton_b200.engine.model import expected_tensors
+    config = config_from_dict(raw)
+    assert isinstance(config, ToyConfig)
+    expected = expected_tensors(config.model_spec())
+    weights = weights_for(expected, dtype, seed=9)
+    with tempfile.TemporaryDirectory() as folder:
+        write_safetensors(f"{folder}/model.safetensors", weights)
+        import json
+        with open(f"{folder}/config.json", "w") as handle:
+            json.dump(raw, handle)
+        engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
+    assert len(engine.cache.groups) == 1 and len(engine.cache.groups[0].owners) == 1      # one attention entry, shared by two calls
+    assert engine.cache.view(0).state is not engine.cache.view(2).state                   # the layer that runs twice has two states
+    wf = {k: v.float() for k, v in weights.items()}
+    requests = [[5, 9, 2, 77, 30, 11, 4, 8, 60, 1, 13], [96, 0, 41]]
+    whole = {}
+    for i, tokens in enumerate(requests):
+        slot = engine.new_sequence()
+        whole[i] = engine.step([StepEntry(slot, tokens, list(range(len(tokens))))])
+        engine.release(slot)
+        assert_close(whole[i], toy_oracle(raw, wf, tokens), dtype, f"toy model, request {i} whole")
+    # both requests as a batch: prompts of unequal length, then one token each; slots are the ones just given back,
+    # so their state must have been cleared
+    slots = [engine.new_sequence() for _ in requests]
+    rows = {0: [], 1: []}
+    first = engine.step([StepEntry(slots[0], requests[0][:4], [0, 1, 2, 3]), StepEntry(slots[1], requests[1][:1], [0])])
+    rows[0].append(first[:4])
+    rows[1].append(first[4:])
+    for t in range(7):
+        entries, owners = [], []
+        for i in (0, 1):
+            at = (4 if i == 0 else 1) + t
+            if at < len(requests[i]):
+                entries.append(StepEntry(slots[i], [requests[i][at]], [0]))
+                owners.append(i)
+        out = engine.step(entries)
+        for row, i in enumerate(owners):
+            rows[i].append(out[row:row + 1])
+    for i in (0, 1):
+        assert_close(torch.cat(rows[i]), toy_oracle(raw, wf, requests[i]), dtype, f"toy model, request {i} step by step")
+        engine.release(slots[i])
