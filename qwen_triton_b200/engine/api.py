@@ -14,7 +14,7 @@ import torch
 from ..config import config_from_dict, load_config
 from ..sampling import Sampler, SamplingParams
 from .engine import Engine, parse_dtype
-from .generate import GenerationResult, generate
+from .generate import BatchRun, GenerationResult, generate, stop_set
 from .step import StepEntry
 
 
@@ -104,6 +104,16 @@ class QwenB200ForCausalLM:
         return generate(self.engine, prompts, max_new_tokens=max_new_tokens,
                         sampling=SamplingParams(temperature=temperature, seed=seed), stop_token_ids=stop_token_ids,
                         ignore_eos=ignore_eos, max_batch_size=max_batch_size, sampler=self.sampler)
+
+    def start_batch(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16, temperature: float = 0.0,
+                    seed: int = 0, stop_token_ids: Sequence[int] | None = None, ignore_eos: bool = False) -> BatchRun:
+        """Step-by-step generation of one batch: ``run.start()`` runs the prompts and returns each request's
+        first token, every ``run.advance()`` one more token per request still going; ``run.results`` collects
+        them and ``run.close()`` gives the cache back.  ``generate`` is this, looped over batches."""
+        results = [GenerationResult() for _ in prompts]
+        return BatchRun(self.engine, self.sampler, prompts, results, range(len(prompts)), max_new_tokens=max_new_tokens,
+                        sampling=SamplingParams(temperature=temperature, seed=seed),
+                        stop=stop_set(self.engine, stop_token_ids, ignore_eos))
 
     @torch.no_grad()
     def greedy_generate(self, input_ids, attention_mask=None, max_new_tokens: int = 16) -> torch.LongTensor:

@@ -78,6 +78,7 @@ class Engine:
                                  device=self.device)
         self._ctx = StepContext(device=self.device, meta=self._meta)
         self.steps_run = 0
+        self.last_meta_bytes = 0        # host-to-device bytes of the latest pass (its packed metadata)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -190,6 +191,7 @@ class Engine:
                     table[i, :len(pages)] = pages
                 tables.append(table)
             self._ctx.fill(slots, tokens, past, rows, tables)
+            self.last_meta_bytes = self._ctx.meta_bytes
             direct = len(passes) == 1 or final_rows == list(range(final_rows[0], final_rows[0] + len(rows))) if rows else True
             if not rows:
                 self.model.forward(self._ctx, self.cache, None)

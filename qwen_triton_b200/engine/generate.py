@@ -69,6 +69,70 @@ def finish_reason(token: int, produced: int, total_length: int, *, stop_ids: fro
     return ""
 
 
+class BatchRun:
+    """One batch of requests that start together: ``start()`` runs every prompt in one step and
+    samples each request's first token; every ``advance()`` then feeds the last tokens back, one per
+    request that is still going, and samples the next.  Host token ids go in and come out at every step.
+    A request that ends gives its slot back at once."""
+
+    def __init__(self, engine, sampler, prompts: Sequence[Sequence[int]], results: list[GenerationResult],
+                 indices: Sequence[int], *, max_new_tokens: int, sampling: SamplingParams, stop: frozenset[int]) -> None:
+        self.engine, self.sampler = engine, sampler
+        self.prompts, self.results = prompts, results
+        self.max_new_tokens, self.sampling, self.stop = max_new_tokens, sampling, stop
+        self.active = list(indices)
+        self.slot_of: dict[int, int] = {}
+        self._entries: list[StepEntry] = []
+
+    @property
+    def done(self) -> bool:
+        return not self.active
+
+    def start(self) -> list[int]:
+        self.slot_of = {index: self.engine.new_sequence() for index in self.active}
+        self._entries = [StepEntry(self.slot_of[i], list(self.prompts[i]), [len(self.prompts[i]) - 1]) for i in self.active]
+        return self._run()
+
+    def advance(self) -> list[int]:
+        return self._run()
+
+    def _run(self) -> list[int]:
+        """One step and one sampled token per active request; returns the tokens in the order of ``active``
+        as it was before the step."""
+        logits = self.engine.step(self._entries)
+        steps = [len(self.results[i].tokens) for i in self.active]
+        tokens = self.sampler.sample(logits, self.sampling, self.active, steps)
+        still: list[int] = []
+        for index, token in zip(self.active, tokens):
+            result = self.results[index]
+            result.tokens.append(int(token))
+            reason = finish_reason(int(token), len(result.tokens), len(self.prompts[index]) + len(result.tokens),
+                                   stop_ids=self.stop, max_new_tokens=self.max_new_tokens,
+                                   max_seq_len=self.engine.max_seq_len)
+            if reason:
+                result.finish_reason = reason
+                self.engine.release(self.slot_of.pop(index))
+            else:
+                still.append(index)
+        self.active = still
+        self._entries = [StepEntry(self.slot_of[i], [self.results[i].tokens[-1]], [0]) for i in still]
+        return tokens
+
+    def close(self) -> None:
+        """Give back whatever the batch still holds (after an error, or when the caller stops early)."""
+        for slot in self.slot_of.values():
+            self.engine.release(slot)
+        self.slot_of = {}
+        self.active = []
+
+
+def stop_set(engine, stop_token_ids: Sequence[int] | None, ignore_eos: bool) -> frozenset[int]:
+    stop_ids = set(stop_token_ids or ())
+    if not ignore_eos:
+        stop_ids |= set(engine.eos_token_ids)
+    return frozenset(stop_ids)
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 16,
              sampling: SamplingParams | None = None, stop_token_ids: Sequence[int] | None = None,
              ignore_eos: bool = False, max_batch_size: int | None = None, sampler=None) -> list[GenerationResult]:
@@ -82,10 +146,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
     if sampler is None:
         from ..sampling import Sampler
         sampler = Sampler(engine.device)
-    stop_ids = set(stop_token_ids or ())
-    if not ignore_eos:
-        stop_ids |= set(engine.eos_token_ids)
-    stop = frozenset(stop_ids)
+    stop = stop_set(engine, stop_token_ids, ignore_eos)
     results = [GenerationResult() for _ in prompts]
     if max_new_tokens <= 0:
         for result in results:
@@ -95,28 +156,12 @@ def generate(engine, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 
                            total_pages=engine.total_pages, num_slots=engine.num_slots,
                            max_seq_len=engine.max_seq_len, max_batch_size=max_batch_size)
     for batch in batches:
-        slot_of = {index: engine.new_sequence() for index in batch}
-        active = list(batch)
+        run = BatchRun(engine, sampler, prompts, results, batch, max_new_tokens=max_new_tokens, sampling=sampling,
+                       stop=stop)
         try:
-            entries = [StepEntry(slot_of[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in active]
-            while active:
-                logits = engine.step(entries)
-                steps = [len(results[i].tokens) for i in active]
-                tokens = sampler.sample(logits, sampling, active, steps)
-                still: list[int] = []
-                for index, token in zip(active, tokens):
-                    result = results[index]
-                    result.tokens.append(int(token))
-                    reason = finish_reason(int(token), len(result.tokens), len(prompts[index]) + len(result.tokens),
-                                           stop_ids=stop, max_new_tokens=max_new_tokens, max_seq_len=engine.max_seq_len)
-                    if reason:
-                        result.finish_reason = reason
-                        engine.release(slot_of.pop(index))
-                    else:
-                        still.append(index)
-                active = still
-                entries = [StepEntry(slot_of[i], [results[i].tokens[-1]], [0]) for i in active]
+            run.start()
+            while not run.done:
+                run.advance()
         finally:
-            for slot in slot_of.values():
-                engine.release(slot)
+            run.close()
     return results

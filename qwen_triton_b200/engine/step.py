@@ -93,6 +93,7 @@ class StepContext:
         host = torch.empty(total, dtype=torch.int32, pin_memory=True)
         np.concatenate(parts, out=host.numpy())
         self._meta[:total].copy_(host, non_blocking=True)
+        self.meta_bytes = 4 * total
 
         offset = 0
         views = []

@@ -61,7 +61,17 @@ def _fn(library: str, name: str):
     return fn
 
 
-def _call(library: str, name: str, *args) -> None:
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernel launches made through this module since the process started."""
+    return _LAUNCHES
+
+
+def _call(library: str, name: str, *args, launches: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += launches
     code = _fn(library, name)(*args)
     if code != 0:
         raise KernelError(f"{name} failed ({code}): {_build.last_error(library)}")
@@ -259,7 +269,7 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _call("attention", "qt_attention_decode", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_len), n_seqs, num_heads, num_kv_heads, head_dim,
           page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits), _ptr(part_acc), _ptr(part_ml),
-          _stream())
+          _stream(), launches=2 if n_splits > 1 else 1)
 
 
 # ----------------------------------------------------------------------------- matrix product

@@ -209,7 +209,8 @@ class ToyConfig:
         ff = PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": r["inter"], "activation": "silu"})
         toy = PartSpec("toy_decay", {"hidden_size": hidden, "decay": r["decay"]})
         attn = PartSpec("attention", {"hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "window": None,
-                                      "qk_norm": False, "position": PartSpec("none")})
+                                      "qk_norm": False, "position": PartSpec("none"),
+                                      "q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"})
         layers = (LayerSpec("blocks.0", block, toy, ff, norm), LayerSpec("blocks.1", block, attn, ff, norm))
         # layer 0 runs twice (two state entries), and the last call reads the keys the attention call before it wrote
         schedule = (LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(1, cache_of=1))
