@@ -1,0 +1,328 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: Y[M, N] = X[M, K] * W[N, K]^T.
+//
+// The weight is the MMA's A operand (128 weight rows fill the instruction's M), the activations
+// are its B operand (16 to 256 tokens on the instruction's N), so one kernel serves a decode step
+// of a few tokens and a prefill of thousands.  Both operands are K-major in global memory, as the
+// checkpoint stores them; TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) stages
+// 64-element K slices in shared memory, one elected thread issues tcgen05.mma with the float
+// accumulator in tensor memory, and four warps read it back with tcgen05.ld and store Y
+// (transposed back to [M, N]) as bfloat16 or float.  Split-K writes float partial sums
+// [splits, M, N] that the consuming kernel adds up in a fixed order.
+//
+// Warp roles (192 threads): warp 0 lane 0 = TMA producer, warp 1 = tensor-memory allocation and
+// (lane 0) MMA issue, warps 2..5 = epilogue, each on the 32 accumulator lanes its warp id allows.
+// Every mbarrier wait is bounded: after about a second it records a code in `status` and the
+// block winds down (waits briefly for copies in flight, frees its tensor memory, returns).
+//
+// Counterpart in luozoupi/Qwen-Triton: kernels/matmul.py:52-97 (tl.dot tiles, W transposed per call).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+using namespace qt;
+
+namespace {
+
+constexpr int BW = 128;        // weight rows per tile = MMA M
+constexpr int BK = 64;         // K elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;     // K per tcgen05.mma for 16-bit inputs
+constexpr int THREADS = 192;
+constexpr uint32_t W_BYTES = BW * BK * 2;
+constexpr unsigned long long WAIT_LIMIT_NS = 1000ull * 1000 * 1000;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the limit ran out or another role already reported a fault.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    unsigned long long start = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 0x3ffu) == 0) {
+            if (*(volatile int*)status != 0) return false;
+            const unsigned long long now = global_timer();
+            if (start == 0) start = now;
+            else if (now - start > WAIT_LIMIT_NS) { atomicCAS(status, 0, code); return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c_inner, int c_outer) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c_inner), "r"(c_outer) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle; groups of 8 rows
+// lie 1024 bytes apart (stride byte offset); the leading byte offset is unused for this layout.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;          // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BX, typename TO>
+__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                          const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
+                                                          int M, int N, int kb_total, int kb_per_split,
+                                                          size_t split_stride, int stages, int* status) {
+    constexpr uint32_t X_BYTES = BX * BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = BX < 32 ? 32 : BX;
+    // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = BX, M = 128
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BX >> 3) << 17) | ((uint32_t)(BW >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                  // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + (base - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);
+    const uint32_t full0 = base + stages * STAGE_BYTES, empty0 = full0 + 8 * stages, tmem_full = empty0 + 8 * stages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int w0 = blockIdx.x * BW, x0 = blockIdx.y * BX, split = blockIdx.z;
+    const int kb_begin = split * kb_per_split;
+    const int nkb = min(kb_total, kb_begin + kb_per_split) - kb_begin;   // >= 1: the host sizes the splits so
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % stages;
+                const uint32_t phase = (uint32_t)(i / stages) & 1u;
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) break;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const uint32_t dst = base + s * STAGE_BYTES;
+                tma_load_2d(dst, &map_w, full0 + 8 * s, (kb_begin + i) * BK, w0);
+                tma_load_2d(dst + W_BYTES, &map_x, full0 + 8 * s, (kb_begin + i) * BK, x0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % stages;
+                const uint32_t phase = (uint32_t)(i / stages) & 1u;
+                if (!mbar_wait(full0 + 8 * s, phase, status, 2)) break;
+                tc_fence_after();
+                const uint64_t a_desc = operand_desc(base + s * STAGE_BYTES);
+                const uint64_t b_desc = operand_desc(base + s * STAGE_BYTES + W_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K inside the swizzled row
+                    umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);               // the stage is free once these MMAs have read it
+            }
+            umma_commit(tmem_full);                        // the accumulator is complete
+        }
+    } else {
+        const int quarter = warp & 3;                      // the accumulator lanes this warp may read
+        const bool ready = mbar_wait(tmem_full, 0, status, 3);
+        tc_fence_after();
+        const int n = w0 + quarter * 32 + lane;
+        TO* dst = out + (size_t)split * split_stride;
+        if (ready) {
+#pragma unroll 1
+            for (int c = 0; c < BX; c += 16) {
+                uint32_t v[16];
+                tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = x0 + c + j;
+                        if (m < M) dst[(size_t)m * N + n] = from_float<TO>(__uint_as_float(v[j]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*(volatile int*)status != 0) {                     // a wait gave up: let copies in flight land before the block leaves
+        const unsigned long long t0 = global_timer();
+        while (global_timer() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ----------------------------------------------------------------------------- host side
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; uint64_t rows, k; uint32_t box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& key) const {
+        return std::hash<const void*>()(key.ptr) ^ (key.rows * 0x9E3779B97F4A7C15ull) ^ (key.k << 20) ^ key.box_rows;
+    }
+};
+
+// Tensor map of a row-major [rows, k] bfloat16 matrix, box = 64 x box_rows, 128-byte swizzle, zero fill outside.
+int tensor_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k, uint32_t box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    const MapKey key{ptr, rows, k, box_rows};
+    auto found = cache.find(key);
+    if (found != cache.end()) { *map = found->second; return QT_OK; }
+    EncodeFn encode = encode_fn();
+    if (!encode) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc: cuTensorMapEncodeTiled failed with %d for [%llu, %llu]", (int)rc, (unsigned long long)rows, (unsigned long long)k);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *map);
+    return QT_OK;
+}
+
+template <int BX, typename TO>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
+           size_t split_stride, int* status, cudaStream_t stream) {
+    constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
+    // small token tiles: two blocks per SM, each streaming weights through half the shared memory
+    const int budget = BX <= 64 ? 110 * 1024 : 220 * 1024;
+    int stages = (budget - 2048) / (int)STAGE_BYTES;
+    if (stages > 8) stages = 8;
+    const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BX, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    const int kb_per_split = (kb_total + splits - 1) / splits;
+    dim3 grid((N + BW - 1) / BW, (M + BX - 1) / BX, splits);
+    gemm_tc_kernel<BX, TO><<<grid, THREADS, smem, stream>>>(map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, status);
+    QT_CHECK_LAUNCH("gemm_tc");
+    return QT_OK;
+}
+
+template <typename TO>
+int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
+                  size_t split_stride, int* status, cudaStream_t stream) {
+    switch (bx) {
+        case 16: return launch<16, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
+        case 32: return launch<32, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
+        case 64: return launch<64, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
+        case 128: return launch<128, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
+        case 256: return launch<256, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
+    }
+    QT_FAIL(QT_ERR_ARG, "gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", bx);
+}
+
+}  // namespace
+
+// out[splits, M, N] (bfloat16 with splits == 1, or float) = x[M, K] * w[N, K]^T, bfloat16 inputs.
+// `token_tile` is the number of tokens per block (16..256); `splits` must leave no split without K
+// blocks: (splits - 1) * ceil(ceil(K/64) / splits) < ceil(K/64).  `status` is a device int that stays
+// 0 unless a wait inside the kernel ran out (1 = producer, 2 = MMA issuer, 3 = epilogue).
+extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int token_tile,
+                          int splits, long long split_stride, int* status, void* stream) {
+    QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
+    QT_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
+    QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+    QT_REQUIRE(status != nullptr, "gemm_tc: a status word is required");
+    const int kb_total = (K + BK - 1) / BK;
+    QT_REQUIRE(splits >= 1 && splits <= kb_total, "gemm_tc: splits=%d for %d K blocks", splits, kb_total);
+    const int per = (kb_total + splits - 1) / splits;
+    QT_REQUIRE((splits - 1) * per < kb_total, "gemm_tc: splits=%d would leave a split without K blocks (%d blocks)", splits, kb_total);
+    QT_REQUIRE(out_dtype == QT_F32 || splits == 1, "gemm_tc: split-K partial sums are float");
+    QT_REQUIRE((M + token_tile - 1) / token_tile <= 65535, "gemm_tc: M=%d is too large for one launch", M);
+    CUtensorMap map_w, map_x;
+    int rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
+    if (rc) return rc;
+    rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)token_tile);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == QT_BF16)
+        return dispatch_tile<__nv_bfloat16>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, status, s);
+    if (out_dtype == QT_F32)
+        return dispatch_tile<float>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, status, s);
+    QT_FAIL(QT_ERR_ARG, "gemm_tc: unknown output type %d", out_dtype);
+}
+
+QT_DEFINE_LAST_ERROR(gemm_tc)

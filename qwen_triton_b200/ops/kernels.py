@@ -38,6 +38,9 @@ _SIGNATURES = {
     "gemm_simt": {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
+    "gemm_tc": {
+        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
+    },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_sample": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -300,6 +303,72 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
           _stream())
 
 
+_STATUS: dict[int, torch.Tensor] = {}
+_TC_TILES = (16, 32, 64, 128, 256)
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _STATUS:
+        _STATUS[index] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _STATUS[index]
+
+
+def check_status(device: torch.device | str = "cuda") -> None:
+    """Raise if a bounded wait inside a tensor-core kernel ran out since the last check (synchronises)."""
+    word = _status_word(torch.device(device))
+    code = int(word[0].item())
+    if code != 0:
+        word.zero_()
+        role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"role {code}")
+        raise KernelError(f"gemm_tc: a wait of {role} ran out; the result of that launch is invalid")
+
+
+def tc_token_tile(rows: int) -> int:
+    for tile in _TC_TILES:
+        if rows <= tile:
+            return tile
+    return _TC_TILES[-1]
+
+
+def tc_normalise_splits(k: int, wanted: int) -> int:
+    """The largest split count <= ``wanted`` that leaves no split without a 64-wide K block."""
+    blocks = -(-k // 64)
+    wanted = max(1, min(wanted, blocks))
+    per = -(-blocks // wanted)
+    return -(-blocks // per)
+
+
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | None = None) -> None:
+    """out = a [M, K] @ w [N, K]^T on the tcgen05 tensor cores; bfloat16 inputs, K a multiple of 8.
+
+    ``out`` is [1, M, N] bfloat16 or float, or [splits, M, N] float for split-K partial sums.
+    """
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    rows, k = a.shape
+    if k != w.shape[1] or (out.rows, out.cols) != (rows, w.shape[0]):
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.tensor.shape)} do not fit")
+    if rows == 0:
+        return
+    if not out.tensor.is_cuda or out.tensor.dtype not in _CODES:
+        raise KernelError("gemm_tc: the output must be a bfloat16 or float32 CUDA tensor")
+    tile = token_tile or tc_token_tile(rows)
+    _call("gemm_tc", "qt_gemm_tc", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k, tile,
+          out.n_splits, out.split_stride, _ptr(_status_word(a.device)), _stream())
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
-    """out = a @ w^T with the kernel that fits the element type and shape (a static choice)."""
-    gemm_simt(a, w, out)
+    """out = a @ w^T with the kernel that fits the element type and shape (a static choice):
+    tensor cores for bfloat16 with 16-byte aligned rows, the FMA kernel for float32 and the rest."""
+    if gemm_tc_supported(a, w):
+        gemm_tc(a, w, out)
+    elif out.n_splits == 1:
+        gemm_simt(a, w, out)
+    else:
+        raise KernelError("gemm: split-K output is only produced by the tensor-core kernel")

@@ -13,6 +13,10 @@ from ..ops.kernels import GemmOut
 from .base import Runtime
 
 
+_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when the product is bound by reading the weight
+_MAX_SPLITS = 16
+
+
 class Linear:
     def __init__(self, key: str, out_features: int, in_features: int, runtime: Runtime, max_rows: int | None = None,
                  float_out: bool = False) -> None:
@@ -25,6 +29,15 @@ class Linear:
         self.max_rows = runtime.max_step_tokens if max_rows is None else max_rows
         self.out_dtype = torch.float32 if float_out else runtime.dtype
         runtime.workspace.declare(f"{key}.out", self.max_rows * out_features, self.out_dtype)
+        # few rows (decode): split K over more blocks so that every SM streams weights; partial sums are float
+        self.split_rows = 64
+        w_tiles = -(-out_features // 128)
+        wanted = -(-_TARGET_BLOCKS // w_tiles)
+        self.splits = 1
+        if runtime.dtype == torch.bfloat16 and in_features % 8 == 0 and wanted > 1:
+            self.splits = kernels.tc_normalise_splits(in_features, min(wanted, max(1, in_features // 256), _MAX_SPLITS))
+        if self.splits > 1:
+            runtime.workspace.declare(f"{key}.partial", self.splits * self.split_rows * out_features, torch.float32)
 
     def set_weight(self, weight: torch.Tensor) -> None:
         if tuple(weight.shape) != (self.out_features, self.in_features):
@@ -33,6 +46,11 @@ class Linear:
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None) -> GemmOut:
         rows = x.shape[0]
+        if out is None and self.splits > 1 and rows <= self.split_rows:
+            partial = self.runtime.workspace.view(f"{self.key}.partial", self.splits, rows, self.out_features)
+            result = GemmOut(partial)
+            kernels.gemm(x, self.weight, result)
+            return result
         if out is None:
             out = self.runtime.workspace.view(f"{self.key}.out", 1, rows, self.out_features)
         else:

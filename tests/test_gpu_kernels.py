@@ -320,3 +320,42 @@ def test_kernels_refuse_what_they_cannot_run():
                                  torch.ones(1, dtype=torch.int32, device=DEV), 1, PAGE, 0, None, 1.0, 1, None, None)
     with pytest.raises(kernels.KernelError, match="do not fit"):
         kernels.gemm_simt(torch.zeros(2, 8, device=DEV), torch.zeros(4, 8, device=DEV), GemmOut(torch.zeros(2, 2, 4, device=DEV)))
+
+
+# ----------------------------------------------------------------------------- tensor-core matrix product
+@pytest.mark.parametrize("m, n, k, splits, out_dtype", [
+    (1, 503, 96, 1, torch.float32), (8, 640, 512, 2, torch.float32), (8, 6144, 4096, 3, torch.float32),
+    (16, 130, 264, 1, torch.bfloat16), (37, 130, 264, 1, torch.bfloat16), (64, 4096, 1536, 4, torch.float32),
+    (100, 200, 160, 1, torch.bfloat16), (300, 1000, 1024, 1, torch.bfloat16), (2048, 512, 4096, 1, torch.bfloat16),
+    (513, 257, 72, 1, torch.float32), (5, 129, 8, 1, torch.float32)])
+def test_gemm_tensor_cores(m, n, k, splits, out_dtype):
+    a, w = rand(m, k, seed=110, dtype=torch.bfloat16), rand(n, k, seed=111, scale=0.1, dtype=torch.bfloat16)
+    expected = a.double() @ w.double().T
+    splits = kernels.tc_normalise_splits(k, splits)
+    out = torch.full((splits, m, n), float("nan"), dtype=out_dtype, device=DEV)
+    kernels.gemm_tc(a, w, GemmOut(out))
+    kernels.check_status(DEV)
+    close(GemmOut(out).value(), expected, out_dtype, f"{m}x{n}x{k} splits={splits}")
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_gemm_tensor_cores_every_token_tile(tile):
+    m, n, k = 70, 384, 448
+    a, w = rand(m, k, seed=112, dtype=torch.bfloat16), rand(n, k, seed=113, scale=0.1, dtype=torch.bfloat16)
+    out = torch.full((1, m, n), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(a, w, GemmOut(out), token_tile=tile)
+    kernels.check_status(DEV)
+    close(out[0], a.double() @ w.double().T, torch.float32, f"token tile {tile}")
+
+
+def test_gemm_dispatch_is_static():
+    a = rand(4, 100, seed=114, dtype=torch.bfloat16)          # K = 100: rows do not start on 16-byte boundaries
+    w = rand(9, 100, seed=115, dtype=torch.bfloat16)
+    assert not kernels.gemm_tc_supported(a, w)
+    out = torch.empty(1, 4, 9, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm(a, w, GemmOut(out))                           # goes to the FMA kernel
+    close(out[0], a.double() @ w.double().T, torch.bfloat16, "unaligned K")
+    with pytest.raises(kernels.KernelError, match="multiple of 8"):
+        kernels.gemm_tc(a, w, GemmOut(out))
+    assert kernels.tc_normalise_splits(320, 4) == 3 and kernels.tc_normalise_splits(4096, 3) == 3
+    assert kernels.tc_normalise_splits(64, 8) == 1
