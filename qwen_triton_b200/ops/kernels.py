@@ -35,6 +35,12 @@ _SIGNATURES = {
         "qt_attention_decode": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
     },
+    "attention_mma": {
+        "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                    _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
+        "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
+    },
     "gemm_simt": {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
@@ -238,16 +244,38 @@ def _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_t
     return tokens, num_heads, head_dim
 
 
+def attention_mma_supported(q: torch.Tensor, page_tokens: int) -> bool:
+    """The tensor-core attention kernels take bfloat16, head sizes in steps of 16 up to 128, pages of 64 tokens."""
+    return q.dtype == torch.bfloat16 and q.shape[2] % 16 == 0 and q.shape[2] <= 128 and page_tokens == 64
+
+
+def _pick_attention(q: torch.Tensor, page_tokens: int, impl: str | None) -> str:
+    if impl is None:
+        return "mma" if attention_mma_supported(q, page_tokens) else "generic"
+    if impl == "mma" and not attention_mma_supported(q, page_tokens):
+        raise KernelError(f"the tensor-core attention kernels do not take {q.dtype}, head_dim={q.shape[2]}, pages of {page_tokens}")
+    if impl not in ("mma", "generic"):
+        raise KernelError(f"unknown attention implementation {impl!r}")
+    return impl
+
+
 def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                       block_table: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, max_q_len: int,
-                      num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float) -> None:
-    """Causal attention of packed sequences over the cache (which already holds this step's keys)."""
+                      num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
+                      impl: str | None = None) -> None:
+    """Causal attention of packed sequences over the cache (which already holds this step's keys).
+    ``impl`` forces the generic or the tensor-core kernel; by default the shape decides."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
     _need(seq_past, "seq_past", torch.int32)
     if block_table.shape[0] < n_seqs:
         raise KernelError("attention_prefill: block table has fewer rows than sequences")
+    if _pick_attention(q, page_tokens, impl) == "mma":
+        _call("attention_mma", "qt_attention_prefill_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
+              _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
+              num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
+        return
     _call("attention", "qt_attention_prefill", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
           num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
@@ -256,7 +284,7 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                      block_table: torch.Tensor, seq_len: torch.Tensor, num_kv_heads: int, page_tokens: int,
                      ring_tokens: int, window: int | None, scale: float, n_splits: int,
-                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None) -> None:
+                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None) -> None:
     """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
 
     With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
@@ -269,6 +297,12 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _need(part_ml, "part_ml", torch.float32)
         if part_acc.numel() < n_seqs * num_heads * n_splits * head_dim or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
             raise KernelError("attention_decode: scratch is too small for this batch and split count")
+    if _pick_attention(q, page_tokens, impl) == "mma":
+        _call("attention_mma", "qt_attention_decode_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
+              _ptr(block_table), block_table.shape[1], _ptr(seq_len), n_seqs, num_heads, num_kv_heads, head_dim,
+              page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits), _ptr(part_acc), _ptr(part_ml),
+              _stream(), launches=2 if n_splits > 1 else 1)
+        return
     _call("attention", "qt_attention_decode", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
           _ptr(block_table), block_table.shape[1], _ptr(seq_len), n_seqs, num_heads, num_kv_heads, head_dim,
           page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits), _ptr(part_acc), _ptr(part_ml),

@@ -95,7 +95,10 @@ class Attention:
     # ------------------------------------------------------------------ run
     def _splits(self, ctx) -> int:
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
-        heads_per_block = 8 if self.nq // self.nkv > 4 else max(1, self.nq // self.nkv)
+        if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128:
+            heads_per_block = 16                                 # the tensor-core kernel takes a group of up to 16 heads
+        else:
+            heads_per_block = 8 if self.nq // self.nkv > 4 else max(1, self.nq // self.nkv)
         blocks = ctx.n_seqs * self.nkv * math.ceil((self.nq // self.nkv) / heads_per_block)
         wanted = max(1, math.ceil(_DECODE_TARGET_BLOCKS / blocks))
         by_length = max(1, span // _MIN_KEYS_PER_SPLIT)

@@ -179,10 +179,15 @@ def test_gemm_float32_is_true_float32():
 
 
 # ----------------------------------------------------------------------------- attention
+def impls_for(dtype, d):
+    return ["generic", "mma"] if dtype == torch.bfloat16 and d % 16 == 0 and d <= 128 else ["generic"]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq, nkv, d, window, ring", [(6, 2, 80, None, 0), (4, 4, 16, 40, 128), (8, 1, 128, None, 0), (2, 1, 256, 100, 0)])
+@pytest.mark.parametrize("nq, nkv, d, window, ring", [(6, 2, 80, None, 0), (4, 4, 16, 40, 128), (8, 1, 128, None, 0), (2, 1, 256, 100, 0),
+                                                      (3, 1, 48, 70, 192), (4, 2, 112, None, 0)])
 def test_attention_prefill(dtype, nq, nkv, d, window, ring):
-    q_lens, past = [50, 1, 33], [100, 0, 7]
+    q_lens, past = [150, 1, 33, 64], [100, 0, 7, 64]
     if ring:
         q_lens = [min(n, ring - window + 1) for n in q_lens]       # a step never outruns the ring
     totals = [p + n for p, n in zip(past, q_lens)]
@@ -194,18 +199,20 @@ def test_attention_prefill(dtype, nq, nkv, d, window, ring):
     seq_start = torch.tensor([0, *torch.tensor(q_lens).cumsum(0).tolist()], dtype=torch.int32, device=DEV)
     seq_past = torch.tensor(past, dtype=torch.int32, device=DEV)
     scale = d ** -0.5
-    kernels.attention_prefill(q, k_cache, v_cache, out, table, seq_start, seq_past, max(q_lens), nkv, PAGE, ring, window, scale)
-    start = 0
-    for b, n in enumerate(q_lens):
-        ref = attention_reference(q[start:start + n].float().cpu(), k[b], v[b], torch.arange(past[b], past[b] + n), scale, window)
-        close(out[start:start + n], ref, dtype, f"sequence {b}")
-        start += n
+    for impl in impls_for(dtype, d):
+        out.fill_(float("nan"))
+        kernels.attention_prefill(q, k_cache, v_cache, out, table, seq_start, seq_past, max(q_lens), nkv, PAGE, ring, window, scale, impl=impl)
+        start = 0
+        for b, n in enumerate(q_lens):
+            ref = attention_reference(q[start:start + n].float().cpu(), k[b], v[b], torch.arange(past[b], past[b] + n), scale, window)
+            close(out[start:start + n], ref, dtype, f"{impl}, sequence {b}")
+            start += n
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq, nkv, d, window, ring, splits", [
     (6, 2, 80, None, 0, 1), (6, 2, 80, None, 0, 5), (4, 4, 16, 40, 128, 2), (16, 1, 128, None, 0, 3),
-    (32, 8, 128, None, 0, 4), (5, 5, 112, 300, 0, 7), (10, 2, 48, None, 0, 64)])
+    (32, 8, 128, None, 0, 4), (5, 5, 112, 300, 0, 7), (10, 2, 48, None, 0, 64), (40, 2, 64, None, 0, 2), (8, 2, 96, 130, 256, 3)])
 def test_attention_decode(dtype, nq, nkv, d, window, ring, splits):
     lengths = [700, 1, 65, 129]
     k = [rand(t, nkv, d, seed=50 + i, dtype=dtype).float().cpu() for i, t in enumerate(lengths)]
@@ -217,10 +224,12 @@ def test_attention_decode(dtype, nq, nkv, d, window, ring, splits):
     part_acc = torch.full((len(lengths) * nq * splits * d,), float("nan"), device=DEV)
     part_ml = torch.full((len(lengths) * nq * splits * 2,), float("nan"), device=DEV)
     scale = d ** -0.5
-    kernels.attention_decode(q, k_cache, v_cache, out, table, seq_len, nkv, PAGE, ring, window, scale, splits, part_acc, part_ml)
-    for b, n in enumerate(lengths):
-        ref = attention_reference(q[b:b + 1].float().cpu(), k[b], v[b], torch.tensor([n - 1]), scale, window)
-        close(out[b:b + 1], ref, dtype, f"sequence {b}")
+    for impl in impls_for(dtype, d):
+        out.fill_(float("nan"))
+        kernels.attention_decode(q, k_cache, v_cache, out, table, seq_len, nkv, PAGE, ring, window, scale, splits, part_acc, part_ml, impl=impl)
+        for b, n in enumerate(lengths):
+            ref = attention_reference(q[b:b + 1].float().cpu(), k[b], v[b], torch.tensor([n - 1]), scale, window)
+            close(out[b:b + 1], ref, dtype, f"{impl}, sequence {b}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -239,14 +248,16 @@ def test_one_far_key_among_hundreds_wins(dtype, mode):
     k_cache, v_cache, table = paged([k], [v], [n], dtype, seed=3)
     q = query.to(dtype).to(DEV)
     out = torch.empty_like(q)
-    if mode == "decode":
-        kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
-                                 None, 1.0, 4, torch.empty(nq * 4 * d, device=DEV), torch.empty(nq * 4 * 2, device=DEV))
-    else:
-        kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
-                                  torch.tensor([n - 1], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, None, 1.0)
     expected = v[3].repeat_interleave(2, dim=0)[None]
-    close(out, expected, dtype, "far key")
+    for impl in impls_for(dtype, d):
+        out.fill_(float("nan"))
+        if mode == "decode":
+            kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
+                                     None, 1.0, 4, torch.empty(nq * 4 * d, device=DEV), torch.empty(nq * 4 * 2, device=DEV), impl=impl)
+        else:
+            kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                      torch.tensor([n - 1], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, None, 1.0, impl=impl)
+        close(out, expected, dtype, f"far key, {impl}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -268,13 +279,15 @@ def test_window_edge(dtype, mode):
     k_cache, v_cache, table = paged([k], [v], [n], dtype, seed=4)
     q = query.to(dtype).to(DEV)
     out = torch.empty_like(q)
-    if mode == "decode":
-        kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
-                                 window, 1.0, 3, torch.empty(nq * 3 * d, device=DEV), torch.empty(nq * 3 * 2, device=DEV))
-    else:
-        kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
-                                  torch.tensor([last], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, window, 1.0)
-    close(out, v[inside].expand(1, nq, d), dtype, "window edge")
+    for impl in impls_for(dtype, d):
+        out.fill_(float("nan"))
+        if mode == "decode":
+            kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
+                                     window, 1.0, 3, torch.empty(nq * 3 * d, device=DEV), torch.empty(nq * 3 * 2, device=DEV), impl=impl)
+        else:
+            kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                      torch.tensor([last], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, window, 1.0, impl=impl)
+        close(out, v[inside].expand(1, nq, d), dtype, f"window edge, {impl}")
 
 
 # ----------------------------------------------------------------------------- sampling
