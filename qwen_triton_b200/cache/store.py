@@ -85,9 +85,11 @@ class SequenceCache:
         geometry = [GroupGeometry(total_pages, g.ring_tokens // page_tokens) for g in self.groups]
         self.book = CacheBook(self.num_slots, page_tokens, geometry, max_seq_len)
         self.has_window = any(g.ring_tokens for g in self.groups)
+        # one page beyond the book's pool: padded rows of a fixed-shape decode step read and write only this page
+        self.dummy_page = total_pages
         if allocate:
             for group in self.groups:
-                shape = (len(group.owners), total_pages, group.request.kv_heads, page_tokens, group.request.head_dim)
+                shape = (len(group.owners), total_pages + 1, group.request.kv_heads, page_tokens, group.request.head_dim)
                 group.k = torch.zeros(shape, dtype=dtype, device=device)
                 group.v = torch.zeros(shape, dtype=dtype, device=device)
             for position, request in self._state_requests.items():

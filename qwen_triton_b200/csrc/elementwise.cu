@@ -66,14 +66,95 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     }
 }
 
+// Vector form for widths that are multiples of 4: each thread owns up to NORM_CACHE chunks of four
+// consecutive elements, sums the split-K partials with independent 16-byte loads and keeps the new
+// stream values in registers between the two passes.
+constexpr int NORM_CACHE = 4;
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
+                                       size_t split_stride, const float* __restrict__ weight, float eps,
+                                       TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * hidden;
+    const int chunks = hidden >> 2;
+    float4 x[NORM_CACHE];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            float4 v = load4(res + 4 * c);
+            if (delta) {
+                const TD* dp = delta + (size_t)src * hidden + 4 * c;
+#pragma unroll 4
+                for (int s = 0; s < n_splits; ++s) {
+                    const float4 dv = load4(dp + (size_t)s * split_stride);
+                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                }
+            }
+            if (!rows) store4(res + 4 * c, v);
+            x[i] = v;
+            sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    TO* o = out + (size_t)r * hidden;
+#pragma unroll
+    for (int i = 0; i < NORM_CACHE; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            const float4 w = load4(weight + 4 * c);
+            store4(o + 4 * c, make_float4(x[i].x * inv * w.x, x[i].y * inv * w.y, x[i].z * inv * w.z, x[i].w * inv * w.w));
+        }
+    }
+}
+
 extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
                               const float* weight, float eps, void* out, int out_dtype, const int* rows, int n_rows,
                               int hidden, void* stream) {
     QT_REQUIRE(n_rows >= 0 && hidden > 0 && n_splits >= 1, "add_rmsnorm: bad sizes rows=%d H=%d splits=%d", n_rows, hidden, n_splits);
     QT_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
     if (n_rows == 0) return QT_OK;
-    const int threads = hidden >= 2048 ? 512 : 256;
     cudaStream_t s = (cudaStream_t)stream;
+    // the vector kernel needs 16-byte aligned rows everywhere and at most NORM_CACHE chunks per thread
+    const bool aligned = hidden % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                         ((uintptr_t)weight % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && split_stride % 4 == 0));
+    if (aligned && hidden <= 4 * NORM_CACHE * 1024) {
+        int vthreads = ((hidden / 4 + 31) / 32) * 32;
+        if (vthreads > 1024) vthreads = 1024;
+        if (vthreads < 64) vthreads = 64;
+#define QT_LAUNCH_NORM_VEC(TD, TO)                                                                                      \
+    add_rmsnorm_vec_kernel<TD, TO><<<n_rows, vthreads, 0, s>>>(residual, (const TD*)delta, n_splits, (size_t)split_stride, \
+                                                               weight, eps, (TO*)out, rows, hidden)
+        if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM_VEC(float, float);
+        else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM_VEC(float, __nv_bfloat16);
+        else if (delta_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_NORM_VEC(__nv_bfloat16, __nv_bfloat16);
+        else if (delta_dtype == QT_BF16 && out_dtype == QT_F32) QT_LAUNCH_NORM_VEC(__nv_bfloat16, float);
+        else QT_FAIL(QT_ERR_ARG, "add_rmsnorm: unknown element types %d/%d", delta_dtype, out_dtype);
+#undef QT_LAUNCH_NORM_VEC
+        QT_CHECK_LAUNCH("add_rmsnorm");
+        return QT_OK;
+    }
+    const int threads = hidden >= 2048 ? 512 : 256;
 #define QT_LAUNCH_NORM(TD, TO)                                                                                   \
     add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, s>>>(residual, (const TD*)delta, n_splits, (size_t)split_stride, \
                                                           weight, eps, (TO*)out, rows, hidden)
@@ -106,7 +187,7 @@ struct QkvParams {
     int n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj;
 };
 
-template <typename TI, typename TO>
+template <typename TI, typename TO, bool VEC>
 __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,19 +201,31 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     float* vec = smem + warp * p.d;
     const size_t in_base = (size_t)t * heads_total * p.d + (size_t)head * p.d;
     const TI* in = (const TI*)p.qkv;
-
-    float sq = 0.f;
-    for (int i = lane; i < p.d; i += 32) {
-        const float x = load_sum(in, in_base + i, p.n_splits, p.split_stride);
-        vec[i] = x;
-        sq += x * x;
-    }
     const float* w = is_q ? p.q_weight : (is_k ? p.k_weight : nullptr);
-    if (w) {
-        sq = warp_sum(sq);
-        const float inv = rsqrtf(sq / (float)p.d + p.eps);
-        for (int i = lane; i < p.d; i += 32) vec[i] = vec[i] * inv * w[i];
+
+    // 1. the head's vector in float (split-K partials added up), its sum of squares
+    float sq = 0.f;
+    if (VEC) {
+        for (int c = lane; c < (p.d >> 2); c += 32) {
+            float4 v = load4(in + in_base + 4 * c);
+#pragma unroll 4
+            for (int s = 1; s < p.n_splits; ++s) {
+                const float4 dv = load4(in + in_base + 4 * c + (size_t)s * p.split_stride);
+                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            }
+            *reinterpret_cast<float4*>(vec + 4 * c) = v;
+            sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = lane; i < p.d; i += 32) {
+            const float x = load_sum(in, in_base + i, p.n_splits, p.split_stride);
+            vec[i] = x;
+            sq += x * x;
+        }
     }
+    // 2. RMSNorm over the head (q and k heads with a weight)
+    float inv = 1.f;
+    if (w) inv = rsqrtf(warp_sum(sq) / (float)p.d + p.eps);
     __syncwarp();
 
     TO* dst;
@@ -144,16 +237,24 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
         const int* table = p.block_table + (size_t)p.token_seq[t] * p.max_blocks;
         dst = (TO*)(is_k ? p.k_cache : p.v_cache) + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, kvh, p.d);
     }
+    // 3. rotate-half over the first rotary_dim dims with the normed values, store
     const int half = p.rotary_dim >> 1;
     const bool rotate = (is_q || is_k) && half > 0;
     const float* cs = p.cos_sin + (size_t)(pos < p.max_pos ? pos : p.max_pos - 1) * p.rotary_dim;
-    for (int i = lane; i < p.d; i += 32) {
-        float y = vec[i];
+    auto value = [&](int i) { return w ? vec[i] * inv * w[i] : vec[i]; };
+    auto rotated = [&](int i) {
+        float y = value(i);
         if (rotate && i < p.rotary_dim) {
-            if (i < half) y = vec[i] * cs[i] - vec[i + half] * cs[half + i];
-            else y = vec[i] * cs[i - half] + vec[i - half] * cs[i];
+            if (i < half) y = y * cs[i] - value(i + half) * cs[half + i];
+            else y = y * cs[i - half] + value(i - half) * cs[i];
         }
-        dst[i] = from_float<TO>(y);
+        return y;
+    };
+    if (VEC) {
+        for (int c = lane; c < (p.d >> 2); c += 32)
+            store4(dst + 4 * c, make_float4(rotated(4 * c), rotated(4 * c + 1), rotated(4 * c + 2), rotated(4 * c + 3)));
+    } else {
+        for (int i = lane; i < p.d; i += 32) dst[i] = from_float<TO>(rotated(i));
     }
 }
 
@@ -177,10 +278,19 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * d * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == QT_F32 && out_dtype == QT_F32) qk_norm_rope_write_kernel<float, float><<<grid, warps * 32, smem, s>>>(p);
-    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) qk_norm_rope_write_kernel<float, __nv_bfloat16><<<grid, warps * 32, smem, s>>>(p);
-    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) qk_norm_rope_write_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, warps * 32, smem, s>>>(p);
+    // 16-byte loads and stores need head_dim % 8 == 0 (bfloat16 rows of the cache and of q) and aligned bases
+    const bool vec = d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+                     (!write_kv || (((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0)));
+#define QT_LAUNCH_QKV(TI, TO)                                                                    \
+    do {                                                                                         \
+        if (vec) qk_norm_rope_write_kernel<TI, TO, true><<<grid, warps * 32, smem, s>>>(p);      \
+        else qk_norm_rope_write_kernel<TI, TO, false><<<grid, warps * 32, smem, s>>>(p);         \
+    } while (0)
+    if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_QKV(float, float);
+    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_QKV(float, __nv_bfloat16);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_QKV(__nv_bfloat16, __nv_bfloat16);
     else QT_FAIL(QT_ERR_ARG, "qk_norm_rope_write: unsupported element types %d -> %d", in_dtype, out_dtype);
+#undef QT_LAUNCH_QKV
     QT_CHECK_LAUNCH("qk_norm_rope_write");
     return QT_OK;
 }

@@ -261,12 +261,17 @@ int tensor_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k, uin
 
 template <int BX, typename TO>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-           size_t split_stride, int* status, cudaStream_t stream) {
+           size_t split_stride, int stages, int* status, cudaStream_t stream) {
     constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
     // small token tiles: two blocks per SM, each streaming weights through half the shared memory
     const int budget = BX <= 64 ? 110 * 1024 : 220 * 1024;
-    int stages = (budget - 2048) / (int)STAGE_BYTES;
-    if (stages > 8) stages = 8;
+    const int most = (224 * 1024) / (int)STAGE_BYTES;
+    if (stages <= 0) {
+        stages = (budget - 2048) / (int)STAGE_BYTES;
+        if (stages > 8) stages = 8;
+    }
+    if (stages > most) stages = most;
+    if (stages < 2) stages = 2;
     const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 16;
     static bool configured = false;
     if (!configured) {
@@ -283,13 +288,13 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, i
 
 template <typename TO>
 int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-                  size_t split_stride, int* status, cudaStream_t stream) {
+                  size_t split_stride, int stages, int* status, cudaStream_t stream) {
     switch (bx) {
-        case 16: return launch<16, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
-        case 32: return launch<32, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
-        case 64: return launch<64, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
-        case 128: return launch<128, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
-        case 256: return launch<256, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, status, stream);
+        case 16: return launch<16, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
+        case 32: return launch<32, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
+        case 64: return launch<64, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
+        case 128: return launch<128, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
+        case 256: return launch<256, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
     }
     QT_FAIL(QT_ERR_ARG, "gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", bx);
 }
@@ -300,8 +305,9 @@ int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO
 // `token_tile` is the number of tokens per block (16..256); `splits` must leave no split without K
 // blocks: (splits - 1) * ceil(ceil(K/64) / splits) < ceil(K/64).  `status` is a device int that stays
 // 0 unless a wait inside the kernel ran out (1 = producer, 2 = MMA issuer, 3 = epilogue).
+// `stages` > 0 overrides the depth of the shared-memory ring (a tuning knob; 0 picks the default).
 extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int token_tile,
-                          int splits, long long split_stride, int* status, void* stream) {
+                          int splits, long long split_stride, int stages, int* status, void* stream) {
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
@@ -319,9 +325,9 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == QT_BF16)
-        return dispatch_tile<__nv_bfloat16>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, status, s);
+        return dispatch_tile<__nv_bfloat16>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, stages, status, s);
     if (out_dtype == QT_F32)
-        return dispatch_tile<float>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, status, s);
+        return dispatch_tile<float>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, stages, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc: unknown output type %d", out_dtype);
 }
 

@@ -21,6 +21,7 @@ import torch
 from ..cache import SequenceCache
 from ..config import load_config
 from ..config.spec import ModelSpec
+from ..ops import kernels
 from ..parts.base import Runtime, Workspace
 from ..weights import open_checkpoint, random_source
 from .model import CausalLM, expected_tensors
@@ -52,7 +53,8 @@ def require_gpu(device: torch.device) -> None:
 class Engine:
     def __init__(self, spec: ModelSpec, source, *, dtype=torch.bfloat16, max_tokens: int = 8192,
                  max_seq_len: int | None = None, max_step_tokens: int = 4096, device: str | torch.device = "cuda:0",
-                 page_tokens: int = 64, chunk_tokens: int = 256, options: dict | None = None) -> None:
+                 page_tokens: int = 64, chunk_tokens: int = 256, options: dict | None = None,
+                 cuda_graphs: bool = True, max_graph_batch: int = 256) -> None:
         self.device = torch.device(device)
         require_gpu(self.device)
         torch.cuda.set_device(self.device)
@@ -73,11 +75,17 @@ class Engine:
                                    device=self.device, page_tokens=page_tokens, chunk_tokens=chunk_tokens)
         workspace.allocate()
         widths = [self.cache.max_blocks(g) for g in range(len(self.cache.groups))]
-        max_seqs = min(self.max_step_tokens, self.cache.num_slots)
+        max_seqs = self.max_step_tokens            # a pass never has more sequences than tokens (padded decode rows included)
         self._meta = torch.zeros(StepContext.meta_size(self.max_step_tokens, max_seqs, widths), dtype=torch.int32,
                                  device=self.device)
         self._ctx = StepContext(device=self.device, meta=self._meta)
         self.steps_run = 0
+        # one-token steps are captured once per shape and replayed: the launches of a step cost more on the
+        # host than they run on the device.  Mixers that touch the host in forward() opt out (graph_safe).
+        self._graphs_enabled = bool(cuda_graphs) and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)
+        self._graphs: dict[tuple, object] = {}
+        self.max_graph_batch = max_graph_batch
+        self.graph_replays = 0
         self.last_meta_bytes = 0        # host-to-device bytes of the latest pass (its packed metadata)
 
     # ------------------------------------------------------------------ construction
@@ -164,6 +172,11 @@ class Engine:
         if not book.can_hold(targets):
             raise RuntimeError("the cache cannot hold this step: too many tokens are live (raise max_tokens)")
 
+        if (self._graphs_enabled and len(entries) <= min(self.max_graph_batch, self.max_step_tokens // 2)
+                and all(len(e.tokens) == 1 and e.want == [0] for e in entries)):
+            self.steps_run += 1
+            return self._decode_step(entries)
+
         n_want = sum(len(e.want) for e in entries)
         logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         want_base = np.cumsum([0] + [len(e.want) for e in entries])
@@ -203,6 +216,55 @@ class Engine:
                 logits.index_copy_(0, torch.tensor(final_rows, device=self.device), part)
         self.steps_run += 1
         return logits
+
+    def _decode_step(self, entries: list[StepEntry]) -> torch.Tensor:
+        """One token per sequence, every logit wanted: run at a fixed shape (batch padded to a power of
+        two, page tables to a multiple of 16 pages) so that a captured CUDA graph can be replayed.  Padded
+        rows read and write only the cache's spare page, and their logits are dropped."""
+        book, cache = self.cache.book, self.cache
+        count = len(entries)
+        padded = 1
+        while padded < count:
+            padded *= 2
+        slots = [e.slot for e in entries]
+        past = [book.length(s) for s in slots]
+        for slot, before in zip(slots, past):
+            book.extend(slot, before + 1)
+        widths, tables = [], []
+        for group in range(len(cache.groups)):
+            need = max(len(book.pages(s, group)) for s in slots)
+            width = min(cache.max_blocks(group), -(-need // 16) * 16)
+            table = np.full((padded, width), cache.dummy_page, dtype=np.int32)
+            for i, s in enumerate(slots):
+                pages = book.pages(s, group)
+                table[i, :len(pages)] = pages
+            widths.append(width)
+            tables.append(table)
+        context = -(-(max(past) + 1) // 1024) * 1024
+        pad = padded - count
+        self._ctx.fill(slots + [0] * pad, [e.tokens for e in entries] + [[0]] * pad, past + [0] * pad,
+                       list(range(padded)), tables, max_context=context)
+        self.last_meta_bytes = self._ctx.meta_bytes
+        key = (padded, tuple(widths), context)
+        state = self._graphs.get(key)
+        if state is None:                      # first time at this shape: run the launches themselves
+            logits = torch.empty((padded, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+            self.model.forward(self._ctx, cache, logits)
+            self._graphs[key] = "warm"
+            return logits[:count]
+        if state == "warm":                    # second time: capture (nothing runs during capture), then replay
+            logits = torch.empty((padded, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = kernels.launch_count()
+            with torch.cuda.graph(graph):
+                self.model.forward(self._ctx, cache, logits)
+            state = (graph, logits, kernels.launch_count() - before)
+            self._graphs[key] = state
+        graph, logits, launches = state
+        graph.replay()
+        kernels.count_launches(launches)
+        self.graph_replays += 1
+        return logits[:count].clone()
 
     def memory_report(self) -> dict[str, int]:
         return {"weights": self.model.weight_bytes(), "cache": self.cache.bytes(),

@@ -71,8 +71,10 @@ class StepContext:
         return 4 * max_tokens + 5 * max_seqs + 8 + max_seqs * sum(table_widths) + 64
 
     def fill(self, slots: list[int], tokens: list[list[int]], past: list[int], want_rows: list[int],
-             tables: list[np.ndarray]) -> None:
-        """Pack the pass on the host and copy it to the device in one transfer."""
+             tables: list[np.ndarray], max_context: int | None = None) -> None:
+        """Pack the pass on the host and copy it to the device in one transfer.  For given counts of
+        tokens, sequences, wanted rows and table widths every array lands at the same address, which is
+        what lets a captured decode step be replayed on new contents."""
         n_seqs = len(slots)
         q_lens = [len(t) for t in tokens]
         n_tokens = sum(q_lens)
@@ -105,5 +107,5 @@ class StepContext:
         self._tables = {g: views[8 + g].view(n_seqs, tables[g].shape[1]) for g in range(len(tables))}
         self.n_tokens, self.n_seqs, self.n_want = n_tokens, n_seqs, len(want_rows)
         self.max_q_len = max(q_lens) if q_lens else 0
-        self.max_context = int(seq_len.max()) if n_seqs else 0
+        self.max_context = max_context if max_context is not None else (int(seq_len.max()) if n_seqs else 0)
         self.is_decode = bool(q_lens) and all(q == 1 for q in q_lens)

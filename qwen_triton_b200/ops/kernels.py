@@ -45,7 +45,7 @@ _SIGNATURES = {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "gemm_tc": {
-        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
+        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
     },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -76,6 +76,12 @@ _LAUNCHES = 0
 def launch_count() -> int:
     """Kernel launches made through this module since the process started."""
     return _LAUNCHES
+
+
+def count_launches(n: int) -> None:
+    """Account for kernels launched outside this module's calls (a replayed CUDA graph of them)."""
+    global _LAUNCHES
+    _LAUNCHES += n
 
 
 def _call(library: str, name: str, *args, launches: int = 1) -> None:
@@ -378,7 +384,7 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | None = None) -> None:
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | None = None, stages: int = 0) -> None:
     """out = a [M, K] @ w [N, K]^T on the tcgen05 tensor cores; bfloat16 inputs, K a multiple of 8.
 
     ``out`` is [1, M, N] bfloat16 or float, or [splits, M, N] float for split-K partial sums.
@@ -394,7 +400,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
         raise KernelError("gemm_tc: the output must be a bfloat16 or float32 CUDA tensor")
     tile = token_tile or tc_token_tile(rows)
     _call("gemm_tc", "qt_gemm_tc", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k, tile,
-          out.n_splits, out.split_stride, _ptr(_status_word(a.device)), _stream())
+          out.n_splits, out.split_stride, int(stages), _ptr(_status_word(a.device)), _stream())
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:

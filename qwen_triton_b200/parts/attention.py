@@ -24,6 +24,8 @@ _MIN_KEYS_PER_SPLIT = 128
 
 @register_mixer("attention")
 class Attention:
+    graph_safe = True      # forward() only launches kernels: a decode step with this mixer can be captured in a CUDA graph
+
     def __init__(self, params, prefix: str, runtime: Runtime) -> None:
         self.prefix = prefix
         self.runtime = runtime

@@ -17,6 +17,24 @@ _TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when the product is bound
 _MAX_SPLITS = 16
 
 
+def pick_splits(out_features: int, in_features: int) -> int:
+    """Split count for a product with few rows: the one whose blocks (128-row weight tiles x splits) fill
+    whole waves of the SMs best, each split keeping at least four 64-wide K blocks; fewer splits win ties."""
+    tiles = -(-out_features // 128)
+    blocks_k = -(-in_features // 64)
+    best, best_fill = 1, 0.0
+    for splits in range(1, _MAX_SPLITS + 1):
+        if splits > 1 and blocks_k // splits < 4:
+            break
+        if kernels.tc_normalise_splits(in_features, splits) != splits:
+            continue
+        blocks = tiles * splits
+        fill = blocks / (-(-blocks // _TARGET_BLOCKS) * _TARGET_BLOCKS)
+        if fill > best_fill + 0.03:
+            best, best_fill = splits, fill
+    return best
+
+
 class Linear:
     def __init__(self, key: str, out_features: int, in_features: int, runtime: Runtime, max_rows: int | None = None,
                  float_out: bool = False) -> None:
@@ -31,11 +49,9 @@ class Linear:
         runtime.workspace.declare(f"{key}.out", self.max_rows * out_features, self.out_dtype)
         # few rows (decode): split K over more blocks so that every SM streams weights; partial sums are float
         self.split_rows = 64
-        w_tiles = -(-out_features // 128)
-        wanted = -(-_TARGET_BLOCKS // w_tiles)
         self.splits = 1
-        if runtime.dtype == torch.bfloat16 and in_features % 8 == 0 and wanted > 1:
-            self.splits = kernels.tc_normalise_splits(in_features, min(wanted, max(1, in_features // 256), _MAX_SPLITS))
+        if runtime.dtype == torch.bfloat16 and in_features % 8 == 0:
+            self.splits = pick_splits(out_features, in_features)
         if self.splits > 1:
             runtime.workspace.declare(f"{key}.partial", self.splits * self.split_rows * out_features, torch.float32)
 

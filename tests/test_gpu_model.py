@@ -93,6 +93,30 @@ def test_long_decoding(case):
         rows.append(engine.step([StepEntry(slot, [token], [0])]))
     engine.release(slot)
     assert_close(torch.cat(rows), plain_logits(preset, dtype, tokens), dtype, "long decoding")
+    assert engine.graph_replays > 200           # the one-token steps ran as replays of a captured step
+
+
+def test_captured_steps_equal_plain_launches(case):
+    """The same decode steps with and without CUDA graphs, at batch sizes that need padding rows."""
+    preset, dtype, _ = case
+    requests = [random_tokens(preset, n, 600 + n) for n in (70, 3, 41)]
+    outputs = []
+    for graphs in (True, False):
+        engine = make_engine(preset, dtype, max_tokens=1024, chunk_tokens=16, cuda_graphs=graphs)
+        slots = [engine.new_sequence() for _ in requests]
+        engine.step([StepEntry(s, r[:2], []) for s, r in zip(slots, requests)])
+        rows = []
+        for at in range(2, 70):
+            live = [(s, r) for s, r in zip(slots, requests) if at < len(r)]
+            rows.append(engine.step([StepEntry(s, [r[at]], [0]) for s, r in live]))
+        outputs.append(torch.cat(rows))
+        assert (engine.graph_replays > 0) == graphs
+        for s in slots:
+            engine.release(s)
+    # the same values up to rounding: the captured step runs at a padded shape with its own split counts
+    assert_close(outputs[0], outputs[1], dtype, "captured against plain launches")
+    expected = torch.cat([torch.stack([plain_logits(preset, dtype, r)[at] for r in requests if at < len(r)]) for at in range(2, 70)])
+    assert_close(outputs[0], expected, dtype, "captured steps against the plain implementation")
 
 
 def test_first_tokens_of_a_sequence(case):
