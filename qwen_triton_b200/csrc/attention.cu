@@ -34,6 +34,8 @@ constexpr int PF_ROWS = PF_BQ / PF_WARPS;
 
 template <typename T, int DMAX>
 __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(const AttnParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int d = p.d;
     const int kstride = d + 1;
@@ -141,7 +143,7 @@ static int launch_prefill(const AttnParams& p, int max_q_len, cudaStream_t strea
         configured = true;
     }
     dim3 grid((max_q_len + PF_BQ - 1) / PF_BQ, p.nq, p.n_seqs);
-    attention_prefill_kernel<T, DMAX><<<grid, PF_WARPS * 32, smem, stream>>>(p);
+    launch_kernel(attention_prefill_kernel<T, DMAX>, dim3(grid), dim3(PF_WARPS * 32), smem, stream, p);
     QT_CHECK_LAUNCH("attention_prefill");
     return QT_OK;
 }
@@ -189,6 +191,8 @@ struct DecodeParams {
 
 template <typename T, int DMAX, int DEC_HEADS>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const DecodeParams dp) {
+    pdl_launch_dependents();
+    pdl_wait();
     const AttnParams& p = dp.a;
     extern __shared__ float smem[];
     const int d = p.d;
@@ -310,6 +314,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int n_splits, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t item = blockIdx.x;   // seq * nq + head
     float m_all = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(item * n_splits + s) * 2]);
@@ -340,10 +346,10 @@ static int launch_decode_heads(const DecodeParams& dp, cudaStream_t stream) {
     }
     const int group = p.nq / p.nkv;
     dim3 grid(dp.n_splits, p.nkv * ((group + DEC_HEADS - 1) / DEC_HEADS), p.n_seqs);
-    attention_decode_kernel<T, DMAX, DEC_HEADS><<<grid, DEC_WARPS * 32, smem, stream>>>(dp);
+    launch_kernel(attention_decode_kernel<T, DMAX, DEC_HEADS>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, dp);
     QT_CHECK_LAUNCH("attention_decode");
     if (dp.n_splits > 1) {
-        attention_combine_kernel<T><<<p.n_seqs * p.nq, 128, 0, stream>>>(dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.d);
+        launch_kernel(attention_combine_kernel<T>, dim3(p.n_seqs * p.nq), dim3(128), 0, stream, dp.part_acc, dp.part_ml, (T*)p.out, dp.n_splits, p.d);
         QT_CHECK_LAUNCH("attention_combine");
     }
     return QT_OK;

@@ -101,6 +101,8 @@ constexpr int DEC_STAGES = 3;
 
 template <int DMAX>
 __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int d = p.d, lds = d + PAD, dsteps = d >> 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -271,6 +273,8 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaPara
 // One block per (sequence, head): out = sum_s acc_s e^{m_s - m} / sum_s l_s e^{m_s - m}; empty splits have m = -inf.
 __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                              __nv_bfloat16* __restrict__ out, int n_splits, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t item = blockIdx.x;
     float m_all = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m_all = fmaxf(m_all, part_ml[(item * n_splits + s) * 2]);
@@ -294,6 +298,8 @@ constexpr int PF_BQ = 64;
 
 template <int DMAX>
 __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const MmaParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int d = p.d, lds = d + PAD, dsteps = d >> 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -481,15 +487,15 @@ extern "C" int qt_attention_decode_mma(const void* q, const void* k_cache, const
     if (d <= 64) {
         static bool ok = false;
         if (!ok) { rc = raise_smem(attention_decode_mma_kernel<64>, 100 * 1024, "attention_decode_mma"); if (rc) return rc; ok = true; }
-        attention_decode_mma_kernel<64><<<grid, 128, smem, s>>>(p);
+        launch_kernel(attention_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, s, p);
     } else {
         static bool ok = false;
         if (!ok) { rc = raise_smem(attention_decode_mma_kernel<128>, 128 * 1024, "attention_decode_mma"); if (rc) return rc; ok = true; }
-        attention_decode_mma_kernel<128><<<grid, 128, smem, s>>>(p);
+        launch_kernel(attention_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, s, p);
     }
     QT_CHECK_LAUNCH("attention_decode_mma");
     if (n_splits > 1) {
-        attention_combine_mma_kernel<<<n_seqs * nq, 128, 0, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d);
+        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d);
         QT_CHECK_LAUNCH("attention_combine_mma");
     }
     return QT_OK;
@@ -512,11 +518,11 @@ extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, cons
     if (d <= 64) {
         static bool ok = false;
         if (!ok) { rc = raise_smem(attention_prefill_mma_kernel<64>, 100 * 1024, "attention_prefill_mma"); if (rc) return rc; ok = true; }
-        attention_prefill_mma_kernel<64><<<grid, 128, smem, s>>>(p);
+        launch_kernel(attention_prefill_mma_kernel<64>, dim3(grid), dim3(128), smem, s, p);
     } else {
         static bool ok = false;
         if (!ok) { rc = raise_smem(attention_prefill_mma_kernel<128>, 100 * 1024, "attention_prefill_mma"); if (rc) return rc; ok = true; }
-        attention_prefill_mma_kernel<128><<<grid, 128, smem, s>>>(p);
+        launch_kernel(attention_prefill_mma_kernel<128>, dim3(grid), dim3(128), smem, s, p);
     }
     QT_CHECK_LAUNCH("attention_prefill_mma");
     return QT_OK;

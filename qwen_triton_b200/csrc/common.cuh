@@ -10,6 +10,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <utility>
 
 #define QT_OK 0
 #define QT_ERR_ARG -1
@@ -44,6 +47,38 @@ static thread_local char g_error[512] = "";
 
 #define QT_DEFINE_LAST_ERROR(libname)                                   \
     extern "C" const char* qt_last_error_##libname() { return qt::g_error; }
+
+// Programmatic dependent launch.  Every kernel is launched so that it may start while the kernel before
+// it in the stream is still draining; it announces its own dependents at once and, before it touches
+// anything a predecessor wrote (or writes anything a predecessor may still read), waits for the
+// predecessors to finish.  Work that depends on nothing earlier (set-up, weight prefetch) runs ahead of
+// that wait.  QT_B200_PDL=0 in the environment turns the launch attribute off; the wait is then a no-op.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* env = getenv("QT_B200_PDL");
+        enabled = (env && env[0] == '0') ? 0 : 1;
+    }
+    return enabled != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // errors surface in QT_CHECK_LAUNCH
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

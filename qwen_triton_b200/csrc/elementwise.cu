@@ -14,6 +14,8 @@ using namespace qt;
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ residual, const T* __restrict__ table,
                                  const int* __restrict__ ids, int hidden, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     const bool valid = id >= 0 && id < vocab;   // ids are range-checked on the host; never read outside the table
@@ -27,7 +29,7 @@ extern "C" int qt_embedding(float* residual, const void* table, const int* ids, 
     QT_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", n_tokens, hidden, vocab);
     if (n_tokens == 0) return QT_OK;
     return QT_DISPATCH_DTYPE(table_dtype, "embedding", {
-        embedding_kernel<T><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(residual, (const T*)table, ids, hidden, vocab);
+        launch_kernel(embedding_kernel<T>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, residual, (const T*)table, ids, hidden, vocab);
         QT_CHECK_LAUNCH("embedding");
         return QT_OK;
     });
@@ -44,6 +46,8 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                    size_t split_stride, const float* __restrict__ weight, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -90,6 +94,8 @@ template <typename TD, typename TO>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                        size_t split_stride, const float* __restrict__ weight, float eps,
                                        TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -143,7 +149,7 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
         if (vthreads > 1024) vthreads = 1024;
         if (vthreads < 64) vthreads = 64;
 #define QT_LAUNCH_NORM_VEC(TD, TO)                                                                                      \
-    add_rmsnorm_vec_kernel<TD, TO><<<n_rows, vthreads, 0, s>>>(residual, (const TD*)delta, n_splits, (size_t)split_stride, \
+    launch_kernel(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(vthreads), 0, s, residual, (const TD*)delta, n_splits, (size_t)split_stride, \
                                                                weight, eps, (TO*)out, rows, hidden)
         if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM_VEC(float, float);
         else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM_VEC(float, __nv_bfloat16);
@@ -156,7 +162,7 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     }
     const int threads = hidden >= 2048 ? 512 : 256;
 #define QT_LAUNCH_NORM(TD, TO)                                                                                   \
-    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, 0, s>>>(residual, (const TD*)delta, n_splits, (size_t)split_stride, \
+    launch_kernel(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), 0, s, residual, (const TD*)delta, n_splits, (size_t)split_stride, \
                                                           weight, eps, (TO*)out, rows, hidden)
     if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM(float, float);
     else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM(float, __nv_bfloat16);
@@ -189,6 +195,8 @@ struct QkvParams {
 
 template <typename TI, typename TO, bool VEC>
 __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads_total = p.nq + (p.kv_in_proj ? 2 * p.nkv : 0);
@@ -283,8 +291,8 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
                      (!write_kv || (((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0)));
 #define QT_LAUNCH_QKV(TI, TO)                                                                    \
     do {                                                                                         \
-        if (vec) qk_norm_rope_write_kernel<TI, TO, true><<<grid, warps * 32, smem, s>>>(p);      \
-        else qk_norm_rope_write_kernel<TI, TO, false><<<grid, warps * 32, smem, s>>>(p);         \
+        if (vec) launch_kernel(qk_norm_rope_write_kernel<TI, TO, true>, dim3(grid), dim3(warps * 32), smem, s, p);      \
+        else launch_kernel(qk_norm_rope_write_kernel<TI, TO, false>, dim3(grid), dim3(warps * 32), smem, s, p);         \
     } while (0)
     if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_QKV(float, float);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_QKV(float, __nv_bfloat16);
@@ -300,6 +308,8 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
                               long long total, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inter;
@@ -320,9 +330,9 @@ extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long l
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148LL * 32) blocks = 148LL * 32;
     cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == QT_F32 && out_dtype == QT_F32) swiglu_kernel<float, float><<<(unsigned)blocks, threads, 0, s>>>((const float*)gate_up, n_splits, (size_t)split_stride, (float*)out, total, inter);
-    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) swiglu_kernel<float, __nv_bfloat16><<<(unsigned)blocks, threads, 0, s>>>((const float*)gate_up, n_splits, (size_t)split_stride, (__nv_bfloat16*)out, total, inter);
-    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) swiglu_kernel<__nv_bfloat16, __nv_bfloat16><<<(unsigned)blocks, threads, 0, s>>>((const __nv_bfloat16*)gate_up, n_splits, (size_t)split_stride, (__nv_bfloat16*)out, total, inter);
+    if (in_dtype == QT_F32 && out_dtype == QT_F32) launch_kernel(swiglu_kernel<float, float>, dim3((unsigned)blocks), dim3(threads), 0, s, (const float*)gate_up, n_splits, (size_t)split_stride, (float*)out, total, inter);
+    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) launch_kernel(swiglu_kernel<float, __nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, s, (const float*)gate_up, n_splits, (size_t)split_stride, (__nv_bfloat16*)out, total, inter);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) launch_kernel(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, n_splits, (size_t)split_stride, (__nv_bfloat16*)out, total, inter);
     else QT_FAIL(QT_ERR_ARG, "swiglu: unsupported element types %d -> %d", in_dtype, out_dtype);
     QT_CHECK_LAUNCH("swiglu");
     return QT_OK;

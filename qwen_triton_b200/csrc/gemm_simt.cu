@@ -11,6 +11,8 @@ constexpr int GS_BM = 64, GS_BN = 64, GS_BK = 16, GS_THREADS = 256;
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TI* __restrict__ a, const TI* __restrict__ w,
                                                               TO* __restrict__ c, int M, int N, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float as[GS_BK][GS_BM + 4];
     __shared__ float ws[GS_BK][GS_BN + 4];
     const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
@@ -57,9 +59,9 @@ extern "C" int qt_gemm_simt(const void* a, const void* w, int in_dtype, void* c,
     dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
     QT_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d is too large for one launch", M);
     cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == QT_F32 && out_dtype == QT_F32) gemm_simt_kernel<float, float><<<grid, GS_THREADS, 0, s>>>((const float*)a, (const float*)w, (float*)c, M, N, K);
-    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, GS_THREADS, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)c, M, N, K);
-    else if (in_dtype == QT_BF16 && out_dtype == QT_F32) gemm_simt_kernel<__nv_bfloat16, float><<<grid, GS_THREADS, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (float*)c, M, N, K);
+    if (in_dtype == QT_F32 && out_dtype == QT_F32) launch_kernel(gemm_simt_kernel<float, float>, dim3(grid), dim3(GS_THREADS), 0, s, (const float*)a, (const float*)w, (float*)c, M, N, K);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) launch_kernel(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(GS_THREADS), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)c, M, N, K);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_F32) launch_kernel(gemm_simt_kernel<__nv_bfloat16, float>, dim3(grid), dim3(GS_THREADS), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (float*)c, M, N, K);
     else QT_FAIL(QT_ERR_ARG, "gemm_simt: unsupported element types %d -> %d", in_dtype, out_dtype);
     QT_CHECK_LAUNCH("gemm_simt");
     return QT_OK;

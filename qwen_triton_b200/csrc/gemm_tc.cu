@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     const uint32_t full0 = base + stages * STAGE_BYTES, empty0 = full0 + 8 * stages, tmem_full = empty0 + 8 * stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 1);
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int w0 = blockIdx.x * BW, x0 = blockIdx.y * BX, split = blockIdx.z;
     const int kb_begin = split * kb_per_split;
@@ -150,7 +151,17 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb; ++i) {
+            // the weight depends on no earlier kernel: fill the ring with weight tiles first, then wait for
+            // the kernel that produces the activations, then fetch their tiles
+            const int ahead = min(nkb, stages);
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(base + i * STAGE_BYTES, &map_w, full0 + 8 * i, (kb_begin + i) * BK, w0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(base + i * STAGE_BYTES + W_BYTES, &map_x, full0 + 8 * i, (kb_begin + i) * BK, x0);
+            for (int i = ahead; i < nkb; ++i) {
                 const int s = i % stages;
                 const uint32_t phase = (uint32_t)(i / stages) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) break;
@@ -178,6 +189,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         }
     } else {
         const int quarter = warp & 3;                      // the accumulator lanes this warp may read
+        pdl_wait();                                        // the output may still be read by an earlier kernel
         const bool ready = mbar_wait(tmem_full, 0, status, 3);
         tc_fence_after();
         const int n = w0 + quarter * 32 + lane;
@@ -281,7 +293,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, i
     }
     const int kb_per_split = (kb_total + splits - 1) / splits;
     dim3 grid((N + BW - 1) / BW, (M + BX - 1) / BX, splits);
-    gemm_tc_kernel<BX, TO><<<grid, THREADS, smem, stream>>>(map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, status);
+    launch_kernel(gemm_tc_kernel<BX, TO>, dim3(grid), dim3(THREADS), smem, stream, map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, status);
     QT_CHECK_LAUNCH("gemm_tc");
     return QT_OK;
 }

@@ -11,6 +11,8 @@ constexpr int SMP_THREADS = 1024;
 
 // One block per row.
 __global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -45,7 +47,7 @@ __global__ void __launch_bounds__(SMP_THREADS) argmax_kernel(const float* __rest
 extern "C" int qt_argmax(const float* logits, int* out, int rows, int vocab, void* stream) {
     QT_REQUIRE(rows >= 0 && vocab > 0, "argmax: bad sizes rows=%d vocab=%d", rows, vocab);
     if (rows == 0) return QT_OK;
-    argmax_kernel<<<rows, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+    launch_kernel(argmax_kernel, dim3(rows), dim3(SMP_THREADS), 0, (cudaStream_t)stream, logits, out, vocab);
     QT_CHECK_LAUNCH("argmax");
     return QT_OK;
 }
@@ -54,6 +56,8 @@ extern "C" int qt_argmax(const float* logits, int* out, int rows, int vocab, voi
 // weight_i = exp((logit_i - max) / T).  Thread t owns the contiguous ids [t * span, (t + 1) * span).
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
                                                             const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     __shared__ float sums[SMP_THREADS];
     __shared__ int chosen;
@@ -104,7 +108,7 @@ extern "C" int qt_sample(const float* logits, const float* temperature, const fl
                          int vocab, void* stream) {
     QT_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     if (rows == 0) return QT_OK;
-    sample_kernel<<<rows, SMP_THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, uniform, out, vocab);
+    launch_kernel(sample_kernel, dim3(rows), dim3(SMP_THREADS), 0, (cudaStream_t)stream, logits, temperature, uniform, out, vocab);
     QT_CHECK_LAUNCH("sample");
     return QT_OK;
 }

@@ -96,16 +96,24 @@ class Attention:
 
     # ------------------------------------------------------------------ run
     def _splits(self, ctx) -> int:
+        """Ranges the keys of each sequence are cut into for a one-token step: the count whose blocks fill
+        whole waves of the SMs best (two blocks of the tensor-core kernel fit an SM), with at least two
+        pages per range and within what the scratch holds; fewer ranges win near-ties."""
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
+        group = self.nq // self.nkv
         if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128:
             heads_per_block = 16                                 # the tensor-core kernel takes a group of up to 16 heads
         else:
-            heads_per_block = 8 if self.nq // self.nkv > 4 else max(1, self.nq // self.nkv)
-        blocks = ctx.n_seqs * self.nkv * math.ceil((self.nq // self.nkv) / heads_per_block)
-        wanted = max(1, math.ceil(_DECODE_TARGET_BLOCKS / blocks))
-        by_length = max(1, span // _MIN_KEYS_PER_SPLIT)
-        by_scratch = max(1, _MAX_SPLIT_PAIRS // ctx.n_seqs)
-        return max(1, min(wanted, by_length, by_scratch, 64))
+            heads_per_block = 8 if group > 4 else max(1, group)
+        blocks = ctx.n_seqs * self.nkv * math.ceil(group / heads_per_block)
+        most = max(1, min(span // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
+        best, best_fill = 1, 0.0
+        for splits in range(1, most + 1):
+            total = blocks * splits
+            fill = total / (math.ceil(total / _DECODE_TARGET_BLOCKS) * _DECODE_TARGET_BLOCKS)
+            if fill > best_fill + 0.15:
+                best, best_fill = splits, fill
+        return best
 
     def forward(self, x: torch.Tensor, ctx, cache) -> GemmOut:
         tokens = x.shape[0]
