@@ -73,6 +73,7 @@ def _find_build_dir() -> Path:
 
 
 def _source_hash(name: str) -> str:
+    """Hash of the source, every header of the folder and the flags: any change rebuilds the library."""
     digest = hashlib.sha256()
     digest.update(" ".join(NVCC_FLAGS).encode())
     for path in [CSRC / f"{name}.cu", *sorted(CSRC.glob("*.cuh")), *sorted(CSRC.glob("*.h"))]:

@@ -27,6 +27,7 @@ def main(argv=None) -> None:
     parser.add_argument("--warmup", type=int, default=2)
     parser.add_argument("--fill", choices=["prefill", "skip"], default="prefill",
                         help="'skip' leaves the cache content as allocated (zeros): same work for a decode step, no prefill launches")
+    parser.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step (no CUDA graph replay)")
     args = parser.parse_args(argv)
 
     import torch
@@ -38,7 +39,7 @@ def main(argv=None) -> None:
     span = (args.context if args.mode == "decode" else args.tokens) + args.steps + args.warmup + 64
     span = -(-span // 64) * 64
     model = QwenB200ForCausalLM.from_config(config, seed=0, dtype=args.dtype, max_tokens=args.batch * span + 4096,
-                                            max_seq_len=span, max_step_tokens=4096)
+                                            max_seq_len=span, max_step_tokens=4096, cuda_graphs=not args.no_graphs)
     engine = model.engine
     generator = torch.Generator().manual_seed(3)
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
