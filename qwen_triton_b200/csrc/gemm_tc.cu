@@ -110,6 +110,19 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Order of output tiles: groups of RASTER_W consecutive weight tiles, inside a group weight tiles fastest, then
+// token tiles.  Blocks that run at the same time then cover a near-square patch of the output whose weight and
+// activation tiles stay in L2, instead of one long row that streams a whole operand per token tile.
+constexpr int RASTER_W = 16;
+__device__ __forceinline__ void tile_coords(int t, int w_tiles, int x_tiles, int& w, int& x) {
+    const int per_group = RASTER_W * x_tiles;
+    const int group = t / per_group, r = t % per_group;
+    const int first = group * RASTER_W;
+    const int width = min(RASTER_W, w_tiles - first);
+    w = first + r % width;
+    x = r / width;
+}
+
 template <int BX, typename TO>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
@@ -131,7 +144,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int w0 = blockIdx.x * BW, x0 = blockIdx.y * BX, split = blockIdx.z;
+    int w_tile, x_tile;
+    tile_coords(blockIdx.x, (N + BW - 1) / BW, (M + BX - 1) / BX, w_tile, x_tile);
+    const int w0 = w_tile * BW, x0 = x_tile * BX, split = blockIdx.z;
     const int kb_begin = split * kb_per_split;
     const int nkb = min(kb_total, kb_begin + kb_per_split) - kb_begin;   // >= 1: the host sizes the splits so
 
@@ -220,6 +235,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     }
 }
 
+
 // ----------------------------------------------------------------------------- host side
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -275,8 +291,10 @@ template <int BX, typename TO>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
            size_t split_stride, int stages, int* status, cudaStream_t stream) {
     constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
-    // small token tiles: two blocks per SM, each streaming weights through half the shared memory
-    const int budget = BX <= 64 ? 110 * 1024 : 220 * 1024;
+    // Two blocks per SM at every tile size: with few tokens each streams weights through half the shared memory;
+    // with many, the two blocks overlap each other's epilogue and keep two MMA issuers feeding the tensor pipe
+    // (measured faster than one persistent block per SM with a deeper ring and a double-buffered accumulator).
+    const int budget = 110 * 1024;
     const int most = (224 * 1024) / (int)STAGE_BYTES;
     if (stages <= 0) {
         stages = (budget - 2048) / (int)STAGE_BYTES;
@@ -292,11 +310,12 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, i
         configured = true;
     }
     const int kb_per_split = (kb_total + splits - 1) / splits;
-    dim3 grid((N + BW - 1) / BW, (M + BX - 1) / BX, splits);
+    dim3 grid(((N + BW - 1) / BW) * ((M + BX - 1) / BX), 1, splits);
     launch_kernel(gemm_tc_kernel<BX, TO>, dim3(grid), dim3(THREADS), smem, stream, map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, status);
     QT_CHECK_LAUNCH("gemm_tc");
     return QT_OK;
 }
+
 
 template <typename TO>
 int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
@@ -329,7 +348,7 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
     const int per = (kb_total + splits - 1) / splits;
     QT_REQUIRE((splits - 1) * per < kb_total, "gemm_tc: splits=%d would leave a split without K blocks (%d blocks)", splits, kb_total);
     QT_REQUIRE(out_dtype == QT_F32 || splits == 1, "gemm_tc: split-K partial sums are float");
-    QT_REQUIRE((M + token_tile - 1) / token_tile <= 65535, "gemm_tc: M=%d is too large for one launch", M);
+    QT_REQUIRE((long long)((M + token_tile - 1) / token_tile) * ((N + BW - 1) / BW) < (1ll << 31), "gemm_tc: M=%d x N=%d is too large for one launch", M, N);
     CUtensorMap map_w, map_x;
     int rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
     if (rc) return rc;

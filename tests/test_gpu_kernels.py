@@ -340,7 +340,8 @@ def test_kernels_refuse_what_they_cannot_run():
     (1, 503, 96, 1, torch.float32), (8, 640, 512, 2, torch.float32), (8, 6144, 4096, 3, torch.float32),
     (16, 130, 264, 1, torch.bfloat16), (37, 130, 264, 1, torch.bfloat16), (64, 4096, 1536, 4, torch.float32),
     (100, 200, 160, 1, torch.bfloat16), (300, 1000, 1024, 1, torch.bfloat16), (2048, 512, 4096, 1, torch.bfloat16),
-    (513, 257, 72, 1, torch.float32), (5, 129, 8, 1, torch.float32)])
+    (513, 257, 72, 1, torch.float32), (5, 129, 8, 1, torch.float32),
+    (1000, 5000, 256, 1, torch.bfloat16), (4096, 2560, 192, 1, torch.float32), (129, 19000, 64, 1, torch.bfloat16)])
 def test_gemm_tensor_cores(m, n, k, splits, out_dtype):
     a, w = rand(m, k, seed=110, dtype=torch.bfloat16), rand(n, k, seed=111, scale=0.1, dtype=torch.bfloat16)
     expected = a.double() @ w.double().T
@@ -355,10 +356,11 @@ def test_gemm_tensor_cores(m, n, k, splits, out_dtype):
 def test_gemm_tensor_cores_every_token_tile(tile):
     m, n, k = 70, 384, 448
     a, w = rand(m, k, seed=112, dtype=torch.bfloat16), rand(n, k, seed=113, scale=0.1, dtype=torch.bfloat16)
-    out = torch.full((1, m, n), float("nan"), dtype=torch.float32, device=DEV)
-    kernels.gemm_tc(a, w, GemmOut(out), token_tile=tile)
-    kernels.check_status(DEV)
-    close(out[0], a.double() @ w.double().T, torch.float32, f"token tile {tile}")
+    for stages in (0, 3):           # the default ring depth for the tile, and a forced one
+        out = torch.full((1, m, n), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.gemm_tc(a, w, GemmOut(out), token_tile=tile, stages=stages)
+        kernels.check_status(DEV)
+        close(out[0], a.double() @ w.double().T, torch.float32, f"token tile {tile}, stages {stages}")
 
 
 def test_gemm_dispatch_is_static():
