@@ -69,10 +69,10 @@ extern "C" int qt_attention_decode_static(const void* q, const void* k_cache, co
 
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                n_splits, part_acc, part_ml};
+                n_splits, part_acc, part_ml, DEC_MAX_STAGES};
     const int lds = d + PAD;
     const size_t stage = 2 * (size_t)PAGE * lds * 2;
-    size_t smem = 16 * lds * 2 + DEC_STAGES * stage;
+    size_t smem = 16 * lds * 2 + DEC_MAX_STAGES * stage;
     const size_t merge = 16 * lds * 2 + (size_t)4 * 16 * d * 4 + 4 * 16 * 2 * 4;
     if (merge > smem) smem = merge;
     const int group = nq / nkv;

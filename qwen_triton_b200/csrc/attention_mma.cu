@@ -32,6 +32,18 @@ int check(const char* name, int n_seqs, int nq, int nkv, int d, int page_tokens,
     return QT_OK;
 }
 
+// Depth of the decode kernel's tile ring.  Two stages leave room for three blocks per SM at head size 128, which
+// measured faster than three stages and two blocks (the kernel is bound by latency, not by bytes in flight);
+// QT_B200_DECODE_STAGES=3 selects the deeper ring.
+int decode_stages() {
+    static int stages = 0;
+    if (stages == 0) {
+        const char* env = getenv("QT_B200_DECODE_STAGES");
+        stages = (env && env[0] == '3') ? 3 : 2;
+    }
+    return stages;
+}
+
 template <typename K>
 int raise_smem(K kernel, size_t bytes, const char* name) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -52,10 +64,10 @@ extern "C" int qt_attention_decode_mma(const void* q, const void* k_cache, const
     QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode_mma: split results need scratch memory");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                n_splits, part_acc, part_ml};
+                n_splits, part_acc, part_ml, decode_stages()};
     const int lds = d + PAD;
     const size_t stage = 2 * (size_t)PAGE * lds * 2;
-    size_t smem = 16 * lds * 2 + DEC_STAGES * stage;
+    size_t smem = 16 * lds * 2 + p.stages * stage;
     const size_t merge = 16 * lds * 2 + (size_t)4 * 16 * d * 4 + 4 * 16 * 2 * 4;
     if (merge > smem) smem = merge;
     const int group = nq / nkv;
@@ -87,9 +99,9 @@ extern "C" int qt_attention_prefill_mma(const void* q, const void* k_cache, cons
     if (rc) return rc;
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, seq_start, seq_past, nullptr, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                1, nullptr, nullptr};
+                1, nullptr, nullptr, 2};
     const int lds = d + PAD;
-    const size_t smem = (size_t)5 * PAGE * lds * 2;
+    const size_t smem = (size_t)4 * PAGE * lds * 2;
     dim3 grid((max_q_len + PF_BQ - 1) / PF_BQ, nq, n_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     if (d <= 64) {

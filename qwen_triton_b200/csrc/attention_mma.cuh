@@ -40,6 +40,7 @@ struct MmaParams {
     int n_seqs, nq, nkv, d, ring_tokens, window;
     float scale;
     int n_splits; float* part_acc; float* part_ml;
+    int stages;                    // decode: tiles in the shared-memory ring
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -99,7 +100,7 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[DMAX / 16][4], uint3
 }
 
 // ----------------------------------------------------------------------------- decode
-constexpr int DEC_STAGES = 3;
+constexpr int DEC_MAX_STAGES = 3;     // depth of the key/value tile ring (2 or 3; fewer stages, more blocks per SM)
 
 template <int DMAX>
 __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaParams p) {
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaPara
     const int rows = min(16, group - h0);
     const int head_base = kvh * group + h0;
     const int seq = blockIdx.z, split = blockIdx.x;
+    const int stages = p.stages;
 
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][lds]
     const uint32_t tile_bytes = (uint32_t)PAGE * lds * 2u;
@@ -141,14 +143,14 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaPara
         if (tile < n_tiles) {
             const int page = cache_page(table, page_begin + tile, p.ring_tokens);
             const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
-            const uint32_t dst = kv0 + (uint32_t)(tile % DEC_STAGES) * 2u * tile_bytes;
+            const uint32_t dst = kv0 + (uint32_t)(tile % stages) * 2u * tile_bytes;
             load_tile(dst, p.k_cache + off, d, lds, tid, 128);
             load_tile(dst + tile_bytes, p.v_cache + off, d, lds, tid, 128);
         }
         cp_async_commit();
     };
     issue(0);
-    issue(1);
+    if (stages > 2) issue(1);
     __syncthreads();
     uint32_t qf[DMAX / 16][4];
     load_q_frags<DMAX>(qf, smem_u32(q_s), lds, dsteps, lane);
@@ -160,10 +162,10 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaPara
     const float scale2 = p.scale * LOG2E;
 
     for (int tile = 0; tile < n_tiles; ++tile) {
-        issue(tile + 2);
-        cp_async_wait<2>();
+        issue(tile + stages - 1);                                    // keeps stages - 1 tiles in flight behind this one
+        if (stages > 2) cp_async_wait<2>(); else cp_async_wait<1>();
         __syncthreads();
-        const uint32_t k_s = kv0 + (uint32_t)(tile % DEC_STAGES) * 2u * tile_bytes, v_s = k_s + tile_bytes;
+        const uint32_t k_s = kv0 + (uint32_t)(tile % stages) * 2u * tile_bytes, v_s = k_s + tile_bytes;
         const int key0 = warp * 16;                                  // this warp's keys within the tile
         const int pos0 = (page_begin + tile) * PAGE + key0;
         if (pos0 < len && pos0 + 16 > lo) {                          // some key of this warp is visible
@@ -315,8 +317,9 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const MmaPar
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
 
     const uint32_t tile_bytes = (uint32_t)PAGE * lds * 2u;
-    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [64][lds]
-    const uint32_t kv0 = smem_u32(smem_raw) + tile_bytes;                            // two stages of (K tile, V tile)
+    const uint32_t kv0 = smem_u32(smem_raw);                                         // two stages of (K tile, V tile)
+    // the query tile borrows the second stage's key tile until its fragments sit in registers
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw + 2 * tile_bytes);   // [64][lds]
 
     const int p_first = past + q0, p_last = past + q0 + rows - 1;
     const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
@@ -342,6 +345,7 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const MmaPar
     __syncthreads();
     uint32_t qf[DMAX / 16][4];
     load_q_frags<DMAX>(qf, smem_u32(q_s) + (uint32_t)(warp * 16 * lds) * 2u, lds, dsteps, lane);
+    __syncthreads();                                                                 // before the second stage is filled
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[DMAX / 8][4];

@@ -321,19 +321,53 @@ __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size
     }
 }
 
+// Four elements per thread with 8- or 16-byte loads and stores (widths that are multiples of 4, aligned bases).
+template <typename TI, typename TO>
+__global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
+                                  long long total4, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int chunks = inter >> 2;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / chunks;
+        const int i = (int)(idx % chunks) * 4;
+        const TI* gp = gate_up + (size_t)t * 2 * inter + i;
+        float4 g = load4(gp), u = load4(gp + inter);
+#pragma unroll 4
+        for (int s = 1; s < n_splits; ++s) {
+            const float4 dg = load4(gp + (size_t)s * split_stride), du = load4(gp + inter + (size_t)s * split_stride);
+            g.x += dg.x; g.y += dg.y; g.z += dg.z; g.w += dg.w;
+            u.x += du.x; u.y += du.y; u.z += du.z; u.w += du.w;
+        }
+        store4(out + (size_t)t * inter + i, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
+                                                        g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+    }
+}
+
 extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long long split_stride, void* out, int out_dtype,
                          int n_tokens, int inter, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && inter > 0 && n_splits >= 1, "swiglu: bad sizes T=%d I=%d", n_tokens, inter);
     if (n_tokens == 0) return QT_OK;
     const long long total = (long long)n_tokens * inter;
     const int threads = 256;
-    long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148LL * 32) blocks = 148LL * 32;
     cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == QT_F32 && out_dtype == QT_F32) launch_kernel(swiglu_kernel<float, float>, dim3((unsigned)blocks), dim3(threads), 0, s, (const float*)gate_up, n_splits, (size_t)split_stride, (float*)out, total, inter);
-    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) launch_kernel(swiglu_kernel<float, __nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, s, (const float*)gate_up, n_splits, (size_t)split_stride, (__nv_bfloat16*)out, total, inter);
-    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) launch_kernel(swiglu_kernel<__nv_bfloat16, __nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gate_up, n_splits, (size_t)split_stride, (__nv_bfloat16*)out, total, inter);
+    const bool vec = inter % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const long long work = vec ? total / 4 : total;
+    long long blocks = (work + threads - 1) / threads;
+    if (blocks > 148LL * 16) blocks = 148LL * 16;
+#define QT_LAUNCH_SWIGLU(TI, TO)                                                                                              \
+    do {                                                                                                                      \
+        if (vec) launch_kernel(swiglu_vec_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up,    \
+                               n_splits, (size_t)split_stride, (TO*)out, work, inter);                                        \
+        else launch_kernel(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up, n_splits,  \
+                           (size_t)split_stride, (TO*)out, work, inter);                                                      \
+    } while (0)
+    if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_SWIGLU(float, float);
+    else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_SWIGLU(float, __nv_bfloat16);
+    else if (in_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_SWIGLU(__nv_bfloat16, __nv_bfloat16);
     else QT_FAIL(QT_ERR_ARG, "swiglu: unsupported element types %d -> %d", in_dtype, out_dtype);
+#undef QT_LAUNCH_SWIGLU
     QT_CHECK_LAUNCH("swiglu");
     return QT_OK;
 }

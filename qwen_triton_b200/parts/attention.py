@@ -17,7 +17,7 @@ from ..weights.tensors import TensorSpec
 from .base import KVRequest, Runtime, part_class, register_mixer, to_device
 from .linear import Linear
 
-_DECODE_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight for the one-token kernel
+_DECODE_TARGET_BLOCKS = 3 * 148     # blocks of the one-token kernel that are resident at once (three per SM)
 _MAX_SPLIT_PAIRS = 640              # (sequence, split) pairs the scratch holds
 _MIN_KEYS_PER_SPLIT = 128
 
@@ -97,8 +97,8 @@ class Attention:
     # ------------------------------------------------------------------ run
     def _splits(self, ctx) -> int:
         """Ranges the keys of each sequence are cut into for a one-token step: the count whose blocks fill
-        whole waves of the SMs best (two blocks of the tensor-core kernel fit an SM), with at least two
-        pages per range and within what the scratch holds; fewer ranges win near-ties."""
+        whole waves of the SMs (three blocks of the tensor-core kernel fit an SM) nearly as well as the best
+        count does, the smallest such; at least two pages per range and within what the scratch holds."""
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
         group = self.nq // self.nkv
         if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128:
@@ -107,13 +107,12 @@ class Attention:
             heads_per_block = 8 if group > 4 else max(1, group)
         blocks = ctx.n_seqs * self.nkv * math.ceil(group / heads_per_block)
         most = max(1, min(span // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
-        best, best_fill = 1, 0.0
+        fills = []
         for splits in range(1, most + 1):
             total = blocks * splits
-            fill = total / (math.ceil(total / _DECODE_TARGET_BLOCKS) * _DECODE_TARGET_BLOCKS)
-            if fill > best_fill + 0.15:
-                best, best_fill = splits, fill
-        return best
+            fills.append(total / (math.ceil(total / _DECODE_TARGET_BLOCKS) * _DECODE_TARGET_BLOCKS))
+        enough = max(fills) - 0.13
+        return next(splits for splits, fill in enumerate(fills, start=1) if fill >= enough)
 
     def forward(self, x: torch.Tensor, ctx, cache) -> GemmOut:
         tokens = x.shape[0]
