@@ -1,0 +1,70 @@
+"""The engine at the layer sizes of the benchmark model (hidden 4096, 32/8 heads of 128, intermediate
+12288) with two layers and a smaller vocabulary, against the plain implementation: the tile shapes, split
+counts and tensor-core kernels that the tiny configurations never reach.
+
+Sums here run over 4,096 to 12,288 terms and logits reach +-4, so the bars are stated against the float64
+result of the plain implementation and scaled to the logits: the float32 engine may be at most four times
+as far from it as the plain float32 implementation itself is (both differ from it only by the order of
+their float32 sums); the bfloat16 engine at most 2e-2 (the reference's bfloat16 bar,
+tests/test_kernels.py:150) of the largest logit."""
+import dataclasses
+import tempfile
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from qwen_triton_b200 import Engine, StepEntry, load_preset, write_random_model
+from qwen_triton_b200.weights import Checkpoint
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def big():
+    full = load_preset("qwen3-8b")
+    config = dataclasses.replace(full, num_hidden_layers=2, layer_types=full.layer_types[:2], vocab_size=20011,
+                                 eos_token_id=())
+    with tempfile.TemporaryDirectory(prefix="qt_big_") as folder:
+        write_random_model(folder, config, seed=5, dtype=torch.bfloat16)
+        checkpoint = Checkpoint(folder)
+        weights = {name: checkpoint.read(name).float() for name in checkpoint.names()}
+        yield config, folder, weights
+
+
+def tokens_for(config, length, seed):
+    return torch.randint(0, config.vocab_size, (length,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_benchmark_layer_shapes_against_the_plain_implementation(big, dtype):
+    config, folder, weights = big
+    raw = config.to_hf_dict()
+    engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=1024)
+    requests = [tokens_for(config, 70, 1), tokens_for(config, 9, 2)]
+    truth = [plain.forward(raw, weights, r, dtype=torch.float64) for r in requests]
+    plain32 = [plain.forward(raw, weights, r) for r in requests]
+    slots = [engine.new_sequence() for _ in requests]
+    # prompts of unequal length in one step, then one token each (plain launches, then captured steps)
+    prompt = [40, 3]
+    got = {0: [], 1: []}
+    first = engine.step([StepEntry(s, r[:p], list(range(p))) for s, r, p in zip(slots, requests, prompt)])
+    got[0].append(first[:prompt[0]])
+    got[1].append(first[prompt[0]:])
+    at = list(prompt)
+    while any(a < len(r) for a, r in zip(at, requests)):
+        live = [i for i in (0, 1) if at[i] < len(requests[i])]
+        out = engine.step([StepEntry(slots[i], [requests[i][at[i]]], [0]) for i in live])
+        for row, i in enumerate(live):
+            got[i].append(out[row:row + 1])
+            at[i] += 1
+    for slot in slots:
+        engine.release(slot)
+    for i in (0, 1):
+        engine_error = float((torch.cat(got[i]).double().cpu() - truth[i]).abs().max())
+        scale = float(truth[i].abs().max())
+        if dtype == "fp32":
+            plain_error = float((plain32[i].double() - truth[i]).abs().max())
+            assert engine_error <= 4 * plain_error + 1e-6, (i, engine_error, plain_error)
+        else:
+            assert engine_error <= 2e-2 * scale, (i, engine_error, scale)
