@@ -81,14 +81,40 @@ __device__ __forceinline__ int cache_page(const int* table, int position_page, i
     return table[index];
 }
 
-// Start the copy of one [64, d] tile (a page of one kv head) into padded shared-memory rows.
-__device__ __forceinline__ void load_tile(uint32_t dst, const __nv_bfloat16* src, int d, int lds, int tid, int nthreads) {
-    const int chunks = d >> 3;                       // 16-byte chunks per row
-    for (int i = tid; i < PAGE * chunks; i += nthreads) {
-        const int r = i / chunks, c = i % chunks;
-        cp_async16(dst + (uint32_t)(r * lds + c * 8) * 2u, src + (size_t)r * d + c * 8);
+// Copy of a [64, d] tile (a page of one kv head) into padded shared-memory rows by a 128-thread block, 16 bytes
+// per cp.async.  Where the chunks of a row divide the block size (head sizes 16, 32, 64, 128) a thread's chunks
+// lie a fixed stride apart, so the loop is one add per chunk; other head sizes work the row and chunk out per
+// piece (integer divisions by the runtime head size, which cost more than the copy itself).
+struct TileCopy {
+    int d, lds, chunks, pieces;          // pieces: 16-byte chunks of the tile
+    bool linear;
+    uint32_t dst0, dst_step;             // bytes
+    int src0, src_step;                  // elements
+    int tid;
+
+    __device__ __forceinline__ TileCopy(int d_, int lds_, int tid_) : d(d_), lds(lds_), tid(tid_) {
+        chunks = d >> 3;
+        pieces = PAGE * chunks;
+        linear = (128 % chunks) == 0;
+        const int r = tid / chunks, c8 = (tid % chunks) * 8, rows_per_round = 128 / chunks;
+        dst0 = (uint32_t)(r * lds + c8) * 2u;
+        dst_step = (uint32_t)(rows_per_round * lds) * 2u;
+        src0 = r * d + c8;
+        src_step = rows_per_round * d;
     }
-}
+    __device__ __forceinline__ void start(uint32_t tile_smem, const __nv_bfloat16* tile_global) const {
+        if (linear) {
+            uint32_t dst = tile_smem + dst0;
+            const __nv_bfloat16* src = tile_global + src0;
+            for (int i = tid; i < pieces; i += 128, dst += dst_step, src += src_step) cp_async16(dst, src);
+        } else {
+            for (int i = tid; i < pieces; i += 128) {
+                const int r = i / chunks, c8 = (i % chunks) * 8;
+                cp_async16(tile_smem + (uint32_t)(r * lds + c8) * 2u, tile_global + r * d + c8);
+            }
+        }
+    }
+};
 
 // Query fragments of a 16-row tile held in shared memory (row stride lds): qf[ks] covers dims 16 ks .. 16 ks + 15.
 template <int DMAX>
@@ -103,9 +129,8 @@ __device__ __forceinline__ void load_q_frags(uint32_t (&qf)[DMAX / 16][4], uint3
 constexpr int DEC_MAX_STAGES = 3;     // depth of the key/value tile ring (2 or 3; fewer stages, more blocks per SM)
 
 template <int DMAX>
-__global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaParams p) {
+__global__ void __launch_bounds__(128, 3) attention_decode_mma_kernel(const MmaParams p) {
     pdl_launch_dependents();
-    pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int d = p.d, lds = d + PAD, dsteps = d >> 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -133,23 +158,29 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(const MmaPara
     const int n_tiles = max(0, page_end - page_begin);
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
 
+    const TileCopy copy(d, lds, tid);
+    auto issue = [&](int tile) {
+        if (tile < n_tiles) {
+            const int page = cache_page(table, page_begin + tile, p.ring_tokens);
+            const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
+            const uint32_t dst = kv0 + (uint32_t)(tile % stages) * 2u * tile_bytes;
+            copy.start(dst, p.k_cache + off);
+            copy.start(dst + tile_bytes, p.v_cache + off);
+        }
+        cp_async_commit();
+    };
+    // Keys and values of earlier positions do not depend on the kernel before this one (it writes only the new
+    // token's row, which lies in the last page): their first tile is requested before waiting for that kernel.
+    const bool early = n_tiles > 0 && page_begin < last_page;
+    if (early) issue(0);
+    pdl_wait();
     for (int i = tid; i < 16 * (d >> 3); i += 128) {                                 // query rows, zero beyond the group
         const int r = i / (d >> 3), c = i % (d >> 3);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)seq * p.nq + head_base + r) * d + c * 8);
         *reinterpret_cast<uint4*>(q_s + r * lds + c * 8) = v;
     }
-    auto issue = [&](int tile) {
-        if (tile < n_tiles) {
-            const int page = cache_page(table, page_begin + tile, p.ring_tokens);
-            const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
-            const uint32_t dst = kv0 + (uint32_t)(tile % stages) * 2u * tile_bytes;
-            load_tile(dst, p.k_cache + off, d, lds, tid, 128);
-            load_tile(dst + tile_bytes, p.v_cache + off, d, lds, tid, 128);
-        }
-        cp_async_commit();
-    };
-    issue(0);
+    if (!early) issue(0);
     if (stages > 2) issue(1);
     __syncthreads();
     uint32_t qf[DMAX / 16][4];
@@ -331,13 +362,14 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const MmaPar
         if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(q_begin + q0 + r) * p.nq + head) * d + c * 8);
         *reinterpret_cast<uint4*>(q_s + r * lds + c * 8) = v;
     }
+    const TileCopy copy(d, lds, tid);
     auto issue = [&](int tile) {
         if (tile < n_tiles) {
             const int page = cache_page(table, page_begin + tile, p.ring_tokens);
             const size_t off = ((size_t)page * p.nkv + kvh) * PAGE * d;
             const uint32_t dst = kv0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
-            load_tile(dst, p.k_cache + off, d, lds, tid, 128);
-            load_tile(dst + tile_bytes, p.v_cache + off, d, lds, tid, 128);
+            copy.start(dst, p.k_cache + off);
+            copy.start(dst + tile_bytes, p.v_cache + off);
         }
         cp_async_commit();
     };
