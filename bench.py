@@ -30,7 +30,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 def parse_args():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=128)
     parser.add_argument("--warmup", type=int, default=4)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--preset", default="qwen3-8b")
@@ -75,7 +75,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.device_index), "-lms", "100"], stdout=self.file,
+                                          "-i", str(self.device_index), "-lms", "50"], stdout=self.file,
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
