@@ -332,7 +332,7 @@ __global__ void attention_combine_mma_kernel(const float* __restrict__ part_acc,
 constexpr int PF_BQ = 64;
 
 template <int DMAX>
-__global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const MmaParams p) {
+__global__ void __launch_bounds__(128, 3) attention_prefill_mma_kernel(const MmaParams p) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -415,32 +415,40 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const MmaPar
                     }
                 }
             }
+            // Scores stay unscaled; the scale is folded into the exponent: p = 2^(s * scale2 - m * scale2), one FMA
+            // and one ex2 per score.  Most tiles lie wholly below the diagonal (and inside the window) for every row
+            // of the warp and need no mask.
             const bool all_visible = pos0 + PAGE - 1 <= warp_pos_min && (p.window <= 0 || pos0 > warp_pos_max - p.window);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (!all_visible) {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int pos = pos0 + nt * 8 + 2 * t + (e & 1);
+                        const int qp = qpos[e >> 1];
+                        const bool visible = pos <= qp && (p.window <= 0 || pos > qp - p.window);
+                        if (!visible) s[nt][e] = -INFINITY;
+                    }
+            }
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int pos = pos0 + nt * 8 + 2 * t + (e & 1);
-                    const int qp = qpos[e >> 1];
-                    const bool visible = all_visible || (pos <= qp && (p.window <= 0 || pos > qp - p.window));
-                    s[nt][e] = visible ? s[nt][e] * scale2 : -INFINITY;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
-                }
+                for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
             float alpha[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-                const float m_new = fmaxf(m[r], mx[r]);
+                const float m_new = fmaxf(m[r], mx[r] * scale2);       // scale2 > 0: the max of the scaled scores
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 alpha[r] = fast_exp2(m[r] - m_use);
                 m[r] = m_new;
                 float sum = 0.f;
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
-                    s[nt][2 * r] = fast_exp2(s[nt][2 * r] - m_use);
-                    s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - m_use);
+                    s[nt][2 * r] = fast_exp2(fmaf(s[nt][2 * r], scale2, -m_use));
+                    s[nt][2 * r + 1] = fast_exp2(fmaf(s[nt][2 * r + 1], scale2, -m_use));
                     sum += s[nt][2 * r] + s[nt][2 * r + 1];
                 }
                 l[r] = l[r] * alpha[r] + sum;
