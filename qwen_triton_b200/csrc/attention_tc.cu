@@ -1,0 +1,418 @@
+// Causal attention for steps with many tokens per sequence on the fifth-generation tensor cores
+// (bfloat16, head size 64 or 128, paged cache with 64-token pages).
+//
+// A block takes 128 query rows of one head and walks the keys in tiles of 128 (two pages):
+//
+//   S = Q K^T        tcgen05.mma, Q and K tiles in shared memory (TMA, 128-byte swizzle), S in tensor memory
+//   P = softmax(S)   four warps, one thread per query row: a row of S is read with tcgen05.ld, so the row
+//                    maximum and sum need no shuffles; P goes to shared memory as bfloat16 in the MMA's
+//                    swizzled K-major layout
+//   O += P V         tcgen05.mma with V as an MN-major operand (V is stored [key][dim]); the product lands in
+//                    tensor memory and is folded into the float accumulator O that each thread keeps for its row
+//
+// Warp roles (352 threads): warp 0 lane 0 = TMA producer of Q and of the K tiles, warp 10 lane 0 = TMA producer of
+// the V tiles (two-stage rings each; separate producers so that a key tile is requested as soon as its stage is
+// free, not behind a value tile), warp 1 = tensor-memory allocation and (lane 0) MMA issue, warps 2..9 = softmax
+// and output: two threads per
+// query row, each on 64 of the tile's 128 keys and on half of the output columns.  S is double
+// buffered: Q K^T of tile j+1 runs while the softmax of tile j is computed, and P V of tile j runs while the
+// maximum of tile j+1 is taken.  Key j is visible to the query at absolute position p iff j <= p and, in a
+// windowed group, j > p - window.  Every mbarrier wait is bounded and reports through a status word.
+//
+// Counterpart in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (32 x 32 tl.dot tiles) and the masked
+// SDPA branch of modules/attention.py:110-123.
+#include "tc_common.cuh"
+
+#include <math.h>
+
+using namespace qt;
+using namespace qt_tc;
+
+namespace {
+
+constexpr int PAGE = 64;
+constexpr int BQ = 128;            // query rows per block = MMA M
+constexpr int BKEY = 128;          // keys per tile = two pages
+constexpr int THREADS = 352;        // warp 0: TMA of Q and K, warp 1: MMA + tensor-memory allocation, warps 2..9: softmax, warp 10: TMA of V
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr uint32_t HALF_BYTES = 128 * 64 * 2;   // a [128 rows][64 columns] bfloat16 half tile: 16 KB
+
+struct TcAttnParams {
+    __nv_bfloat16* out;            // [T, nq, d]
+    const int* block_table; int max_blocks;
+    const int* seq_start; const int* seq_past;
+    int nq, nkv, ring_tokens, window;
+    float scale;
+    int* status;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Operand descriptor of an MN-major tile stored as [64-element MN blocks][K rows][64 elements], 128-byte swizzle:
+// groups of 8 K rows lie 1024 bytes apart (stride byte offset), MN blocks `mn_block_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t operand_desc_mn(uint32_t saddr, uint32_t mn_block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ int cache_page(const int* table, int max_blocks, int position_page, int ring_tokens) {
+    int index = ring_tokens > 0 ? position_page % (ring_tokens / PAGE) : position_page;
+    if (index >= max_blocks) index = max_blocks - 1;     // beyond the sequence: any valid page, its keys are masked
+    return table[index];
+}
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                       const __grid_constant__ CUtensorMap map_k,
+                                                                       const __grid_constant__ CUtensorMap map_v,
+                                                                       const TcAttnParams p) {
+    constexpr int HALVES = HD / 64;                       // 64-column halves of a [*, HD] tile
+    constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES;     // [128 rows][HD]
+    constexpr uint32_t KV_BYTES = HALVES * HALF_BYTES;    // [128 keys][HD]
+    constexpr uint32_t P_BYTES = 2 * HALF_BYTES;          // [128 rows][128 keys]
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t S_COL0 = 0, S_COL1 = 128, PV_COL = 256;
+    // S = Q K^T: M 128, N 128 keys, both operands K-major.  O = P V: M 128, N HD, A K-major, B MN-major.
+    constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKEY >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+
+    pdl_launch_dependents();
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_begin = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q_begin;
+    // blocks are handed out in launch order: the last query tiles of a sequence walk the most keys, so they go first
+    const int q0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BQ;
+    if (q0 >= q_len) return;                              // uniform for the block, before any barrier or allocation
+    const int rows = min(BQ, q_len - q0);
+    const int past = p.seq_past[seq];
+    const int kvh = head / (p.nq / p.nkv);
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+    const int p_first = past + q0, p_last = past + q0 + rows - 1;
+    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int tile_begin = lo / BKEY;
+    const int n_tiles = p_last / BKEY - tile_begin + 1;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
+    const uint32_t bars = p_s + P_BYTES;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_full, x_bar[2], l_bar
+    const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56;
+    const uint32_t s_full = bars + 72, s_empty = bars + 88, p_full = bars + 104, pv_full = bars + 112;
+    const uint32_t x_bar = bars + 120, l_bar = bars + 136;   // the softmax threads' own exchanges: x_bar[2], l_bar
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + 144);
+    float* exchange = reinterpret_cast<float*>(smem + (bars - base) + 160);      // [2 parities][2 halves][128 rows]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int* status = p.status;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1); mbar_init(s_empty + 8 * i, 8);
+        }
+        mbar_init(p_full, 8);
+        mbar_init(pv_full, 1);
+        mbar_init(x_bar, 8); mbar_init(x_bar + 8, 8); mbar_init(l_bar, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();                                   // queries and this step's keys come from the kernel before
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_2d(q_s + h * HALF_BYTES, &map_q, q_full, head * HD + h * 64, q_begin + q0);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t phase = (uint32_t)(j >> 1) & 1u;
+                if (!mbar_wait(k_empty + 8 * s, phase ^ 1u, status, 1)) break;
+                mbar_expect_tx(k_full + 8 * s, KV_BYTES);
+                for (int pg = 0; pg < 2; ++pg) {
+                    const int row0 = (cache_page(table, p.max_blocks, (tile_begin + j) * 2 + pg, p.ring_tokens) * p.nkv + kvh) * PAGE;
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(k_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_k, k_full + 8 * s, h * 64, row0);
+                }
+            }
+        }
+    } else if (warp == 10) {
+        if (lane == 0) {
+            pdl_wait();
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j & 1;
+                const uint32_t phase = (uint32_t)(j >> 1) & 1u;
+                if (!mbar_wait(v_empty + 8 * s, phase ^ 1u, status, 1)) break;
+                mbar_expect_tx(v_full + 8 * s, KV_BYTES);
+                for (int pg = 0; pg < 2; ++pg) {
+                    const int row0 = (cache_page(table, p.max_blocks, (tile_begin + j) * 2 + pg, p.ring_tokens) * p.nkv + kvh) * PAGE;
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(v_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_v, v_full + 8 * s, h * 64, row0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait(q_full, 0, status, 2);
+            auto issue_qk = [&](int i) {
+                const int s = i & 1;
+                const uint32_t phase = (uint32_t)(i >> 1) & 1u;
+                if (!mbar_wait(k_full + 8 * s, phase, status, 2)) return false;
+                if (!mbar_wait(s_empty + 8 * s, phase ^ 1u, status, 2)) return false;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (s ? S_COL1 : S_COL0);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {    // 16 dims per MMA; 4 MMAs per 64-column half
+                    const uint32_t off = (uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32u;
+                    umma_bf16(acc, operand_desc(q_s + off), operand_desc(k_s + s * KV_BYTES + off), IDESC_QK, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(s_full + 8 * s);
+                umma_commit(k_empty + 8 * s);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
+                const int s = j & 1;
+                if (!mbar_wait(p_full, (uint32_t)j & 1u, status, 2)) break;
+                if (!mbar_wait(v_full + 8 * s, (uint32_t)(j >> 1) & 1u, status, 2)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < BKEY / 16; ++ks) {  // 16 keys per MMA
+                    const uint64_t a_desc = operand_desc(p_s + (uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32u);
+                    const uint64_t b_desc = operand_desc_mn(v_s + s * KV_BYTES + (uint32_t)ks * (16 * 128), HALF_BYTES);
+                    umma_bf16(tmem_base + PV_COL, a_desc, b_desc, IDESC_PV, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(pv_full);
+                umma_commit(v_empty + 8 * s);
+            }
+        }
+    } else if (warp < 10) {
+        constexpr int HC = HD / 2;                         // output columns of this thread
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                  // which 64 keys of a tile, and which half of the output columns
+        const int r = quarter * 32 + lane;                 // this thread's query row = its tensor-memory lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const int qpos = min(past + q0 + r, p_last);       // rows beyond the sequence act as its last row
+        const float scale2 = p.scale * LOG2E;
+        float o[HC];
+#pragma unroll
+        for (int c = 0; c < HC; ++c) o[c] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
+        pdl_wait();                                        // the output may still be read by an earlier kernel
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j & 1;
+            if (!mbar_wait(s_full + 8 * s, (uint32_t)(j >> 1) & 1u, status, 3)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t s_addr = lane_addr + (s ? S_COL1 : S_COL0) + (uint32_t)(half * 64);
+            const int pos0 = (tile_begin + j) * BKEY + half * 64;
+            // mask only where some row of the block cannot see the whole tile
+            const bool masked = (tile_begin + j) * BKEY + BKEY - 1 > p_first || (p.window > 0 && (tile_begin + j) * BKEY <= p_last - p.window);
+            // pass 1: the maximum of this thread's 64 scores, then of the whole row through shared memory
+            float mx = -INFINITY;
+            if (!masked) {                                 // the common case: one max per score
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_load32(s_addr + (uint32_t)c0, v);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(v[c]));
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_load32(s_addr + (uint32_t)c0, v);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int pos = pos0 + c0 + c;
+                        const bool visible = pos <= qpos && (p.window <= 0 || pos > qpos - p.window);
+                        mx = fmaxf(mx, visible ? __uint_as_float(v[c]) : -INFINITY);
+                    }
+                }
+            }
+            exchange[(s * 2 + half) * 128 + r] = mx;
+            __syncwarp();                                  // the warp's values are written; one arrival per warp releases them
+            if (lane == 0) mbar_arrive(x_bar + 8 * s);
+            if (!mbar_wait(x_bar + 8 * s, (uint32_t)(j >> 1) & 1u, status, 3)) { ok = false; break; }
+            mx = fmaxf(mx, exchange[(s * 2 + (half ^ 1)) * 128 + r]);
+            const float m_new = fmaxf(m_run, mx * scale2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = fast_exp2(m_run - m_use);
+            // the product of the previous tile: fold it into O (this also frees P and the product buffer)
+            if (j > 0) {
+                if (!mbar_wait(pv_full, (uint32_t)(j - 1) & 1u, status, 3)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < HC; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_load32(lane_addr + PV_COL + (uint32_t)(half * HC + c0), v);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c0 + c] = fmaf(o[c0 + c], alpha_pending, __uint_as_float(v[c]));
+                }
+            }
+            // pass 2: P = 2^(s * scale2 - m), as bfloat16 into the swizzled K-major tile; the row sum
+            float sum = 0.f;
+            const uint32_t p_row = p_s + (uint32_t)half * HALF_BYTES + (uint32_t)r * 128u;
+            const float neg_m = -m_use;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                uint32_t v[32];
+                tmem_load32(s_addr + (uint32_t)c0, v);
+                if (masked) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int pos = pos0 + c0 + c;
+                        if (!(pos <= qpos && (p.window <= 0 || pos > qpos - p.window))) v[c] = 0xff800000u;   // -inf
+                    }
+                }
+                uint32_t packed[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(v[c]), scale2, neg_m));
+                    const float e1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), scale2, neg_m));
+                    sum += e0 + e1;
+                    packed[c >> 1] = pack_bf16(e0, e1);
+                }
+                // 32 keys = four 16-byte chunks of this row; the chunk index inside the 64-key half is XORed with row % 8
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint32_t chunk = (uint32_t)((c0 >> 3) + q4) ^ (uint32_t)(r & 7);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + chunk * 16u), "r"(packed[4 * q4]),
+                                 "r"(packed[4 * q4 + 1]), "r"(packed[4 * q4 + 2]), "r"(packed[4 * q4 + 3]) : "memory");
+                }
+            }
+            // S is read: the buffer may take the scores of tile j + 2; P is written: hand it to the MMA
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(s_empty + 8 * s); mbar_arrive(p_full); }
+            l_run = l_run * alpha + sum;
+            m_run = m_new;
+            alpha_pending = alpha;
+        }
+        if (ok && mbar_wait(pv_full, (uint32_t)(n_tiles - 1) & 1u, status, 3)) {
+            tc_fence_after();
+            // the two threads of a row add up their sums
+            exchange[half * 128 + r] = l_run;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(l_bar);
+            const bool both = mbar_wait(l_bar, 0, status, 3);
+            const float inv = both ? 1.f / (l_run + exchange[(half ^ 1) * 128 + r]) : 0.f;
+            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + q0 + r) * p.nq + head) * HD + half * HC;
+#pragma unroll
+            for (int c0 = 0; c0 < HC; c0 += 32) {
+                uint32_t v[32];
+                tmem_load32(lane_addr + PV_COL + (uint32_t)(half * HC + c0), v);
+                if (r < rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(fmaf(o[c0 + c], alpha_pending, __uint_as_float(v[c])) * inv, fmaf(o[c0 + c + 1], alpha_pending, __uint_as_float(v[c + 1])) * inv);
+                        w.y = pack_bf16(fmaf(o[c0 + c + 2], alpha_pending, __uint_as_float(v[c + 2])) * inv, fmaf(o[c0 + c + 3], alpha_pending, __uint_as_float(v[c + 3])) * inv);
+                        w.z = pack_bf16(fmaf(o[c0 + c + 4], alpha_pending, __uint_as_float(v[c + 4])) * inv, fmaf(o[c0 + c + 5], alpha_pending, __uint_as_float(v[c + 5])) * inv);
+                        w.w = pack_bf16(fmaf(o[c0 + c + 6], alpha_pending, __uint_as_float(v[c + 6])) * inv, fmaf(o[c0 + c + 7], alpha_pending, __uint_as_float(v[c + 7])) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*(volatile int*)status != 0) {                     // a wait gave up: let copies in flight land before the block leaves
+        const unsigned long long t0 = global_timer();
+        while (global_timer() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD>
+int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcAttnParams& p, int n_seqs,
+           int max_q_len, cudaStream_t stream) {
+    constexpr uint32_t HALVES = HD / 64;
+    const size_t smem = (size_t)HALVES * HALF_BYTES * 5 + 2 * HALF_BYTES + 1024 + 160 + 2 * 2 * 128 * 4 + 64;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "attention_prefill_tc: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    dim3 grid((max_q_len + BQ - 1) / BQ, p.nq, n_seqs);
+    launch_kernel(attention_prefill_tc_kernel<HD>, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p);
+    QT_CHECK_LAUNCH("attention_prefill_tc");
+    return QT_OK;
+}
+
+}  // namespace
+
+// q [n_tokens, nq, d] bfloat16; caches [n_pages, nkv, 64, d] bfloat16 (they already hold this step's keys); out like q.
+// `status` is a device int that stays 0 unless a wait inside the kernel ran out.
+extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, int n_tokens,
+                                       int n_pages, const int* block_table, int max_blocks, const int* seq_start,
+                                       const int* seq_past, int n_seqs, int max_q_len, int nq, int nkv, int d,
+                                       int page_tokens, int ring_tokens, int window, float scale, int* status, void* stream) {
+    if (n_seqs == 0 || max_q_len == 0) return QT_OK;
+    QT_REQUIRE(n_seqs > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill_tc: bad head counts nq=%d nkv=%d (B=%d)", nq, nkv, n_seqs);
+    QT_REQUIRE(d == 64 || d == 128, "attention_prefill_tc: head_dim=%d (this kernel takes 64 or 128)", d);
+    QT_REQUIRE(page_tokens == PAGE, "attention_prefill_tc: pages of %d tokens (this kernel walks pages of %d)", page_tokens, PAGE);
+    QT_REQUIRE(ring_tokens >= 0 && ring_tokens % PAGE == 0, "attention_prefill_tc: the ring of %d tokens is not a whole number of pages", ring_tokens);
+    QT_REQUIRE(ring_tokens == 0 || (window > 0 && ring_tokens >= window), "attention_prefill_tc: a ring of %d tokens cannot hold a window of %d", ring_tokens, window);
+    QT_REQUIRE(n_seqs <= 65535 && nq <= 65535 && max_blocks > 0 && n_pages > 0 && n_tokens > 0, "attention_prefill_tc: bad sizes");
+    QT_REQUIRE(status != nullptr, "attention_prefill_tc: a status word is required");
+    QT_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0) && ((uintptr_t)out % 16 == 0),
+               "attention_prefill_tc: operands must be 16-byte aligned");
+    CUtensorMap map_q, map_k, map_v;
+    int rc = tensor_map(&map_q, q, (uint64_t)n_tokens, (uint64_t)nq * d, BQ);
+    if (rc) return rc;
+    rc = tensor_map(&map_k, k_cache, (uint64_t)n_pages * nkv * PAGE, (uint64_t)d, PAGE);
+    if (rc) return rc;
+    rc = tensor_map(&map_v, v_cache, (uint64_t)n_pages * nkv * PAGE, (uint64_t)d, PAGE);
+    if (rc) return rc;
+    TcAttnParams p{(__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past, nq, nkv, ring_tokens, window, scale, status};
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64) return launch<64>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
+    return launch<128>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
+}
+
+QT_DEFINE_LAST_ERROR(attention_tc)

@@ -41,6 +41,10 @@ _SIGNATURES = {
         "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
     },
+    "attention_tc": {
+        "qt_attention_prefill_tc": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr],
+    },
     "gemm_simt": {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
@@ -255,12 +259,21 @@ def attention_mma_supported(q: torch.Tensor, page_tokens: int) -> bool:
     return q.dtype == torch.bfloat16 and q.shape[2] % 16 == 0 and q.shape[2] <= 128 and page_tokens == 64
 
 
-def _pick_attention(q: torch.Tensor, page_tokens: int, impl: str | None) -> str:
+def attention_tc_supported(q: torch.Tensor, page_tokens: int) -> bool:
+    """The tcgen05 prefill attention takes bfloat16, head size 64 or 128, pages of 64 tokens."""
+    return q.dtype == torch.bfloat16 and q.shape[2] in (64, 128) and page_tokens == 64
+
+
+def _pick_attention(q: torch.Tensor, page_tokens: int, impl: str | None, prefill: bool = False) -> str:
     if impl is None:
+        if prefill and attention_tc_supported(q, page_tokens):
+            return "tc"
         return "mma" if attention_mma_supported(q, page_tokens) else "generic"
+    if impl == "tc" and not (prefill and attention_tc_supported(q, page_tokens)):
+        raise KernelError(f"the tcgen05 attention kernel does not take {q.dtype}, head_dim={q.shape[2]}, pages of {page_tokens}")
     if impl == "mma" and not attention_mma_supported(q, page_tokens):
         raise KernelError(f"the tensor-core attention kernels do not take {q.dtype}, head_dim={q.shape[2]}, pages of {page_tokens}")
-    if impl not in ("mma", "generic"):
+    if impl not in ("tc", "mma", "generic"):
         raise KernelError(f"unknown attention implementation {impl!r}")
     return impl
 
@@ -270,14 +283,21 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                       num_kv_heads: int, page_tokens: int, ring_tokens: int, window: int | None, scale: float,
                       impl: str | None = None) -> None:
     """Causal attention of packed sequences over the cache (which already holds this step's keys).
-    ``impl`` forces the generic or the tensor-core kernel; by default the shape decides."""
+    ``impl`` forces a kernel ("tc": tcgen05, "mma": mma.sync, "generic"); by default the shape decides."""
     _, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
     n_seqs = seq_past.shape[0]
     _need(seq_start, "seq_start", torch.int32, (n_seqs + 1,))
     _need(seq_past, "seq_past", torch.int32)
     if block_table.shape[0] < n_seqs:
         raise KernelError("attention_prefill: block table has fewer rows than sequences")
-    if _pick_attention(q, page_tokens, impl) == "mma":
+    choice = _pick_attention(q, page_tokens, impl, prefill=True)
+    if choice == "tc":
+        _call("attention_tc", "qt_attention_prefill_tc", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), q.shape[0],
+              k_cache.shape[0], _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs,
+              int(max_q_len), num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale),
+              _ptr(_status_word(q.device)), _stream())
+        return
+    if choice == "mma":
         _call("attention_mma", "qt_attention_prefill_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
               _ptr(block_table), block_table.shape[1], _ptr(seq_start), _ptr(seq_past), n_seqs, int(max_q_len), num_heads,
               num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())

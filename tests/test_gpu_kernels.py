@@ -179,13 +179,16 @@ def test_gemm_float32_is_true_float32():
 
 
 # ----------------------------------------------------------------------------- attention
-def impls_for(dtype, d):
-    return ["generic", "mma"] if dtype == torch.bfloat16 and d % 16 == 0 and d <= 128 else ["generic"]
+def impls_for(dtype, d, prefill=False):
+    if dtype != torch.bfloat16 or d % 16 or d > 128:
+        return ["generic"]
+    return ["generic", "mma"] + (["tc"] if prefill and d in (64, 128) else [])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq, nkv, d, window, ring", [(6, 2, 80, None, 0), (4, 4, 16, 40, 128), (8, 1, 128, None, 0), (2, 1, 256, 100, 0),
-                                                      (3, 1, 48, 70, 192), (4, 2, 112, None, 0)])
+                                                      (3, 1, 48, 70, 192), (4, 2, 112, None, 0), (4, 2, 64, None, 0), (6, 3, 128, 90, 256),
+                                                      (2, 2, 64, 50, 192), (32, 8, 128, None, 0)])
 def test_attention_prefill(dtype, nq, nkv, d, window, ring):
     q_lens, past = [150, 1, 33, 64], [100, 0, 7, 64]
     if ring:
@@ -199,9 +202,10 @@ def test_attention_prefill(dtype, nq, nkv, d, window, ring):
     seq_start = torch.tensor([0, *torch.tensor(q_lens).cumsum(0).tolist()], dtype=torch.int32, device=DEV)
     seq_past = torch.tensor(past, dtype=torch.int32, device=DEV)
     scale = d ** -0.5
-    for impl in impls_for(dtype, d):
+    for impl in impls_for(dtype, d, prefill=True):
         out.fill_(float("nan"))
         kernels.attention_prefill(q, k_cache, v_cache, out, table, seq_start, seq_past, max(q_lens), nkv, PAGE, ring, window, scale, impl=impl)
+        kernels.check_status(DEV)
         start = 0
         for b, n in enumerate(q_lens):
             ref = attention_reference(q[start:start + n].float().cpu(), k[b], v[b], torch.arange(past[b], past[b] + n), scale, window)
@@ -249,7 +253,7 @@ def test_one_far_key_among_hundreds_wins(dtype, mode):
     q = query.to(dtype).to(DEV)
     out = torch.empty_like(q)
     expected = v[3].repeat_interleave(2, dim=0)[None]
-    for impl in impls_for(dtype, d):
+    for impl in impls_for(dtype, d, prefill=mode == "prefill"):
         out.fill_(float("nan"))
         if mode == "decode":
             kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
