@@ -3,10 +3,11 @@
 //
 //  * decode: one query token per sequence.  A block takes one kv head, up to 16 of its query
 //    heads (the MMA's 16 rows: the whole group shares one read of the keys and values) and a
-//    range of whole pages; cp.async streams each page's [64, d] key and value tiles through a
-//    three-stage ring in shared memory; each of the four warps owns 16 keys of a tile with its
-//    own online softmax, merged at the end.  Partial results of the splits go to float scratch
-//    and are merged by the combine kernel.
+//    range of keys.  Two kernels: in the one that serves the engine every warp walks a range of
+//    its own, 32 keys at a time through its own two-stage cp.async ring, with one online softmax
+//    per tile and no barrier until the warps of a block merge; in the older one the four warps
+//    of a block share each page's tile, 16 keys per warp.  Partial results of the blocks of a
+//    (sequence, kv head) go to float scratch and are merged by the combine kernel.
 //  * prefill: packed sequences with a past.  A block takes 64 query rows of one head (16 per
 //    warp) and walks the pages its rows can see, double-buffered.
 //
@@ -83,6 +84,47 @@ extern "C" int qt_attention_decode_mma(const void* q, const void* k_cache, const
         launch_kernel(attention_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, s, p);
     }
     QT_CHECK_LAUNCH("attention_decode_mma");
+    if (n_splits > 1) {
+        launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d);
+        QT_CHECK_LAUNCH("attention_combine_mma");
+    }
+    return QT_OK;
+}
+
+// The decode kernel that gives every warp a key range of its own: `n_splits` blocks of `warps` warps per
+// (sequence, kv head); partial results per block, merged by the combine kernel when n_splits > 1.
+extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
+                                      int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
+                                      int n_splits, int warps, float* part_acc, float* part_ml, void* stream) {
+    if (n_seqs == 0) return QT_OK;
+    int rc = check("attention_decode_ws", n_seqs, nq, nkv, d, page_tokens, ring_tokens, window);
+    if (rc) return rc;
+    QT_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode_ws: n_splits=%d", n_splits);
+    QT_REQUIRE(warps >= 1 && warps <= WS_MAX_WARPS, "attention_decode_ws: %d warps per block (1 to %d)", warps, WS_MAX_WARPS);
+    QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode_ws: split results need scratch memory");
+    QT_REQUIRE(scale > 0.f, "attention_decode_ws: the score scale must be positive (the row maximum is taken before scaling)");
+    MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
+                block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
+                n_splits, part_acc, part_ml, 2};
+    const int lds = d + PAD;
+    const size_t smem = 16 * (size_t)lds * 2 + (size_t)warps * 4 * WS_TILE * lds * 2;
+    const int group = nq / nkv;
+    dim3 grid(n_splits, nkv * ((group + 15) / 16), n_seqs), block(32 * warps);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t most = 16 * (128 + PAD) * 2 + (size_t)WS_MAX_WARPS * 4 * WS_TILE * (128 + PAD) * 2;
+#define QT_LAUNCH_WS(DMAX, EXACT)                                                                                        \
+    do {                                                                                                                 \
+        static bool ok = false;                                                                                          \
+        if (!ok) { rc = raise_smem(attention_decode_ws_kernel<DMAX, EXACT>, most, "attention_decode_ws"); if (rc) return rc; ok = true; } \
+        launch_kernel(attention_decode_ws_kernel<DMAX, EXACT>, grid, block, smem, s, p);                                  \
+    } while (0)
+    if (d == 128) QT_LAUNCH_WS(128, true);
+    else if (d == 64) QT_LAUNCH_WS(64, true);
+    else if (d < 64) QT_LAUNCH_WS(64, false);
+    else QT_LAUNCH_WS(128, false);
+#undef QT_LAUNCH_WS
+    QT_CHECK_LAUNCH("attention_decode_ws");
     if (n_splits > 1) {
         launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d);
         QT_CHECK_LAUNCH("attention_combine_mma");

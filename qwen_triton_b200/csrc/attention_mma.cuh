@@ -3,10 +3,11 @@
 //
 //  * decode: one query token per sequence.  A block takes one kv head, up to 16 of its query
 //    heads (the MMA's 16 rows: the whole group shares one read of the keys and values) and a
-//    range of whole pages; cp.async streams each page's [64, d] key and value tiles through a
-//    three-stage ring in shared memory; each of the four warps owns 16 keys of a tile with its
-//    own online softmax, merged at the end.  Partial results of the splits go to float scratch
-//    and are merged by the combine kernel.
+//    range of keys.  Two kernels: in the one that serves the engine every warp walks a range of
+//    its own, 32 keys at a time through its own two-stage cp.async ring, with one online softmax
+//    per tile and no barrier until the warps of a block merge; in the older one the four warps
+//    of a block share each page's tile, 16 keys per warp.  Partial results of the blocks of a
+//    (sequence, kv head) go to float scratch and are merged by the combine kernel.
 //  * prefill: packed sequences with a past.  A block takes 64 query rows of one head (16 per
 //    warp) and walks the pages its rows can see, double-buffered.
 //
@@ -299,6 +300,232 @@ __global__ void __launch_bounds__(128, 3) attention_decode_mma_kernel(const MmaP
             p.out[((size_t)seq * p.nq + head) * d + c] = __float2bfloat16_rn(a_all / l_all);
         } else {
             const size_t slot = ((size_t)seq * p.nq + head) * p.n_splits + split;
+            p.part_acc[slot * d + c] = a_all;
+            if (c == 0) { p.part_ml[slot * 2] = m_all * LN2; p.part_ml[slot * 2 + 1] = l_all; }   // natural-log domain for the combine kernel
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------- decode, one key range per warp
+// The same work cut differently: every warp of a block walks a key range of its own, 32 keys (half a page) at a
+// time, through a two-stage cp.async ring of its own, so that nothing in the loop waits for another warp.  A warp
+// owns whole tiles: one online softmax and one accumulator rescale per 32 keys (the kernel above spends them per
+// 16 keys in each of four warps), four independent QK^T accumulator chains, and no block barrier until the warps
+// of a block merge their results at the end.  gridDim.x * warps ranges per (sequence, kv head); the block writes
+// one partial result per gridDim.x.
+constexpr int WS_TILE = 32;
+constexpr int WS_MAX_WARPS = 6;
+
+// Copy of a [32, d] tile by one warp, 16 bytes per cp.async (see TileCopy).
+struct WarpTileCopy {
+    int d, lds, chunks, pieces;
+    bool linear;
+    uint32_t dst0, dst_step;
+    int src0, src_step;
+    int lane;
+
+    __device__ __forceinline__ WarpTileCopy(int d_, int lds_, int lane_) : d(d_), lds(lds_), lane(lane_) {
+        chunks = d >> 3;
+        pieces = WS_TILE * chunks;
+        linear = (32 % chunks) == 0;
+        const int r = lane / chunks, c8 = (lane % chunks) * 8, rows_per_round = 32 / chunks;
+        dst0 = (uint32_t)(r * lds + c8) * 2u;
+        dst_step = (uint32_t)(rows_per_round * lds) * 2u;
+        src0 = r * d + c8;
+        src_step = rows_per_round * d;
+    }
+    template <int DMAX, bool EXACT>
+    __device__ __forceinline__ void start(uint32_t tile_smem, const __nv_bfloat16* tile_global) const {
+        if (EXACT) {                                     // d == DMAX (64 or 128): a fixed number of pieces per lane
+            uint32_t dst = tile_smem + dst0;
+            const __nv_bfloat16* src = tile_global + src0;
+#pragma unroll
+            for (int i = 0; i < DMAX / 8; ++i, dst += dst_step, src += src_step) cp_async16(dst, src);
+        } else if (linear) {
+            uint32_t dst = tile_smem + dst0;
+            const __nv_bfloat16* src = tile_global + src0;
+            for (int i = lane; i < pieces; i += 32, dst += dst_step, src += src_step) cp_async16(dst, src);
+        } else {
+            for (int i = lane; i < pieces; i += 32) {
+                const int r = i / chunks, c8 = (i % chunks) * 8;
+                cp_async16(tile_smem + (uint32_t)(r * lds + c8) * 2u, tile_global + r * d + c8);
+            }
+        }
+    }
+};
+
+template <int DMAX, bool EXACT>
+__global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(const MmaParams p) {
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int d = EXACT ? DMAX : p.d, lds = d + PAD, dsteps = d >> 4;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int warps = blockDim.x >> 5;
+    const int group = p.nq / p.nkv;
+    const int chunks_per_kv = (group + 15) / 16;
+    const int kvh = blockIdx.y / chunks_per_kv;
+    const int h0 = (blockIdx.y % chunks_per_kv) * 16;
+    const int rows = min(16, group - h0);
+    const int head_base = kvh * group + h0;
+    const int seq = blockIdx.z, split = blockIdx.x;
+    const int stream = split * warps + warp, n_streams = gridDim.x * warps;
+
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [16][lds]
+    const uint32_t tile_bytes = (uint32_t)WS_TILE * lds * 2u;
+    const uint32_t q_bytes = 16u * lds * 2u;
+    const uint32_t ring0 = smem_u32(smem_raw) + q_bytes + (uint32_t)warp * 4u * tile_bytes;   // [stage][K tile, V tile]
+
+    const int len = p.seq_len[seq];
+    const int lo = p.window > 0 ? max(0, len - p.window) : 0;
+    const int first_tile = lo / WS_TILE, last_tile = (len - 1) / WS_TILE;
+    const int per_stream = (last_tile - first_tile + n_streams) / n_streams;
+    const int tile_begin = first_tile + stream * per_stream;
+    const int n_tiles = max(0, min(last_tile + 1, tile_begin + per_stream) - tile_begin);
+    const int* table = p.block_table + (size_t)seq * p.max_blocks;
+
+    const WarpTileCopy copy(d, lds, lane);
+    auto issue = [&](int tile) {
+        if (tile < n_tiles) {
+            const int t32 = tile_begin + tile;
+            const int page = cache_page(table, t32 >> 1, p.ring_tokens);
+            const size_t off = (((size_t)page * p.nkv + kvh) * PAGE + (t32 & 1) * WS_TILE) * d;
+            const uint32_t dst = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
+            copy.template start<DMAX, EXACT>(dst, p.k_cache + off);
+            copy.template start<DMAX, EXACT>(dst + tile_bytes, p.v_cache + off);
+        }
+        cp_async_commit();
+    };
+    // Keys and values of earlier positions do not depend on the kernel before this one (it writes only the new
+    // token's row, which lies in the last tile): a first tile that is not the last is requested before the wait.
+    const bool early = n_tiles > 0 && tile_begin < last_tile;
+    if (early) issue(0);
+    pdl_wait();
+    for (int i = tid; i < 16 * (d >> 3); i += blockDim.x) {                          // query rows, zero beyond the group
+        const int r = i / (d >> 3), c = i % (d >> 3);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)seq * p.nq + head_base + r) * d + c * 8);
+        *reinterpret_cast<uint4*>(q_s + r * lds + c * 8) = v;
+    }
+    if (!early) issue(0);
+    __syncthreads();
+    uint32_t qf[DMAX / 16][4];
+    load_q_frags<DMAX>(qf, smem_u32(q_s), lds, dsteps, lane);
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};          // m in the scaled base-2 domain
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    const float scale2 = p.scale * LOG2E;                            // positive (checked by the host)
+    const int mi = lane >> 3;
+    const uint32_t k_lane = (uint32_t)(((mi >> 1) * 8 + (lane & 7)) * lds + (mi & 1) * 8) * 2u;
+    const uint32_t v_lane = (uint32_t)(((mi & 1) * 8 + (lane & 7)) * lds + (mi >> 1) * 8) * 2u;
+    const uint32_t half_tile = (uint32_t)(16 * lds) * 2u;            // 16 keys further down
+
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        issue(tile + 1);                                             // into the stage that the tile before this one used
+        cp_async_wait<1>();
+        __syncwarp();
+        const uint32_t k_s = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes, v_s = k_s + tile_bytes;
+        const int pos0 = (tile_begin + tile) * WS_TILE;
+        float s[4][4] = {};
+#pragma unroll
+        for (int ks = 0; ks < DMAX / 16; ++ks) {
+            if (EXACT || ks < dsteps) {
+                uint32_t b0[4], b1[4];
+                ldmatrix_x4(b0, k_s + k_lane + (uint32_t)(ks * 32));
+                ldmatrix_x4(b1, k_s + k_lane + half_tile + (uint32_t)(ks * 32));
+                mma_bf16(s[0], qf[ks], b0[0], b0[1]);
+                mma_bf16(s[1], qf[ks], b0[2], b0[3]);
+                mma_bf16(s[2], qf[ks], b1[0], b1[1]);
+                mma_bf16(s[3], qf[ks], b1[2], b1[3]);
+            }
+        }
+        if (pos0 < lo || pos0 + WS_TILE > len) {                     // a tile at an edge of what the query sees
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int pos = pos0 + nt * 8 + 2 * t + (e & 1);
+                    if (pos < lo || pos >= len) s[nt][e] = -INFINITY;
+                }
+        }
+        float alpha[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+            mx = fmaxf(mx, fmaxf(fmaxf(s[2][2 * r], s[2][2 * r + 1]), fmaxf(s[3][2 * r], s[3][2 * r + 1])));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[r], mx * scale2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            alpha[r] = fast_exp2(m[r] - m_use);
+            m[r] = m_new;
+            float sum = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                s[nt][2 * r] = fast_exp2(fmaf(s[nt][2 * r], scale2, -m_use));
+                s[nt][2 * r + 1] = fast_exp2(fmaf(s[nt][2 * r + 1], scale2, -m_use));
+                sum += s[nt][2 * r] + s[nt][2 * r + 1];
+            }
+            l[r] = l[r] * alpha[r] + sum;                            // this thread's share of the row sum
+        }
+        const uint32_t pa0[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                                 pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+        const uint32_t pa1[4] = {pack_bf16(s[2][0], s[2][1]), pack_bf16(s[2][2], s[2][3]),
+                                 pack_bf16(s[3][0], s[3][1]), pack_bf16(s[3][2], s[3][3])};
+#pragma unroll
+        for (int nt2 = 0; nt2 < DMAX / 16; ++nt2) {
+            if (EXACT || nt2 < dsteps) {
+                o[2 * nt2][0] *= alpha[0]; o[2 * nt2][1] *= alpha[0]; o[2 * nt2][2] *= alpha[1]; o[2 * nt2][3] *= alpha[1];
+                o[2 * nt2 + 1][0] *= alpha[0]; o[2 * nt2 + 1][1] *= alpha[0]; o[2 * nt2 + 1][2] *= alpha[1]; o[2 * nt2 + 1][3] *= alpha[1];
+                uint32_t b0[4], b1[4];
+                ldmatrix_x4_trans(b0, v_s + v_lane + (uint32_t)(nt2 * 32));
+                ldmatrix_x4_trans(b1, v_s + v_lane + half_tile + (uint32_t)(nt2 * 32));
+                mma_bf16(o[2 * nt2], pa0, b0[0], b0[1]);
+                mma_bf16(o[2 * nt2 + 1], pa0, b0[2], b0[3]);
+                mma_bf16(o[2 * nt2], pa1, b1[0], b1[1]);
+                mma_bf16(o[2 * nt2 + 1], pa1, b1[2], b1[3]);
+            }
+        }
+        __syncwarp();                                                // the stage may be overwritten by the next issue
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the warps through shared memory (the rings are free now)
+    float* red_o = reinterpret_cast<float*>(smem_raw + q_bytes);     // [warps][16][d]
+    float* red_ml = red_o + warps * 16 * d;                          // [warps][16][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        if (t == 0) { red_ml[(warp * 16 + g + 8 * r) * 2] = m[r]; red_ml[(warp * 16 + g + 8 * r) * 2 + 1] = l[r]; }
+    }
+#pragma unroll
+    for (int nt = 0; nt < DMAX / 8; ++nt) {
+        if (EXACT || nt < 2 * dsteps) {
+            const int c = nt * 8 + 2 * t;
+            *reinterpret_cast<float2*>(red_o + (warp * 16 + g) * d + c) = make_float2(o[nt][0], o[nt][1]);
+            *reinterpret_cast<float2*>(red_o + (warp * 16 + g + 8) * d + c) = make_float2(o[nt][2], o[nt][3]);
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < rows * d; i += blockDim.x) {
+        const int r = i / d, c = i % d;
+        float m_all = -INFINITY;
+        for (int w = 0; w < warps; ++w) m_all = fmaxf(m_all, red_ml[(w * 16 + r) * 2]);
+        float l_all = 0.f, a_all = 0.f;
+        for (int w = 0; w < warps; ++w) {
+            const float mw = red_ml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - m_all);
+            l_all += red_ml[(w * 16 + r) * 2 + 1] * f;
+            a_all += red_o[(w * 16 + r) * d + c] * f;
+        }
+        const int head = head_base + r;
+        if (gridDim.x == 1) {
+            p.out[((size_t)seq * p.nq + head) * d + c] = __float2bfloat16_rn(a_all / l_all);
+        } else {
+            const size_t slot = ((size_t)seq * p.nq + head) * gridDim.x + split;
             p.part_acc[slot * d + c] = a_all;
             if (c == 0) { p.part_ml[slot * 2] = m_all * LN2; p.part_ml[slot * 2 + 1] = l_all; }   // natural-log domain for the combine kernel
         }

@@ -145,7 +145,10 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     const bool aligned = hidden % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
                          ((uintptr_t)weight % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && split_stride % 4 == 0));
     if (aligned && hidden <= 4 * NORM_CACHE * 1024) {
-        int vthreads = ((hidden / 4 + 31) / 32) * 32;
+        // few rows (decode): one chunk per thread, shortest critical path; many rows (prefill): up to NORM_CACHE
+        // independent chunks per thread in smaller blocks, which keeps more loads in flight and more blocks resident
+        const int per_thread = n_rows >= 256 ? NORM_CACHE : 1;
+        int vthreads = ((hidden / 4 + 32 * per_thread - 1) / (32 * per_thread)) * 32;
         if (vthreads > 1024) vthreads = 1024;
         if (vthreads < 64) vthreads = 64;
 #define QT_LAUNCH_NORM_VEC(TD, TO)                                                                                      \
@@ -266,6 +269,143 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     }
 }
 
+// Fast form for many tokens: every dimension rotates (rotary_dim == d) and half a head is IT * 32 * E elements, so
+// a lane holds the E-element pieces (j, j + d/2) of a rotation pair in registers and nothing passes through shared
+// memory.  One warp takes HEADS_PER_WARP consecutive heads of one token, so that position, page and cos/sin are
+// looked up once.  Same arithmetic as the kernel above: float norm, weight, then rotation.
+constexpr int HEADS_PER_WARP = 4;
+
+template <int E> struct Piece;
+template <> struct Piece<1> { float v[1]; };
+template <> struct Piece<2> { float v[2]; };
+
+template <int E> __device__ __forceinline__ Piece<E> load_piece(const float* p) {
+    Piece<E> r;
+    if (E == 2) { const float2 t = *reinterpret_cast<const float2*>(p); r.v[0] = t.x; r.v[E - 1] = t.y; }
+    else r.v[0] = p[0];
+    return r;
+}
+template <int E> __device__ __forceinline__ Piece<E> load_piece(const __nv_bfloat16* p) {
+    Piece<E> r;
+    if (E == 2) { const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p); r.v[0] = __low2float(t); r.v[E - 1] = __high2float(t); }
+    else r.v[0] = __bfloat162float(p[0]);
+    return r;
+}
+template <int E> __device__ __forceinline__ void store_piece(float* p, const Piece<E>& r) {
+    if (E == 2) *reinterpret_cast<float2*>(p) = make_float2(r.v[0], r.v[E - 1]);
+    else p[0] = r.v[0];
+}
+template <int E> __device__ __forceinline__ void store_piece(__nv_bfloat16* p, const Piece<E>& r) {
+    if (E == 2) *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(r.v[0], r.v[E - 1]);
+    else p[0] = __float2bfloat16_rn(r.v[0]);
+}
+
+// blockIdx.x is the token, blockIdx.y * 4 + warp the run of heads.
+template <typename TI, typename TO, int E, int IT>
+__global__ void __launch_bounds__(128) qk_norm_rope_pairs_kernel(const QkvParams p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads_total = p.nq + (p.kv_in_proj ? 2 * p.nkv : 0);
+    const int t = blockIdx.x;
+    const int head0 = (blockIdx.y * 4 + warp) * HEADS_PER_WARP;
+    if (head0 >= heads_total || (head0 >= p.nq && !p.write_kv)) return;
+    const int half = p.d >> 1;
+    const TI* in = (const TI*)p.qkv + ((size_t)t * heads_total + head0) * p.d;
+
+    // every load of the warp's heads is issued before the first store (the compiler cannot move loads across the
+    // stores itself: it does not know that the projection and the outputs are different memory)
+    Piece<E> lo[HEADS_PER_WARP][IT], hi[HEADS_PER_WARP][IT];
+#pragma unroll
+    for (int hh = 0; hh < HEADS_PER_WARP; ++hh) {
+        const TI* src = in + (head0 + hh < heads_total ? hh : 0) * p.d;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int j = (it * 32 + lane) * E;
+            lo[hh][it] = load_piece<E>(src + j);
+            hi[hh][it] = load_piece<E>(src + half + j);
+        }
+    }
+    if (p.n_splits > 1) {
+        for (int s = 1; s < p.n_splits; ++s) {
+#pragma unroll
+            for (int hh = 0; hh < HEADS_PER_WARP; ++hh) {
+                const TI* src = in + (head0 + hh < heads_total ? hh : 0) * p.d + (size_t)s * p.split_stride;
+#pragma unroll
+                for (int it = 0; it < IT; ++it) {
+                    const int j = (it * 32 + lane) * E;
+                    const Piece<E> dl = load_piece<E>(src + j), dh = load_piece<E>(src + half + j);
+#pragma unroll
+                    for (int e = 0; e < E; ++e) { lo[hh][it].v[e] += dl.v[e]; hi[hh][it].v[e] += dh.v[e]; }
+                }
+            }
+        }
+    }
+    // what all heads of the token share: position, cos and sin, the cache page, the norm weights
+    const int pos = p.token_pos[t];
+    const float* cs = p.cos_sin + (size_t)(pos < p.max_pos ? pos : p.max_pos - 1) * p.d;
+    Piece<E> c[IT], sn[IT], wq_lo[IT], wq_hi[IT], wk_lo[IT], wk_hi[IT];
+#pragma unroll
+    for (int it = 0; it < IT; ++it) {
+        const int j = (it * 32 + lane) * E;
+        c[it] = load_piece<E>(cs + j);
+        sn[it] = load_piece<E>(cs + half + j);
+        if (p.q_weight) { wq_lo[it] = load_piece<E>(p.q_weight + j); wq_hi[it] = load_piece<E>(p.q_weight + half + j); }
+        if (p.k_weight) { wk_lo[it] = load_piece<E>(p.k_weight + j); wk_hi[it] = load_piece<E>(p.k_weight + half + j); }
+    }
+    size_t cache_row = 0;    // element offset of (page, kv head 0, token) in the caches
+    if (p.write_kv && head0 + HEADS_PER_WARP > p.nq) {
+        const int slot_pos = p.ring_tokens > 0 ? pos % p.ring_tokens : pos;
+        const int page = p.block_table[(size_t)p.token_seq[t] * p.max_blocks + slot_pos / p.page_tokens];
+        cache_row = ((size_t)page * p.nkv * p.page_tokens + (slot_pos % p.page_tokens)) * (size_t)p.d;
+    }
+    const size_t head_stride = (size_t)p.page_tokens * p.d;
+    const float inv_d = 1.f / (float)p.d;
+#pragma unroll
+    for (int hh = 0; hh < HEADS_PER_WARP; ++hh) {
+        const int head = head0 + hh;
+        if (head >= heads_total) break;
+        const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+        if (!is_q && !p.write_kv) break;
+        TO* dst;
+        if (is_q) dst = (TO*)p.q_out + ((size_t)t * p.nq + head) * p.d;
+        else if (is_k) dst = (TO*)p.k_cache + cache_row + (size_t)(head - p.nq) * head_stride;
+        else dst = (TO*)p.v_cache + cache_row + (size_t)(head - p.nq - p.nkv) * head_stride;
+        const bool normed = is_q ? p.q_weight != nullptr : (is_k && p.k_weight != nullptr);
+        float inv = 1.f;
+        if (normed) {
+            float sq = 0.f;
+#pragma unroll
+            for (int it = 0; it < IT; ++it)
+#pragma unroll
+                for (int e = 0; e < E; ++e) sq += lo[hh][it].v[e] * lo[hh][it].v[e] + hi[hh][it].v[e] * hi[hh][it].v[e];
+            inv = rsqrtf(warp_sum(sq) * inv_d + p.eps);
+        }
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int j = (it * 32 + lane) * E;
+            Piece<E> a = lo[hh][it], b = hi[hh][it];
+            if (normed) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    a.v[e] = a.v[e] * inv * (is_q ? wq_lo[it].v[e] : wk_lo[it].v[e]);
+                    b.v[e] = b.v[e] * inv * (is_q ? wq_hi[it].v[e] : wk_hi[it].v[e]);
+                }
+            }
+            if (is_q || is_k) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const float ya = a.v[e] * c[it].v[e] - b.v[e] * sn[it].v[e];
+                    const float yb = b.v[e] * c[it].v[e] + a.v[e] * sn[it].v[e];
+                    a.v[e] = ya; b.v[e] = yb;
+                }
+            }
+            store_piece<E>(dst + j, a);
+            store_piece<E>(dst + half + j, b);
+        }
+    }
+}
+
 extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits, long long split_stride, void* q_out,
                                      void* k_cache, void* v_cache, int out_dtype, const int* token_seq,
                                      const int* token_pos, const int* block_table, int max_blocks,
@@ -289,6 +429,32 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     // 16-byte loads and stores need head_dim % 8 == 0 (bfloat16 rows of the cache and of q) and aligned bases
     const bool vec = d % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
                      (!write_kv || (((uintptr_t)k_cache % 16 == 0) && ((uintptr_t)v_cache % 16 == 0)));
+    // the register form: all dimensions rotate, half a head is one or two rounds of 32 or 64 elements, enough tokens
+    // to fill the machine with a few heads per warp
+    const int half = d / 2;
+    int pe = 0, pit = 0;
+    if (rotary_dim == d && half % 64 == 0 && half / 64 <= 2) { pe = 2; pit = half / 64; }
+    else if (rotary_dim == d && half == 32) { pe = 1; pit = 1; }
+    const bool pair_aligned = split_stride % 2 == 0 && ((uintptr_t)qkv % 8 == 0) && ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)cos_sin % 8 == 0) &&
+                              (!q_weight || (uintptr_t)q_weight % 8 == 0) && (!k_weight || (uintptr_t)k_weight % 8 == 0) &&
+                              (!write_kv || (((uintptr_t)k_cache % 8 == 0) && ((uintptr_t)v_cache % 8 == 0)));
+    if (pe && pair_aligned && n_tokens >= 256 && nq + 2 * nkv <= 65535 * 16 && (in_dtype == QT_F32 || in_dtype == QT_BF16) && out_dtype == QT_BF16) {
+        const int heads_total = nq + (kv_in_proj ? 2 * nkv : 0);
+        const dim3 pgrid((unsigned)n_tokens, (unsigned)((heads_total + warps * HEADS_PER_WARP - 1) / (warps * HEADS_PER_WARP)));
+#define QT_LAUNCH_PAIRS(TI, E, IT) launch_kernel(qk_norm_rope_pairs_kernel<TI, __nv_bfloat16, E, IT>, pgrid, dim3(warps * 32), 0, s, p)
+        if (in_dtype == QT_BF16) {
+            if (pe == 2 && pit == 1) QT_LAUNCH_PAIRS(__nv_bfloat16, 2, 1);
+            else if (pe == 2) QT_LAUNCH_PAIRS(__nv_bfloat16, 2, 2);
+            else QT_LAUNCH_PAIRS(__nv_bfloat16, 1, 1);
+        } else {
+            if (pe == 2 && pit == 1) QT_LAUNCH_PAIRS(float, 2, 1);
+            else if (pe == 2) QT_LAUNCH_PAIRS(float, 2, 2);
+            else QT_LAUNCH_PAIRS(float, 1, 1);
+        }
+#undef QT_LAUNCH_PAIRS
+        QT_CHECK_LAUNCH("qk_norm_rope_write");
+        return QT_OK;
+    }
 #define QT_LAUNCH_QKV(TI, TO)                                                                    \
     do {                                                                                         \
         if (vec) launch_kernel(qk_norm_rope_write_kernel<TI, TO, true>, dim3(grid), dim3(warps * 32), smem, s, p);      \
@@ -321,27 +487,63 @@ __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size
     }
 }
 
-// Four elements per thread with 8- or 16-byte loads and stores (widths that are multiples of 4, aligned bases).
-template <typename TI, typename TO>
+// Eight elements per thread with 16- or 32-byte loads and stores (widths that are multiples of 8, aligned bases).
+// blockIdx.x is the token, blockIdx.y a run of chunks of its row.
+struct Float8 { float4 a, b; };
+__device__ __forceinline__ Float8 load8(const float* p) { return {load4(p), load4(p + 4)}; }
+__device__ __forceinline__ Float8 load8(const __nv_bfloat16* p) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    return {make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1])),
+            make_float4(__low2float(h[2]), __high2float(h[2]), __low2float(h[3]), __high2float(h[3]))};
+}
+__device__ __forceinline__ void store8(float* p, const Float8& v) { store4(p, v.a); store4(p + 4, v.b); }
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const Float8& v) {
+    __nv_bfloat162 h[4] = {__floats2bfloat162_rn(v.a.x, v.a.y), __floats2bfloat162_rn(v.a.z, v.a.w),
+                           __floats2bfloat162_rn(v.b.x, v.b.y), __floats2bfloat162_rn(v.b.z, v.b.w)};
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(h);
+}
+__device__ __forceinline__ void add4(float4& x, const float4& y) { x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
+// silu(g) * u.  For a float result the exponential and the division are the library's; for a bfloat16 result
+// (8 bits of mantissa) the hardware approximations (2 ulp of float) are used: with the exact forms the kernel was
+// bound by instruction issue, not by memory.
+template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+template <typename TO> __device__ __forceinline__ float4 silu_mul4(const float4& g, const float4& u) {
+    return make_float4(silu_mul<TO>(g.x, u.x), silu_mul<TO>(g.y, u.y), silu_mul<TO>(g.z, u.z), silu_mul<TO>(g.w, u.w));
+}
+
+// PT chunks per thread, all loads issued before the first store.
+template <typename TI, typename TO, int PT>
 __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                                  long long total4, int inter) {
+                                  int inter) {
     pdl_launch_dependents();
     pdl_wait();
-    const int chunks = inter >> 2;
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total4;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const long long t = idx / chunks;
-        const int i = (int)(idx % chunks) * 4;
-        const TI* gp = gate_up + (size_t)t * 2 * inter + i;
-        float4 g = load4(gp), u = load4(gp + inter);
-#pragma unroll 4
-        for (int s = 1; s < n_splits; ++s) {
-            const float4 dg = load4(gp + (size_t)s * split_stride), du = load4(gp + inter + (size_t)s * split_stride);
-            g.x += dg.x; g.y += dg.y; g.z += dg.z; g.w += dg.w;
-            u.x += du.x; u.y += du.y; u.z += du.z; u.w += du.w;
+    const int chunks = inter >> 3;
+    const TI* row = gate_up + (size_t)blockIdx.x * 2 * inter;
+    TO* orow = out + (size_t)blockIdx.x * inter;
+    for (int c0 = blockIdx.y * blockDim.x * PT + threadIdx.x; c0 < chunks; c0 += gridDim.y * blockDim.x * PT) {
+        Float8 g[PT], u[PT];
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+            const int c = c0 + i * blockDim.x;
+            if (c < chunks) { g[i] = load8(row + 8 * c); u[i] = load8(row + 8 * c + inter); }
         }
-        store4(out + (size_t)t * inter + i, make_float4(g.x / (1.f + expf(-g.x)) * u.x, g.y / (1.f + expf(-g.y)) * u.y,
-                                                        g.z / (1.f + expf(-g.z)) * u.z, g.w / (1.f + expf(-g.w)) * u.w));
+        for (int s = 1; s < n_splits; ++s) {
+#pragma unroll
+            for (int i = 0; i < PT; ++i) {
+                const int c = c0 + i * blockDim.x;
+                if (c < chunks) {
+                    const Float8 dg = load8(row + 8 * c + (size_t)s * split_stride), du = load8(row + 8 * c + inter + (size_t)s * split_stride);
+                    add4(g[i].a, dg.a); add4(g[i].b, dg.b); add4(u[i].a, du.a); add4(u[i].b, du.b);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PT; ++i) {
+            const int c = c0 + i * blockDim.x;
+            if (c < chunks) store8(orow + 8 * c, Float8{silu_mul4<TO>(g[i].a, u[i].a), silu_mul4<TO>(g[i].b, u[i].b)});
+        }
     }
 }
 
@@ -352,16 +554,21 @@ extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long l
     const long long total = (long long)n_tokens * inter;
     const int threads = 256;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = inter % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    const long long work = vec ? total / 4 : total;
-    long long blocks = (work + threads - 1) / threads;
+    const bool vec = inter % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    long long blocks = (total + threads - 1) / threads;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
+    // few tokens (decode): one chunk per thread, most blocks; many tokens (prefill): two chunks per thread
+    const int per_thread = n_tokens >= 256 ? 2 : 1;
+    unsigned per_row = (unsigned)((inter / 8 + threads * per_thread - 1) / (threads * per_thread));
+    if (per_row > 65535u) per_row = 65535u;
 #define QT_LAUNCH_SWIGLU(TI, TO)                                                                                              \
     do {                                                                                                                      \
-        if (vec) launch_kernel(swiglu_vec_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up,    \
-                               n_splits, (size_t)split_stride, (TO*)out, work, inter);                                        \
+        if (vec && per_thread == 2) launch_kernel(swiglu_vec_kernel<TI, TO, 2>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s, \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter);                          \
+        else if (vec) launch_kernel(swiglu_vec_kernel<TI, TO, 1>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s,     \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter);                          \
         else launch_kernel(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up, n_splits,  \
-                           (size_t)split_stride, (TO*)out, work, inter);                                                      \
+                           (size_t)split_stride, (TO*)out, total, inter);                                                     \
     } while (0)
     if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_SWIGLU(float, float);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_SWIGLU(float, __nv_bfloat16);

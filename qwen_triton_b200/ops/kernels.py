@@ -38,6 +38,8 @@ _SIGNATURES = {
     "attention_mma": {
         "qt_attention_decode_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr],
+        "qt_attention_decode_ws": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                   _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
         "qt_attention_prefill_mma": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr],
     },
@@ -307,14 +309,21 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
           num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
 
 
+DECODE_WARPS_MAX = 6     # warps per block of the one-range-per-warp decode kernel
+
+
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                      block_table: torch.Tensor, seq_len: torch.Tensor, num_kv_heads: int, page_tokens: int,
                      ring_tokens: int, window: int | None, scale: float, n_splits: int,
-                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None) -> None:
+                     part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, impl: str | None = None,
+                     warps: int = 1) -> None:
     """One query token per sequence; ``seq_len`` counts the keys it sees (its own included).
 
     With ``n_splits`` > 1 the keys of each sequence are cut into that many ranges whose partial
     results pass through ``part_acc`` (float, >= B nq splits d) and ``part_ml`` (float, >= B nq splits 2).
+    The tensor-core kernels are "ws" (every warp of a block walks a range of its own: n_splits * warps
+    ranges, n_splits partial results; the default where it applies) and "mma" (the four warps of a block
+    share each tile); "generic" takes every element type and head size.
     """
     n_seqs, num_heads, head_dim = _check_attention(q, k_cache, v_cache, out, block_table, num_kv_heads, page_tokens)
     _need(seq_len, "seq_len", torch.int32, (n_seqs,))
@@ -323,16 +332,21 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         _need(part_ml, "part_ml", torch.float32)
         if part_acc.numel() < n_seqs * num_heads * n_splits * head_dim or part_ml.numel() < n_seqs * num_heads * n_splits * 2:
             raise KernelError("attention_decode: scratch is too small for this batch and split count")
-    if _pick_attention(q, page_tokens, impl) == "mma":
-        _call("attention_mma", "qt_attention_decode_mma", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out),
-              _ptr(block_table), block_table.shape[1], _ptr(seq_len), n_seqs, num_heads, num_kv_heads, head_dim,
-              page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits), _ptr(part_acc), _ptr(part_ml),
-              _stream(), launches=2 if n_splits > 1 else 1)
-        return
-    _call("attention", "qt_attention_decode", _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q, "q"),
-          _ptr(block_table), block_table.shape[1], _ptr(seq_len), n_seqs, num_heads, num_kv_heads, head_dim,
-          page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits), _ptr(part_acc), _ptr(part_ml),
-          _stream(), launches=2 if n_splits > 1 else 1)
+    if impl == "ws" and not attention_mma_supported(q, page_tokens):
+        raise KernelError(f"the tensor-core attention kernels do not take {q.dtype}, head_dim={q.shape[2]}, pages of {page_tokens}")
+    picked = "ws" if impl == "ws" else _pick_attention(q, page_tokens, impl)
+    if picked == "mma" and impl is None:
+        picked = "ws"
+    common = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(seq_len),
+              n_seqs, num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits))
+    launches = 2 if n_splits > 1 else 1
+    if picked == "ws":
+        _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
+    elif picked == "mma":
+        _call("attention_mma", "qt_attention_decode_mma", *common, _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
+    else:
+        _call("attention", "qt_attention_decode", *common[:4], _code(q, "q"), *common[4:], _ptr(part_acc), _ptr(part_ml),
+              _stream(), launches=launches)
 
 
 # ----------------------------------------------------------------------------- matrix product

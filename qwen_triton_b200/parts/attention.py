@@ -17,7 +17,8 @@ from ..weights.tensors import TensorSpec
 from .base import KVRequest, Runtime, part_class, register_mixer, to_device
 from .linear import Linear
 
-_DECODE_TARGET_BLOCKS = 3 * 148     # blocks of the one-token kernel that are resident at once (three per SM)
+_SM_COUNT = 148
+_DECODE_TARGET_BLOCKS = 3 * _SM_COUNT     # blocks of the generic one-token kernel that are resident at once (three per SM)
 _MAX_SPLIT_PAIRS = 640              # (sequence, split) pairs the scratch holds
 _MIN_KEYS_PER_SPLIT = 128
 
@@ -95,24 +96,37 @@ class Attention:
         return KVRequest(self.nkv, self.d, self.window)
 
     # ------------------------------------------------------------------ run
-    def _splits(self, ctx) -> int:
-        """Ranges the keys of each sequence are cut into for a one-token step: the count whose blocks fill
-        whole waves of the SMs (three blocks of the tensor-core kernel fit an SM) nearly as well as the best
-        count does, the smallest such; at least two pages per range and within what the scratch holds."""
+    def _splits(self, ctx, cache) -> tuple[int, int]:
+        """How a one-token step cuts the keys of each sequence: (blocks per sequence and kv head, warps per block).
+
+        The tensor-core kernel gives every warp a key range of its own.  Measured on the B200: with few
+        (sequence, kv head) pairs, about one block of four warps per SM and as few partial results as that
+        allows; with blocks for two per SM, three warps each and no cut at all.  Every range keeps at least
+        two tiles of 32 keys.  The generic kernel (other element types and head sizes) takes one range per
+        block: the count whose blocks fill whole waves of three blocks per SM nearly as well as the best one.
+        """
         span = ctx.max_context if not self.window else min(ctx.max_context, self.window)
         group = self.nq // self.nkv
-        if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128:
-            heads_per_block = 16                                 # the tensor-core kernel takes a group of up to 16 heads
-        else:
-            heads_per_block = 8 if group > 4 else max(1, group)
+        most = max(1, min(_MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
+        if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
+            pairs = ctx.n_seqs * self.nkv * math.ceil(group / 16)
+            tiles = math.ceil(span / 32)
+            splits = max(1, min(_SM_COUNT // pairs, most))
+            warps = 3 if pairs * splits >= 3 * _SM_COUNT else 4
+            while splits > 1 and splits * warps * 2 > tiles:
+                splits -= 1
+            while warps > 1 and splits * warps * 2 > tiles:
+                warps -= 1
+            return splits, warps
+        heads_per_block = 8 if group > 4 else max(1, group)
         blocks = ctx.n_seqs * self.nkv * math.ceil(group / heads_per_block)
-        most = max(1, min(span // _MIN_KEYS_PER_SPLIT, _MAX_SPLIT_PAIRS // ctx.n_seqs, 32))
+        most = max(1, min(span // _MIN_KEYS_PER_SPLIT, most))
         fills = []
         for splits in range(1, most + 1):
             total = blocks * splits
             fills.append(total / (math.ceil(total / _DECODE_TARGET_BLOCKS) * _DECODE_TARGET_BLOCKS))
         enough = max(fills) - 0.13
-        return next(splits for splits, fill in enumerate(fills, start=1) if fill >= enough)
+        return next(splits for splits, fill in enumerate(fills, start=1) if fill >= enough), 1
 
     def forward(self, x: torch.Tensor, ctx, cache) -> GemmOut:
         tokens = x.shape[0]
@@ -127,11 +141,11 @@ class Attention:
             table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
             cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv)
         if ctx.is_decode:
-            n_splits = self._splits(ctx)
+            n_splits, warps = self._splits(ctx, cache)
             kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,
                                      cache.ring_tokens, self.window, self.scale, n_splits,
                                      ws.view("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.d),
-                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2))
+                                     ws.view("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2), warps=warps)
         else:
             kernels.attention_prefill(q, cache.k, cache.v, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len,
                                       self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale)

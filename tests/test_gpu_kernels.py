@@ -107,10 +107,14 @@ def test_add_rmsnorm(dtype, hidden, splits):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq, nkv, d, rotary, ring, splits", [(3, 3, 80, 40, 0, 1), (8, 2, 16, 16, 128, 2), (5, 1, 128, 128, 0, 1)])
-def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits):
+@pytest.mark.parametrize("nq, nkv, d, rotary, ring, splits, lengths", [
+    (3, 3, 80, 40, 0, 1, [70, 3, 100]), (8, 2, 16, 16, 128, 2, [70, 3, 100]), (5, 1, 128, 128, 0, 1, [70, 3, 100]),
+    # 256 tokens and more with every dimension rotating: the kernel that keeps rotation pairs in registers
+    (5, 2, 128, 128, 0, 1, [200, 3, 150]), (3, 1, 64, 64, 0, 2, [200, 3, 150]), (2, 2, 256, 256, 512, 1, [200, 3, 150]),
+    (7, 7, 128, 128, 0, 3, [190, 1, 99])])
+def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits, lengths):
     import plain_qwen3 as plain
-    lengths, past = [70, 3, 100], [130, 0, 20]          # tokens in this step and tokens before it, per sequence
+    past = [130, 0, 20]                                  # tokens before this step, per sequence; `lengths` are this step's
     tokens = sum(lengths)
     eps = 1e-5
     in_dtype = torch.float32 if splits > 1 else dtype
@@ -145,8 +149,8 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_swiglu(dtype):
-    tokens, inter = 5, 336
+@pytest.mark.parametrize("tokens, inter", [(5, 336), (3, 301), (300, 2056)])     # vector form, scalar form, several blocks a row
+def test_swiglu(dtype, tokens, inter):
     for splits in (1, 3):
         in_dtype = torch.float32 if splits > 1 else dtype
         gate_up = rand(splits, tokens, 2 * inter, seed=9, scale=2.0, dtype=in_dtype)
@@ -182,7 +186,7 @@ def test_gemm_float32_is_true_float32():
 def impls_for(dtype, d, prefill=False):
     if dtype != torch.bfloat16 or d % 16 or d > 128:
         return ["generic"]
-    return ["generic", "mma"] + (["tc"] if prefill and d in (64, 128) else [])
+    return ["generic", "mma"] + ((["tc"] if d in (64, 128) else []) if prefill else ["ws"])
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -228,12 +232,14 @@ def test_attention_decode(dtype, nq, nkv, d, window, ring, splits):
     part_acc = torch.full((len(lengths) * nq * splits * d,), float("nan"), device=DEV)
     part_ml = torch.full((len(lengths) * nq * splits * 2,), float("nan"), device=DEV)
     scale = d ** -0.5
+    refs = [attention_reference(q[b:b + 1].float().cpu(), k[b], v[b], torch.tensor([n - 1]), scale, window) for b, n in enumerate(lengths)]
     for impl in impls_for(dtype, d):
-        out.fill_(float("nan"))
-        kernels.attention_decode(q, k_cache, v_cache, out, table, seq_len, nkv, PAGE, ring, window, scale, splits, part_acc, part_ml, impl=impl)
-        for b, n in enumerate(lengths):
-            ref = attention_reference(q[b:b + 1].float().cpu(), k[b], v[b], torch.tensor([n - 1]), scale, window)
-            close(out[b:b + 1], ref, dtype, f"{impl}, sequence {b}")
+        for warps in ((1, 3, 6) if impl == "ws" else (1,)):      # "ws": splits * warps key ranges
+            out.fill_(float("nan"))
+            kernels.attention_decode(q, k_cache, v_cache, out, table, seq_len, nkv, PAGE, ring, window, scale, splits, part_acc, part_ml,
+                                     impl=impl, warps=warps)
+            for b in range(len(lengths)):
+                close(out[b:b + 1], refs[b], dtype, f"{impl} with {warps} warps, sequence {b}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -257,7 +263,8 @@ def test_one_far_key_among_hundreds_wins(dtype, mode):
         out.fill_(float("nan"))
         if mode == "decode":
             kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
-                                     None, 1.0, 4, torch.empty(nq * 4 * d, device=DEV), torch.empty(nq * 4 * 2, device=DEV), impl=impl)
+                                     None, 1.0, 4, torch.empty(nq * 4 * d, device=DEV), torch.empty(nq * 4 * 2, device=DEV), impl=impl,
+                                     warps=3 if impl == "ws" else 1)
         else:
             kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
                                       torch.tensor([n - 1], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, None, 1.0, impl=impl)
@@ -283,11 +290,12 @@ def test_window_edge(dtype, mode):
     k_cache, v_cache, table = paged([k], [v], [n], dtype, seed=4)
     q = query.to(dtype).to(DEV)
     out = torch.empty_like(q)
-    for impl in impls_for(dtype, d):
+    for impl in impls_for(dtype, d, prefill=mode == "prefill"):
         out.fill_(float("nan"))
         if mode == "decode":
             kernels.attention_decode(q, k_cache, v_cache, out, table, torch.tensor([n], dtype=torch.int32, device=DEV), nkv, PAGE, 0,
-                                     window, 1.0, 3, torch.empty(nq * 3 * d, device=DEV), torch.empty(nq * 3 * 2, device=DEV), impl=impl)
+                                     window, 1.0, 3, torch.empty(nq * 3 * d, device=DEV), torch.empty(nq * 3 * 2, device=DEV), impl=impl,
+                                     warps=2 if impl == "ws" else 1)
         else:
             kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
                                       torch.tensor([last], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, window, 1.0, impl=impl)
