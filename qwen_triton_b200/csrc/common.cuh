@@ -80,6 +80,41 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // errors surface in QT_CHECK_LAUNCH
 }
 
+// The same with the blocks grouped into thread-block clusters of `cluster_x` along x (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, unsigned cluster_x,
+                                  Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = cluster_x;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);   // errors surface in QT_CHECK_LAUNCH
+}
+
+// Thread-block cluster helpers: rank and size along the cluster, the address of a shared-memory word of another
+// block of the cluster, a store to it, and the cluster-wide barrier (release/acquire: stores before it are seen after it).
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_size() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_store_float(const float* local, uint32_t rank, float value) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(value) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

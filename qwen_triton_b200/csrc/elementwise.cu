@@ -134,6 +134,51 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
     }
 }
 
+// Few rows (a decode step): a cluster of NORM_CLUSTER blocks per row, one chunk of four elements per thread, so that
+// 8 rows keep 64 SMs busy instead of 8.  Each block pushes its share of the sum of squares into every block of its
+// cluster (distributed shared memory); after the cluster barrier each block adds the shares up in the same order.
+constexpr int NORM_CLUSTER = 8;
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(1024) add_rmsnorm_cluster_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
+                                                                   size_t split_stride, const float* __restrict__ weight, float eps,
+                                                                   TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    __shared__ float shares[NORM_CLUSTER];
+    const uint32_t rank = cluster_rank();
+    const int r = blockIdx.x / NORM_CLUSTER;
+    const int src = rows ? rows[r] : r;
+    float* res = residual + (size_t)src * hidden;
+    const int chunks = hidden >> 2;
+    const int c = (int)rank * blockDim.x + threadIdx.x;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < chunks) {
+        v = load4(res + 4 * c);
+        if (delta) {
+            const TD* dp = delta + (size_t)src * hidden + 4 * c;
+#pragma unroll 4
+            for (int s = 0; s < n_splits; ++s) {
+                const float4 dv = load4(dp + (size_t)s * split_stride);
+                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+            }
+        }
+        if (!rows) store4(res + 4 * c, v);
+    }
+    const float share = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, scratch);
+    if (threadIdx.x < NORM_CLUSTER) cluster_store_float(&shares[rank], threadIdx.x, share);
+    cluster_barrier();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_CLUSTER; ++i) total += shares[i];
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    if (c < chunks) {
+        const float4 w = load4(weight + 4 * c);
+        store4(out + (size_t)r * hidden + 4 * c, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+    }
+}
+
 extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int n_splits, long long split_stride,
                               const float* weight, float eps, void* out, int out_dtype, const int* rows, int n_rows,
                               int hidden, void* stream) {
@@ -144,6 +189,21 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     // the vector kernel needs 16-byte aligned rows everywhere and at most NORM_CACHE chunks per thread
     const bool aligned = hidden % 4 == 0 && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
                          ((uintptr_t)weight % 16 == 0) && (!delta || ((uintptr_t)delta % 16 == 0 && split_stride % 4 == 0));
+    if (aligned && n_rows < 256 && hidden >= 4 * 32 * NORM_CLUSTER && hidden <= 4 * 1024 * NORM_CLUSTER) {
+        const int per_block = (hidden / 4 + NORM_CLUSTER - 1) / NORM_CLUSTER;
+        const int cthreads = ((per_block + 31) / 32) * 32;
+#define QT_LAUNCH_NORM_CLUSTER(TD, TO)                                                                                  \
+    launch_kernel_cluster(add_rmsnorm_cluster_kernel<TD, TO>, dim3(n_rows * NORM_CLUSTER), dim3(cthreads), 0, s, NORM_CLUSTER, residual, \
+                          (const TD*)delta, n_splits, (size_t)split_stride, weight, eps, (TO*)out, rows, hidden)
+        if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM_CLUSTER(float, float);
+        else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM_CLUSTER(float, __nv_bfloat16);
+        else if (delta_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_NORM_CLUSTER(__nv_bfloat16, __nv_bfloat16);
+        else if (delta_dtype == QT_BF16 && out_dtype == QT_F32) QT_LAUNCH_NORM_CLUSTER(__nv_bfloat16, float);
+        else QT_FAIL(QT_ERR_ARG, "add_rmsnorm: unknown element types %d/%d", delta_dtype, out_dtype);
+#undef QT_LAUNCH_NORM_CLUSTER
+        QT_CHECK_LAUNCH("add_rmsnorm");
+        return QT_OK;
+    }
     if (aligned && hidden <= 4 * NORM_CACHE * 1024) {
         // few rows (decode): one chunk per thread, shortest critical path; many rows (prefill): up to NORM_CACHE
         // independent chunks per thread in smaller blocks, which keeps more loads in flight and more blocks resident
