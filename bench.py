@@ -227,11 +227,19 @@ def run_b200(args) -> dict:
     vocab = config.vocab_size
     weight_bytes = 2 * (numbers["linear_params"] + numbers["head_params"])      # the embedding is read row-wise only
 
+    from qwen_triton_b200.ops import kernels
+
+    def progress(text: str) -> None:
+        kernels.check_status(model.engine.device)        # raises if a bounded wait inside a kernel ran out
+        print(f"[bench] {text}", file=sys.stderr, flush=True)
+
+    progress(f"model built: {layers} layers")
     results = {}
     for batch in batches:
         prompts = random_prompts(batch, args.prompt_len, vocab, 100 + batch)
         steps = args.steps if batch == args.batch else max(8, args.steps // 4)
         ms, launches, clocks, context = time_decode(model, prompts, steps, args.warmup, vocab)
+        progress(f"decode at batch {batch}: {ms:.3f} ms per step")
         results[batch] = {"ms": ms, "tok_s": batch * 1e3 / ms, "launches": launches, "clocks": clocks,
                           "context": context, "steps": steps}
     main = results[args.batch]
@@ -240,6 +248,7 @@ def run_b200(args) -> dict:
 
     prompts = random_prompts(args.batch, args.prompt_len, vocab, 100 + args.batch)
     e2e_ms, h2d, d2h = time_e2e(model, prompts, args.steps, args.warmup)
+    progress(f"end to end at batch {args.batch}: {e2e_ms:.3f} ms per step")
 
     line = {
         "metric": "decode_tokens_per_s", "value": round(main["tok_s"], 2), "unit": "tokens/s", "n_gpus": 1,
@@ -264,6 +273,7 @@ def run_b200(args) -> dict:
     if not args.no_prefill:
         tokens = args.prompt_len
         ms = time_prefill(model, tokens, vocab)
+        progress(f"prefill of {tokens} tokens: {ms:.3f} ms")
         flops = 2 * tokens * numbers["linear_params"] + 2 * numbers["head_params"] \
             + numbers["attn_flops_per_pair"] * tokens * (tokens + 1) // 2
         line["prefill"] = {"value": round(tokens * 1e3 / ms, 1), "tokens": tokens, "ms": round(ms, 3),

@@ -1,6 +1,6 @@
 // C[M, N] = A[M, K] * W[N, K]^T with float accumulation on the FMA pipe, for any sizes and for
 // float or bfloat16 inputs.  This is the whole 32-bit path's matrix product (true float: no
-// tensor cores, no reduced-precision mode) and the bfloat16 path's choice for shapes the
+// tensor cores, no reduced-precision mode; sums blocked over K in three levels) and the bfloat16 path's choice for shapes the
 // tensor-core kernel refuses.  Counterpart in luozoupi/Qwen-Triton: kernels/matmul.py:52-97.
 #include "common.cuh"
 
@@ -18,8 +18,11 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TI* __restr
     const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;   // thread computes rows ty*4.., cols tx*4..
     const int load_row = threadIdx.x / 4, load_k = (threadIdx.x % 4) * 4;
-    float acc[4][4] = {};
-    for (int k0 = 0; k0 < K; k0 += GS_BK) {
+    // Three levels of float sums: the 16 products of a K tile, 16 tiles, and the groups of 16 tiles.  One running sum
+    // over a K of thousands would lose about four times as many low-order bits as a blocked CPU product does.
+    float acc[4][4] = {}, mid[4][4] = {};
+    for (int k0 = 0, tile = 0; k0 < K; k0 += GS_BK, ++tile) {
+        float part[4][4] = {};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int k = k0 + load_k + i;
@@ -36,10 +39,22 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TI* __restr
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(av[i], wv[j], part[i][j]);
         }
+        const bool flush = (tile & 15) == 15;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                mid[i][j] += part[i][j];
+                if (flush) { acc[i][j] += mid[i][j]; mid[i][j] = 0.f; }
+            }
         __syncthreads();
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += mid[i][j];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int m = m0 + ty * 4 + i;

@@ -154,6 +154,203 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 }
 
 
+// ----------------------------------------------------------------------------- CTA pairs, for many tokens
+// The same product with two blocks (a cluster on the two SMs of a TPC) per 256 x 256 output tile: each block stages
+// 128 weight rows and 128 of the tile's 256 tokens per K slice (32 KB instead of 48 KB for the same MMA work, so a
+// third less traffic from L2 and a six-stage ring), the even-ranked block issues tcgen05.mma.cta_group::2 with
+// M = 256, N = 256, and each block reads its own 128 accumulator rows back and stores them.  No split-K.
+//
+// One pair per TPC, persistent: a pair walks the tiles pair, pair + pairs, ... with two accumulators in tensor memory
+// (all 512 columns), so that the epilogue of a tile runs under the MMAs of the next.  One block per SM is also what
+// keeps the allocation safe: tcgen05.alloc.cta_group::2 takes columns on both SMs, and two pairs sharing a TPC that
+// allocate at the same moment can each hold one SM's allocator while waiting for the other's (seen as a rare hang
+// with two such blocks per SM); with 192 KB of shared memory per block no second pair fits beside this one.
+//
+// Waits on mbarriers are bounded as above; every thread of both blocks reaches the cluster barriers at the start
+// and at the end whatever happens in between, so no block waits for one that has left.
+constexpr int PAIR_X = 256;                         // tokens per pair tile = MMA N
+constexpr int PAIR_HALF = PAIR_X / 2;               // tokens staged by each block
+constexpr uint32_t PAIR_STAGE_BYTES = W_BYTES + PAIR_HALF * BK * 2;
+constexpr int PAIR_STAGES = 6;
+constexpr uint32_t PAIR_TMEM_COLS = 2 * PAIR_X;     // two accumulators
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                  const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
+                                                                  int M, int N, int nkb, int* status) {
+    // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = 256, M = 256 over the pair
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PAIR_X >> 3) << 17) | ((uint32_t)((2 * BW) >> 4) << 24);
+    constexpr int S = PAIR_STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    // barriers: full[S], empty[S], acc_full[2], acc_empty[2]; then the tensor-memory address
+    const uint32_t full0 = base + S * PAIR_STAGE_BYTES, empty0 = full0 + 8 * S, acc_full0 = empty0 + 8 * S, acc_empty0 = acc_full0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (size_t)S * PAIR_STAGE_BYTES + 8 * (2 * S + 4));
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int w_tiles = (N + 2 * BW - 1) / (2 * BW), x_tiles = (M + PAIR_X - 1) / PAIR_X;
+    const int n_tiles = w_tiles * x_tiles;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 8); }   // four epilogue warps of each block
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(PAIR_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();                                      // barriers of both blocks exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t leader_full0 = map_to_cta(full0, 0);
+            int g = 0;                                       // K slices staged so far, over all tiles
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                int w_tile, x_tile;
+                tile_coords(tile, w_tiles, x_tiles, w_tile, x_tile);
+                const int w0 = w_tile * 2 * BW + (int)rank * BW, x_stage0 = x_tile * PAIR_X + (int)rank * PAIR_HALF;
+                int kb = 0;
+                if (tile == pair) {
+                    // the weight depends on no earlier kernel: fill the ring with weight tiles first, then wait for
+                    // the kernel that produces the activations, then fetch their tiles
+                    const int ahead = min(nkb, S);
+                    for (int i = 0; i < ahead; ++i) {
+                        if (leader) mbar_expect_tx(full0 + 8 * i, 2 * PAIR_STAGE_BYTES);
+                        tma_load_2d_pair(base + i * PAIR_STAGE_BYTES, &map_w, leader_full0 + 8 * i, i * BK, w0);
+                    }
+                    pdl_wait();
+                    for (int i = 0; i < ahead; ++i)
+                        tma_load_2d_pair(base + i * PAIR_STAGE_BYTES + W_BYTES, &map_x, leader_full0 + 8 * i, i * BK, x_stage0);
+                    kb = ahead;
+                    g = ahead;
+                }
+                for (; kb < nkb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t phase = (uint32_t)(g / S) & 1u;
+                    if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) { ok = false; break; }
+                    if (leader) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
+                    const uint32_t dst = base + s * PAIR_STAGE_BYTES;
+                    tma_load_2d_pair(dst, &map_w, leader_full0 + 8 * s, kb * BK, w0);
+                    tma_load_2d_pair(dst + W_BYTES, &map_x, leader_full0 + 8 * s, kb * BK, x_stage0);
+                }
+            }
+            if (pair >= n_tiles) pdl_wait();
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            int g = 0, it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+                const int b = it & 1;
+                // the epilogues of both blocks have read this accumulator's previous tile (passes at once the first time)
+                if (!mbar_wait(acc_empty0 + 8 * b, (((uint32_t)it >> 1) & 1u) ^ 1u, status, 4)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(b * PAIR_X);
+                for (int kb = 0; kb < nkb; ++kb, ++g) {
+                    const int s = g % S;
+                    const uint32_t phase = (uint32_t)(g / S) & 1u;
+                    if (!mbar_wait(full0 + 8 * s, phase, status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t a_desc = operand_desc(base + s * PAIR_STAGE_BYTES);
+                    const uint64_t b_desc = operand_desc(base + s * PAIR_STAGE_BYTES + W_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_pair(tmem_d, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(empty0 + 8 * s);        // the stage is free in both blocks once these MMAs have read it
+                }
+                if (ok) umma_commit_pair(acc_full0 + 8 * b); // both halves of this accumulator are complete
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const uint32_t leader_acc_empty0 = map_to_cta(acc_empty0, 0);
+        pdl_wait();                                          // the output may still be read by an earlier kernel
+        int it = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++it) {
+            int w_tile, x_tile;
+            tile_coords(tile, w_tiles, x_tiles, w_tile, x_tile);
+            const int b = it & 1;
+            if (!mbar_wait(acc_full0 + 8 * b, ((uint32_t)it >> 1) & 1u, status, 3)) break;
+            tc_fence_after();
+            const int n = w_tile * 2 * BW + (int)rank * BW + quarter * 32 + lane;
+            const int x0 = x_tile * PAIR_X;
+#pragma unroll 1
+            for (int c = 0; c < PAIR_X; c += 16) {
+                uint32_t v[16];
+                tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * PAIR_X + c), v);
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = x0 + c + j;
+                        if (m < M) out[(size_t)m * N + n] = from_float<TO>(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8 * b);    // this warp has read its rows of the accumulator
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*(volatile int*)status != 0) {                       // a wait gave up: let copies in flight land before the blocks leave
+        const unsigned long long t0 = global_timer();
+        while (global_timer() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    cluster_sync_all();                                      // the other block no longer reads this block's tiles or barriers
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(PAIR_TMEM_COLS) : "memory");
+    }
+}
+
+template <typename TO>
+int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int* status,
+                cudaStream_t stream) {
+    const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + (2 * PAIR_STAGES + 4) * 8 + 16;
+    static int resident_pairs = 0;                           // pairs the device runs at once (one per TPC that can host a cluster)
+    if (resident_pairs == 0) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_pair_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc_pair: cannot raise shared memory: %s", cudaGetErrorString(err));
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(2 * 148);
+        config.blockDim = dim3(THREADS);
+        config.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = 2;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        int clusters = 0;
+        err = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<TO>, &config);
+        if (err != cudaSuccess || clusters < 1)
+            QT_FAIL(QT_ERR_LAUNCH, "gemm_tc_pair: no cluster of two blocks fits the device (%s)", cudaGetErrorString(err));
+        resident_pairs = clusters;
+    }
+    const long long tiles = (long long)((N + 2 * BW - 1) / (2 * BW)) * ((M + PAIR_X - 1) / PAIR_X);
+    const unsigned pairs = (unsigned)(tiles < resident_pairs ? tiles : resident_pairs);
+    launch_kernel_cluster(gemm_tc_pair_kernel<TO>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total, status);
+    QT_CHECK_LAUNCH("gemm_tc_pair");
+    return QT_OK;
+}
+
 // ----------------------------------------------------------------------------- host side
 template <int BX, typename TO>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
@@ -228,6 +425,28 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
     if (out_dtype == QT_F32)
         return dispatch_tile<float>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, stages, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc: unknown output type %d", out_dtype);
+}
+
+// The same product by pairs of blocks (see gemm_tc_pair_kernel): bfloat16 or float output, no split-K; meant for
+// many tokens (a pair covers 256 weight rows x 256 tokens).  Codes in `status`: as above, 4 = the MMA issuer waiting
+// for the epilogues to free an accumulator.
+extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
+                               int* status, void* stream) {
+    QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc_pair: bad sizes M=%d N=%d K=%d", M, N, K);
+    QT_REQUIRE(K % 8 == 0, "gemm_tc_pair: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
+    QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc_pair: operands must be 16-byte aligned");
+    QT_REQUIRE(status != nullptr, "gemm_tc_pair: a status word is required");
+    const int kb_total = (K + BK - 1) / BK;
+    QT_REQUIRE((long long)((M + PAIR_X - 1) / PAIR_X) * ((N + 2 * BW - 1) / (2 * BW)) < (1ll << 30), "gemm_tc_pair: M=%d x N=%d is too large for one launch", M, N);
+    CUtensorMap map_w, map_x;
+    int rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
+    if (rc) return rc;
+    rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)PAIR_HALF);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, status, s);
+    if (out_dtype == QT_F32) return launch_pair<float>(map_w, map_x, (float*)out, M, N, kb_total, status, s);
+    QT_FAIL(QT_ERR_ARG, "gemm_tc_pair: unknown output type %d", out_dtype);
 }
 
 QT_DEFINE_LAST_ERROR(gemm_tc)

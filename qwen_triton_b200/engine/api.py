@@ -81,6 +81,7 @@ class QwenB200ForCausalLM:
             wants = [list(range(len(r))) if logits_to_keep <= 0 else list(range(max(0, len(r) - logits_to_keep), len(r)))
                      for r in rows]
             flat = self.engine.step([StepEntry(s, r, w) for s, r, w in zip(slots, rows, wants)])
+            self.engine.check_kernels()
         finally:
             for slot in slots:
                 self.engine.release(slot)

@@ -144,6 +144,11 @@ class Engine:
     def can_hold(self, lengths_by_slot: dict[int, int]) -> bool:
         return self.cache.book.can_hold(lengths_by_slot)
 
+    def check_kernels(self) -> None:
+        """Raise if a bounded wait inside a tensor-core kernel ran out since the last check (its results are then
+        invalid).  Reads one word from the device: callers use it where they wait for the device anyway."""
+        kernels.check_status(self.device)
+
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the given tokens; return float logits [sum of wanted places, vocab] in the order of

@@ -102,6 +102,7 @@ class BatchRun:
         logits = self.engine.step(self._entries)
         steps = [len(self.results[i].tokens) for i in self.active]
         tokens = self.sampler.sample(logits, self.sampling, self.active, steps)
+        self.engine.check_kernels()                      # the tokens are on the host: the step has finished
         still: list[int] = []
         for index, token in zip(self.active, tokens):
             result = self.results[index]

@@ -52,6 +52,7 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -394,7 +395,7 @@ def check_status(device: torch.device | str = "cuda") -> None:
     code = int(word[0].item())
     if code != 0:
         word.zero_()
-        role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"role {code}")
+        role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer (for a free accumulator)"}.get(code, f"role {code}")
         raise KernelError(f"gemm_tc: a wait of {role} ran out; the result of that launch is invalid")
 
 
@@ -437,11 +438,31 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
           out.n_splits, out.split_stride, int(stages), _ptr(_status_word(a.device)), _stream())
 
 
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
+    """The same product by pairs of blocks on the two SMs of a TPC (tcgen05 cta_group::2): 256 weight rows x
+    256 tokens per tile, each block staging half of both operands; one persistent pair per TPC with two
+    accumulators in tensor memory.  No split-K; meant for many tokens."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    rows, k = a.shape
+    if k != w.shape[1] or (out.rows, out.cols) != (rows, w.shape[0]) or out.n_splits != 1:
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.tensor.shape)} do not fit")
+    if rows == 0:
+        return
+    if not out.tensor.is_cuda or out.tensor.dtype not in _CODES:
+        raise KernelError("gemm_tc_pair: the output must be a bfloat16 or float32 CUDA tensor")
+    _call("gemm_tc", "qt_gemm_tc_pair", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k,
+          _ptr(_status_word(a.device)), _stream())
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
     """out = a @ w^T with the kernel that fits the element type and shape (a static choice):
     tensor cores for bfloat16 with 16-byte aligned rows, the FMA kernel for float32 and the rest."""
     if gemm_tc_supported(a, w):
-        gemm_tc(a, w, out)
+        if a.shape[0] > _TC_TILES[-1] and out.n_splits == 1:
+            gemm_tc_pair(a, w, out)         # more tokens than one block's tile: pairs of blocks, a third less operand traffic
+        else:
+            gemm_tc(a, w, out)
     elif out.n_splits == 1:
         gemm_simt(a, w, out)
     else:

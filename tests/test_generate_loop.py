@@ -31,6 +31,9 @@ class ScriptedEngine:
         del self.lengths[slot]
         self.free.append(slot)
 
+    def check_kernels(self):
+        pass
+
     def step(self, entries):
         self.steps.append([(e.slot, len(e.tokens)) for e in entries])
         logits = torch.zeros(len(entries), self.vocab)

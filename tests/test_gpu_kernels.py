@@ -365,6 +365,20 @@ def test_gemm_tensor_cores(m, n, k, splits, out_dtype):
     close(GemmOut(out).value(), expected, out_dtype, f"{m}x{n}x{k} splits={splits}")
 
 
+@pytest.mark.parametrize("m, n, k, out_dtype", [
+    (1, 129, 8, torch.float32), (256, 256, 64, torch.float32), (300, 384, 200, torch.float32), (513, 257, 72, torch.float32),
+    (1000, 1100, 4096, torch.bfloat16), (2048, 512, 4096, torch.bfloat16), (129, 19000, 64, torch.bfloat16),
+    (777, 130, 264, torch.bfloat16), (4096, 24576, 192, torch.bfloat16), (5000, 7000, 448, torch.bfloat16)])   # the last two: several tiles per pair
+def test_gemm_tensor_cores_block_pairs(m, n, k, out_dtype):
+    """The cta_group::2 kernel: sizes that are no multiple of the pair's 256 x 256 tile, one K block and many."""
+    a, w = rand(m, k, seed=114, dtype=torch.bfloat16), rand(n, k, seed=115, scale=0.1, dtype=torch.bfloat16)
+    expected = a.double() @ w.double().T
+    out = torch.full((1, m, n), float("nan"), dtype=out_dtype, device=DEV)
+    kernels.gemm_tc_pair(a, w, GemmOut(out))
+    kernels.check_status(DEV)
+    close(out[0], expected, out_dtype, f"{m}x{n}x{k}")
+
+
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
 def test_gemm_tensor_cores_every_token_tile(tile):
     m, n, k = 70, 384, 448
