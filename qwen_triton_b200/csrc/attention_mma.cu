@@ -92,7 +92,8 @@ extern "C" int qt_attention_decode_mma(const void* q, const void* k_cache, const
 }
 
 // The decode kernel that gives every warp a key range of its own: `n_splits` blocks of `warps` warps per
-// (sequence, kv head); partial results per block, merged by the combine kernel when n_splits > 1.
+// (sequence, kv head).  Two to eight blocks form a cluster and merge in the first block's shared memory (one
+// launch, no scratch); more go through scratch and the combine kernel.
 extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* block_table, int max_blocks, const int* seq_len, int n_seqs, int nq,
                                       int nkv, int d, int page_tokens, int ring_tokens, int window, float scale,
@@ -102,22 +103,29 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
     if (rc) return rc;
     QT_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode_ws: n_splits=%d", n_splits);
     QT_REQUIRE(warps >= 1 && warps <= WS_MAX_WARPS, "attention_decode_ws: %d warps per block (1 to %d)", warps, WS_MAX_WARPS);
-    QT_REQUIRE(n_splits == 1 || (part_acc && part_ml), "attention_decode_ws: split results need scratch memory");
     QT_REQUIRE(scale > 0.f, "attention_decode_ws: the score scale must be positive (the row maximum is taken before scaling)");
+    // Up to eight blocks per (sequence, kv head) run as one cluster and merge through the first block's shared memory;
+    // more than that (or QT_B200_DECODE_CLUSTER=0) go through scratch and the combine kernel.
+    static const bool cluster_allowed = [] { const char* env = getenv("QT_B200_DECODE_CLUSTER"); return !(env && env[0] == '0'); }();
+    const int lds = d + PAD;
+    const int group = nq / nkv;
+    const int rows_most = group < 16 ? group : 16;
+    const size_t rings = 16 * (size_t)lds * 2 + (size_t)warps * 4 * WS_TILE * lds * 2;
+    const size_t inboxes = (size_t)n_splits * (rows_most * d + 2 * rows_most) * sizeof(float);
+    const bool cluster = cluster_allowed && n_splits >= 2 && n_splits <= 8 && rings + inboxes <= 227 * 1024;
+    QT_REQUIRE(n_splits == 1 || cluster || (part_acc && part_ml), "attention_decode_ws: split results need scratch memory");
     MmaParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (__nv_bfloat16*)out,
                 block_table, max_blocks, nullptr, nullptr, seq_len, n_seqs, nq, nkv, d, ring_tokens, window, scale,
-                n_splits, part_acc, part_ml, 2};
-    const int lds = d + PAD;
-    const size_t smem = 16 * (size_t)lds * 2 + (size_t)warps * 4 * WS_TILE * lds * 2;
-    const int group = nq / nkv;
+                n_splits, part_acc, part_ml, 2, cluster ? 1 : 0};
+    const size_t smem = rings + (cluster ? inboxes : 0);
     dim3 grid(n_splits, nkv * ((group + 15) / 16), n_seqs), block(32 * warps);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t most = 16 * (128 + PAD) * 2 + (size_t)WS_MAX_WARPS * 4 * WS_TILE * (128 + PAD) * 2;
 #define QT_LAUNCH_WS(DMAX, EXACT)                                                                                        \
     do {                                                                                                                 \
         static bool ok = false;                                                                                          \
-        if (!ok) { rc = raise_smem(attention_decode_ws_kernel<DMAX, EXACT>, most, "attention_decode_ws"); if (rc) return rc; ok = true; } \
-        launch_kernel(attention_decode_ws_kernel<DMAX, EXACT>, grid, block, smem, s, p);                                  \
+        if (!ok) { rc = raise_smem(attention_decode_ws_kernel<DMAX, EXACT>, 227 * 1024, "attention_decode_ws"); if (rc) return rc; ok = true; } \
+        if (cluster) launch_kernel_cluster(attention_decode_ws_kernel<DMAX, EXACT>, grid, block, smem, s, (unsigned)n_splits, p); \
+        else launch_kernel(attention_decode_ws_kernel<DMAX, EXACT>, grid, block, smem, s, p);                             \
     } while (0)
     if (d == 128) QT_LAUNCH_WS(128, true);
     else if (d == 64) QT_LAUNCH_WS(64, true);
@@ -125,7 +133,7 @@ extern "C" int qt_attention_decode_ws(const void* q, const void* k_cache, const 
     else QT_LAUNCH_WS(128, false);
 #undef QT_LAUNCH_WS
     QT_CHECK_LAUNCH("attention_decode_ws");
-    if (n_splits > 1) {
+    if (n_splits > 1 && !cluster) {
         launch_kernel(attention_combine_mma_kernel, dim3(n_seqs * nq), dim3(128), 0, s, part_acc, part_ml, (__nv_bfloat16*)out, n_splits, d);
         QT_CHECK_LAUNCH("attention_combine_mma");
     }

@@ -42,6 +42,7 @@ struct MmaParams {
     float scale;
     int n_splits; float* part_acc; float* part_ml;
     int stages;                    // decode: tiles in the shared-memory ring
+    int cluster_merge;             // decode, one range per warp: the blocks of a (sequence, kv head) are a cluster and merge in shared memory
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -510,6 +511,11 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
         }
     }
     __syncthreads();
+    // With cluster_merge the blocks of this (sequence, kv head) form a cluster: every block writes its merged rows
+    // into the inbox of the first one (distributed shared memory, beyond that block's rings, which may still be in
+    // use), and after the cluster barrier the first block merges the inboxes and stores the result.
+    float* inbox = reinterpret_cast<float*>(smem_raw + q_bytes + (size_t)warps * 4 * tile_bytes);   // [blocks][rows * d + 2 * rows] in block 0
+    const int inbox_stride = rows * d + 2 * rows;
     for (int i = tid; i < rows * d; i += blockDim.x) {
         const int r = i / d, c = i % d;
         float m_all = -INFINITY;
@@ -524,10 +530,34 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
         const int head = head_base + r;
         if (gridDim.x == 1) {
             p.out[((size_t)seq * p.nq + head) * d + c] = __float2bfloat16_rn(a_all / l_all);
+        } else if (p.cluster_merge) {
+            float* slot = inbox + (size_t)split * inbox_stride;
+            cluster_store_float(slot + i, 0, a_all);
+            if (c == 0) { cluster_store_float(slot + rows * d + 2 * r, 0, m_all); cluster_store_float(slot + rows * d + 2 * r + 1, 0, l_all); }
         } else {
             const size_t slot = ((size_t)seq * p.nq + head) * gridDim.x + split;
             p.part_acc[slot * d + c] = a_all;
             if (c == 0) { p.part_ml[slot * 2] = m_all * LN2; p.part_ml[slot * 2 + 1] = l_all; }   // natural-log domain for the combine kernel
+        }
+    }
+    if (p.cluster_merge && gridDim.x > 1) {
+        cluster_barrier();
+        if (split == 0) {
+            const int blocks = gridDim.x;
+            for (int i = tid; i < rows * d; i += blockDim.x) {
+                const int r = i / d;
+                float m_all = -INFINITY;
+                for (int b = 0; b < blocks; ++b) m_all = fmaxf(m_all, inbox[(size_t)b * inbox_stride + rows * d + 2 * r]);
+                float l_all = 0.f, a_all = 0.f;
+                for (int b = 0; b < blocks; ++b) {
+                    const float* slot = inbox + (size_t)b * inbox_stride;
+                    const float mb = slot[rows * d + 2 * r];
+                    const float f = mb == -INFINITY ? 0.f : fast_exp2(mb - m_all);
+                    l_all += slot[rows * d + 2 * r + 1] * f;
+                    a_all += slot[i] * f;
+                }
+                p.out[((size_t)seq * p.nq + head_base + r) * d + (i % d)] = __float2bfloat16_rn(a_all / l_all);
+            }
         }
     }
 }

@@ -8,6 +8,7 @@ split-K partial sums that the consumer adds up in float.
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -310,6 +311,15 @@ def attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
           num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), _stream())
 
 
+def _ws_merges_in_cluster(n_splits: int, warps: int, group: int, head_dim: int) -> bool:
+    """Whether qt_attention_decode_ws merges its blocks in one launch (the rule of attention_mma.cu)."""
+    if os.environ.get("QT_B200_DECODE_CLUSTER", "1").startswith("0") or not 2 <= n_splits <= 8:
+        return False
+    rows = min(group, 16)
+    rings = 16 * (head_dim + 8) * 2 + warps * 4 * 32 * (head_dim + 8) * 2
+    return rings + n_splits * (rows * head_dim + 2 * rows) * 4 <= 227 * 1024
+
+
 DECODE_WARPS_MAX = 6     # warps per block of the one-range-per-warp decode kernel
 
 
@@ -341,6 +351,8 @@ def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     common = (_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.shape[1], _ptr(seq_len),
               n_seqs, num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens, int(window or 0), float(scale), int(n_splits))
     launches = 2 if n_splits > 1 else 1
+    if picked == "ws" and _ws_merges_in_cluster(n_splits, warps, num_heads // num_kv_heads, head_dim):
+        launches = 1
     if picked == "ws":
         _call("attention_mma", "qt_attention_decode_ws", *common, int(warps), _ptr(part_acc), _ptr(part_ml), _stream(), launches=launches)
     elif picked == "mma":
