@@ -13,13 +13,17 @@ from ..ops.kernels import GemmOut
 from .base import Runtime
 
 
-_TARGET_BLOCKS = 2 * 148     # blocks wanted in flight when the product is bound by reading the weight
+_SM_COUNT = 148
 _MAX_SPLITS = 16
+# (most rows, blocks wanted in flight) for products bound by reading the weight.  Up to 16 rows the kernel's ring is
+# three stages deep and four blocks share an SM, which also lets the next product's blocks move in and fetch their
+# first weight tiles while this one drains; up to 64 rows two blocks with deeper rings measured better.
+_SPLIT_PLANS = ((16, 4 * _SM_COUNT), (64, 2 * _SM_COUNT))
 
 
-def pick_splits(out_features: int, in_features: int) -> int:
+def pick_splits(out_features: int, in_features: int, target_blocks: int = 2 * _SM_COUNT) -> int:
     """Split count for a product with few rows: the one whose blocks (128-row weight tiles x splits) fill
-    whole waves of the SMs best, each split keeping at least four 64-wide K blocks; fewer splits win ties."""
+    whole waves of ``target_blocks`` best, each split keeping at least four 64-wide K blocks; fewer splits win ties."""
     tiles = -(-out_features // 128)
     blocks_k = -(-in_features // 64)
     best, best_fill = 1, 0.0
@@ -29,7 +33,7 @@ def pick_splits(out_features: int, in_features: int) -> int:
         if kernels.tc_normalise_splits(in_features, splits) != splits:
             continue
         blocks = tiles * splits
-        fill = blocks / (-(-blocks // _TARGET_BLOCKS) * _TARGET_BLOCKS)
+        fill = blocks / (-(-blocks // target_blocks) * target_blocks)
         if fill > best_fill + 0.03:
             best, best_fill = splits, fill
     return best
@@ -48,12 +52,12 @@ class Linear:
         self.out_dtype = torch.float32 if float_out else runtime.dtype
         runtime.workspace.declare(f"{key}.out", self.max_rows * out_features, self.out_dtype)
         # few rows (decode): split K over more blocks so that every SM streams weights; partial sums are float
-        self.split_rows = 64
-        self.splits = 1
+        self.split_plans: list[tuple[int, int]] = []          # (most rows, splits), fewest rows first
         if runtime.dtype == torch.bfloat16 and in_features % 8 == 0:
-            self.splits = pick_splits(out_features, in_features)
-        if self.splits > 1:
-            runtime.workspace.declare(f"{key}.partial", self.splits * self.split_rows * out_features, torch.float32)
+            self.split_plans = [(rows, pick_splits(out_features, in_features, target)) for rows, target in _SPLIT_PLANS]
+        words = max((rows * splits for rows, splits in self.split_plans if splits > 1), default=0)
+        if words:
+            runtime.workspace.declare(f"{key}.partial", words * out_features, torch.float32)
 
     def set_weight(self, weight: torch.Tensor) -> None:
         if tuple(weight.shape) != (self.out_features, self.in_features):
@@ -62,8 +66,9 @@ class Linear:
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None) -> GemmOut:
         rows = x.shape[0]
-        if out is None and self.splits > 1 and rows <= self.split_rows:
-            partial = self.runtime.workspace.view(f"{self.key}.partial", self.splits, rows, self.out_features)
+        splits = next((n for most, n in self.split_plans if rows <= most), 1)
+        if out is None and splits > 1:
+            partial = self.runtime.workspace.view(f"{self.key}.partial", splits, rows, self.out_features)
             result = GemmOut(partial)
             kernels.gemm(x, self.weight, result)
             return result
