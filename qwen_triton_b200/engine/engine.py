@@ -81,8 +81,11 @@ class Engine:
         self._ctx = StepContext(device=self.device, meta=self._meta)
         self.steps_run = 0
         # one-token steps are captured once per shape and replayed: the launches of a step cost more on the
-        # host than they run on the device.  Mixers that touch the host in forward() opt out (graph_safe).
-        self._graphs_enabled = bool(cuda_graphs) and all(getattr(b.mixer, "graph_safe", False) for b in self.model.blocks)
+        # host than they run on the device.  A part whose step only launches kernels says so (graph_safe = True;
+        # a block answers for the parts it runs); one part that does not, or touches the host, and every step
+        # launches its kernels one by one.
+        stepped = [self.model.embedding, *self.model.blocks, self.model.final_norm, self.model.head]
+        self._graphs_enabled = bool(cuda_graphs) and all(getattr(part, "graph_safe", False) for part in stepped)
         self._graphs: dict[tuple, object] = {}
         self.max_graph_batch = max_graph_batch
         self.graph_replays = 0

@@ -9,13 +9,17 @@ Interfaces (what a new part must offer):
   ``__init__(params, prefix, runtime)``, ``load(source)`` with ``source(name) -> CPU tensor``.
 * norm:        ``apply(stream, out=None, rows=None) -> Tensor``: folds the pending delta into the
   residual stream and returns the normed rows in the activation dtype.
-* position:    ``table(max_positions) -> float32 [P, rotary_dim]`` (cos | sin), or ``None`` for no encoding.
+* position:    ``__init__(params, runtime)``, ``table(max_positions) -> float32 [P, rotary_dim]`` (cos | sin) or ``None``
+  for no encoding, and ``key() -> tuple`` that names the table's content (equal keys share one table).
 * mixer:       ``cache_request() -> KVRequest | StateRequest | None`` and
   ``forward(x, ctx, cache) -> GemmOut`` where ``cache`` is the view of the cache entry this call
   uses (``cache.writable`` tells whether it owns it).
 * feed-forward: ``forward(x, ctx) -> GemmOut``.
 * block:       ``forward(stream, ctx, cache) -> None``: arranges norm, mixer and feed-forward
   around the residual stream.
+* a part whose work in a step is kernel launches only (no host reads, no shapes that depend on data) may set
+  ``graph_safe = True``; a block reports it for the parts it runs.  One-token steps are captured in CUDA graphs
+  only if the embedding, every block, the final norm and the head say so.
 """
 from __future__ import annotations
 

@@ -37,8 +37,17 @@ class PreNormBlock:
                                                                                    names["feed_forward"]))
         return out
 
+    def parts(self) -> tuple:
+        """The parts this block runs in a step."""
+        return (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward)
+
+    @property
+    def graph_safe(self) -> bool:
+        """True if a one-token step through this block only launches kernels (every part says so of itself)."""
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
+
     def load(self, source) -> None:
-        for part in (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward):
+        for part in self.parts():
             part.load(source)
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:

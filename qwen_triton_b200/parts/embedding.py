@@ -16,6 +16,8 @@ from .linear import Linear
 
 @register_embedding("token_embedding")
 class TokenEmbedding:
+    graph_safe = True
+
     def __init__(self, params, vocab_size: int, hidden_size: int, runtime: Runtime) -> None:
         self.name = params["name"]
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
@@ -35,6 +37,8 @@ class TokenEmbedding:
 
 @register_head("linear_head")
 class LinearHead:
+    graph_safe = True
+
     def __init__(self, params, vocab_size: int, hidden_size: int, runtime: Runtime) -> None:
         self.name = params["name"]
         self.tied_to = params.get("tied_to")

@@ -15,6 +15,8 @@ from .linear import Linear
 
 @register_feed_forward("gated_mlp")
 class GatedMLP:
+    graph_safe = True
+
     def __init__(self, params, prefix: str, runtime: Runtime) -> None:
         self.prefix = prefix
         self.runtime = runtime

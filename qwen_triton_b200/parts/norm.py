@@ -14,6 +14,8 @@ from .base import ResidualStream, Runtime, register_norm, to_device
 
 @register_norm("rmsnorm")
 class RMSNorm:
+    graph_safe = True
+
     def __init__(self, params, name: str, runtime: Runtime) -> None:
         self.size = int(params["size"])
         self.eps = float(params["eps"])
