@@ -385,10 +385,18 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
     const int* table = p.block_table + (size_t)seq * p.max_blocks;
 
     const WarpTileCopy copy(d, lds, lane);
+    // Page numbers of 32 tiles at a time, one per lane: a table lookup in front of every tile's copy would put an L2
+    // round trip on each tile's path.
+    int pages_from = -1, lane_page = 0;
     auto issue = [&](int tile) {
         if (tile < n_tiles) {
+            if ((tile >> 5) != pages_from) {
+                pages_from = tile >> 5;
+                const int mine = min((pages_from << 5) + lane, n_tiles - 1);
+                lane_page = cache_page(table, (tile_begin + mine) >> 1, p.ring_tokens);
+            }
             const int t32 = tile_begin + tile;
-            const int page = cache_page(table, t32 >> 1, p.ring_tokens);
+            const int page = __shfl_sync(0xffffffffu, lane_page, tile & 31);
             const size_t off = (((size_t)page * p.nkv + kvh) * PAGE + (t32 & 1) * WS_TILE) * d;
             const uint32_t dst = ring0 + (uint32_t)(tile & 1) * 2u * tile_bytes;
             copy.template start<DMAX, EXACT>(dst, p.k_cache + off);

@@ -90,8 +90,24 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// v += sum over splits of the four elements at dp + s * split_stride, in the order of the splits.  Up to sixteen
+// loads are issued before the first add: with one block per few hundred elements the kernel's time is the chain of
+// L2 round trips, not the bytes.
+template <int BATCH, typename TD>
+__device__ __forceinline__ void add_splits4(float4& v, const TD* dp, int first, int n_splits, size_t split_stride) {
+    for (int s0 = first; s0 < n_splits; s0 += BATCH) {
+        float4 t[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j)               // unconditional loads (the last split again beyond the end), so that they batch
+            t[j] = load4(dp + (size_t)min(s0 + j, n_splits - 1) * split_stride);
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j)
+            if (s0 + j < n_splits) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+    }
+}
+
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
+__global__ void __launch_bounds__(1024, 1) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                        size_t split_stride, const float* __restrict__ weight, float eps,
                                        TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
@@ -108,14 +124,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
         const int c = threadIdx.x + i * blockDim.x;
         if (c < chunks) {
             float4 v = load4(res + 4 * c);
-            if (delta) {
-                const TD* dp = delta + (size_t)src * hidden + 4 * c;
-#pragma unroll 4
-                for (int s = 0; s < n_splits; ++s) {
-                    const float4 dv = load4(dp + (size_t)s * split_stride);
-                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
-                }
-            }
+            if (delta) add_splits4<8>(v, delta + (size_t)src * hidden + 4 * c, 0, n_splits, split_stride);
             if (!rows) store4(res + 4 * c, v);
             x[i] = v;
             sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -140,7 +149,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* _
 constexpr int NORM_CLUSTER = 8;
 
 template <typename TD, typename TO>
-__global__ void __launch_bounds__(1024) add_rmsnorm_cluster_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
+__global__ void __launch_bounds__(1024, 1) add_rmsnorm_cluster_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                                                    size_t split_stride, const float* __restrict__ weight, float eps,
                                                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
@@ -156,16 +165,10 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_cluster_kernel(float* __rest
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < chunks) {
         v = load4(res + 4 * c);
-        if (delta) {
-            const TD* dp = delta + (size_t)src * hidden + 4 * c;
-#pragma unroll 4
-            for (int s = 0; s < n_splits; ++s) {
-                const float4 dv = load4(dp + (size_t)s * split_stride);
-                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
-            }
-        }
+        if (delta) add_splits4<16>(v, delta + (size_t)src * hidden + 4 * c, 0, n_splits, split_stride);
         if (!rows) store4(res + 4 * c, v);
     }
+    const float4 w = c < chunks ? load4(weight + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);   // in flight under the reductions
     const float share = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, scratch);
     if (threadIdx.x < NORM_CLUSTER) cluster_store_float(&shares[rank], threadIdx.x, share);
     cluster_barrier();
@@ -174,7 +177,6 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_cluster_kernel(float* __rest
     for (int i = 0; i < NORM_CLUSTER; ++i) total += shares[i];
     const float inv = rsqrtf(total / (float)hidden + eps);
     if (c < chunks) {
-        const float4 w = load4(weight + 4 * c);
         store4(out + (size_t)r * hidden + 4 * c, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
     }
 }
@@ -279,11 +281,7 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     if (VEC) {
         for (int c = lane; c < (p.d >> 2); c += 32) {
             float4 v = load4(in + in_base + 4 * c);
-#pragma unroll 4
-            for (int s = 1; s < p.n_splits; ++s) {
-                const float4 dv = load4(in + in_base + 4 * c + (size_t)s * p.split_stride);
-                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
-            }
+            add_splits4<16>(v, in + in_base + 4 * c, 1, p.n_splits, p.split_stride);
             *reinterpret_cast<float4*>(vec + 4 * c) = v;
             sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }

@@ -69,6 +69,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     const int nkb = min(kb_total, kb_begin + kb_per_split) - kb_begin;   // >= 1: the host sizes the splits so
 
     if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_w);
+        prefetch_tensor_map(&map_x);
         for (int s = 0; s < stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(tmem_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -203,6 +205,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_w);
+        prefetch_tensor_map(&map_x);
         for (int s = 0; s < S; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 8); }   // four epilogue warps of each block
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

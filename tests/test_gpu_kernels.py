@@ -80,7 +80,7 @@ def test_embedding(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("hidden, splits, rows", [(200, 1, 7), (96, 3, 7), (4100, 2, 7), (1024, 1, 7), (2048, 9, 9), (4100, 2, 300),
-                                                  (9000, 2, 300), (36000, 1, 7)])
+                                                  (9000, 2, 300), (36000, 1, 7), (16000, 9, 260)])
 def test_add_rmsnorm(dtype, hidden, splits, rows):
     eps = 3e-6                                           # few rows of 1024 and more: a cluster of blocks per row
     residual = rand(rows, hidden, seed=2)
