@@ -106,8 +106,8 @@ __device__ __forceinline__ void add_splits4(float4& v, const TD* dp, int first, 
     }
 }
 
-template <typename TD, typename TO>
-__global__ void __launch_bounds__(1024, 1) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
+template <typename TD, typename TO, int BATCH, int MAX_THREADS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_splits,
                                        size_t split_stride, const float* __restrict__ weight, float eps,
                                        TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(1024, 1) add_rmsnorm_vec_kernel(float* __restr
         const int c = threadIdx.x + i * blockDim.x;
         if (c < chunks) {
             float4 v = load4(res + 4 * c);
-            if (delta) add_splits4<8>(v, delta + (size_t)src * hidden + 4 * c, 0, n_splits, split_stride);
+            if (delta) add_splits4<BATCH>(v, delta + (size_t)src * hidden + 4 * c, 0, n_splits, split_stride);
             if (!rows) store4(res + 4 * c, v);
             x[i] = v;
             sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -213,15 +213,24 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
         int vthreads = ((hidden / 4 + 32 * per_thread - 1) / (32 * per_thread)) * 32;
         if (vthreads > 1024) vthreads = 1024;
         if (vthreads < 64) vthreads = 64;
+        // many rows in blocks of up to 256 threads: few registers, five blocks per SM (partial sums of a split product
+        // are rare there); otherwise up to 1,024 threads with eight loads of partial sums in flight
+#define QT_NORM_VEC_ARGS residual, (const TD_*)delta, n_splits, (size_t)split_stride, weight, eps, (TO_*)out, rows, hidden
 #define QT_LAUNCH_NORM_VEC(TD, TO)                                                                                      \
-    launch_kernel(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(vthreads), 0, s, residual, (const TD*)delta, n_splits, (size_t)split_stride, \
-                                                               weight, eps, (TO*)out, rows, hidden)
+    do {                                                                                                                \
+        using TD_ = TD; using TO_ = TO;                                                                                 \
+        if (per_thread > 1 && vthreads <= 256)                                                                          \
+            launch_kernel(add_rmsnorm_vec_kernel<TD, TO, 2, 256, 5>, dim3(n_rows), dim3(vthreads), 0, s, QT_NORM_VEC_ARGS); \
+        else                                                                                                            \
+            launch_kernel(add_rmsnorm_vec_kernel<TD, TO, 8, 1024, 1>, dim3(n_rows), dim3(vthreads), 0, s, QT_NORM_VEC_ARGS); \
+    } while (0)
         if (delta_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_NORM_VEC(float, float);
         else if (delta_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_NORM_VEC(float, __nv_bfloat16);
         else if (delta_dtype == QT_BF16 && out_dtype == QT_BF16) QT_LAUNCH_NORM_VEC(__nv_bfloat16, __nv_bfloat16);
         else if (delta_dtype == QT_BF16 && out_dtype == QT_F32) QT_LAUNCH_NORM_VEC(__nv_bfloat16, float);
         else QT_FAIL(QT_ERR_ARG, "add_rmsnorm: unknown element types %d/%d", delta_dtype, out_dtype);
 #undef QT_LAUNCH_NORM_VEC
+#undef QT_NORM_VEC_ARGS
         QT_CHECK_LAUNCH("add_rmsnorm");
         return QT_OK;
     }
