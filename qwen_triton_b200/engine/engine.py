@@ -12,6 +12,7 @@ length (qwen_triton/modules/cache.py:21), correct for unequal lengths only in pr
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from pathlib import Path
 from typing import Sequence
 
@@ -48,6 +49,17 @@ def require_gpu(device: torch.device) -> None:
     major, minor = torch.cuda.get_device_capability(device)
     if major != 10:
         raise RuntimeError(f"the kernels are built for sm_100a; device {device} is sm_{major}{minor}")
+
+
+@dataclass
+class PlannedDecode:
+    """A one-token step that has been prepared up to the tokens' values (``Engine.plan_decode``)."""
+
+    count: int              # sequences
+    padded: int             # rows the step runs (a power of two)
+    key: tuple              # shape the CUDA graph is kept under
+    context: int            # bucket of the longest sequence
+    prepared: object        # the packed metadata in pinned memory
 
 
 class Engine:
@@ -87,6 +99,8 @@ class Engine:
         stepped = [self.model.embedding, *self.model.blocks, self.model.final_norm, self.model.head]
         self._graphs_enabled = bool(cuda_graphs) and all(getattr(part, "graph_safe", False) for part in stepped)
         self._graphs: dict[tuple, object] = {}
+        self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        self._status_event: torch.cuda.Event | None = None
         self.max_graph_batch = max_graph_batch
         self.graph_replays = 0
         self.last_meta_bytes = 0        # host-to-device bytes of the latest pass (its packed metadata)
@@ -148,9 +162,20 @@ class Engine:
         return self.cache.book.can_hold(lengths_by_slot)
 
     def check_kernels(self) -> None:
-        """Raise if a bounded wait inside a tensor-core kernel ran out since the last check (its results are then
-        invalid).  Reads one word from the device: callers use it where they wait for the device anyway."""
-        kernels.check_status(self.device)
+        """Raise if a bounded wait inside a tensor-core kernel ran out during a step (its results are then invalid).
+        Every step ends with a copy of the status word into pinned memory; this waits for the latest of those
+        copies (no wait at all where the caller has already read the step's results) and looks at the host's copy."""
+        if self._status_event is None:
+            return
+        self._status_event.synchronize()
+        if int(self._status_host[0]) != 0:
+            kernels.check_status(self.device)            # reads the word itself, clears it and raises with the role that gave up
+
+    def _mirror_status(self) -> None:
+        self._status_host.copy_(kernels.status_word(self.device), non_blocking=True)
+        if self._status_event is None:
+            self._status_event = torch.cuda.Event()
+        self._status_event.record()
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -183,7 +208,9 @@ class Engine:
         if (self._graphs_enabled and len(entries) <= min(self.max_graph_batch, self.max_step_tokens // 2)
                 and all(len(e.tokens) == 1 and e.want == [0] for e in entries)):
             self.steps_run += 1
-            return self._decode_step(entries)
+            logits = self._decode_step(entries)
+            self._mirror_status()
+            return logits
 
         n_want = sum(len(e.want) for e in entries)
         logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -223,21 +250,70 @@ class Engine:
                 self.model.forward(self._ctx, self.cache, part)
                 logits.index_copy_(0, torch.tensor(final_rows, device=self.device), part)
         self.steps_run += 1
+        self._mirror_status()
         return logits
 
     def _decode_step(self, entries: list[StepEntry]) -> torch.Tensor:
-        """One token per sequence, every logit wanted: run at a fixed shape (batch padded to a power of
-        two, page tables to a multiple of 16 pages) so that a captured CUDA graph can be replayed.  Padded
-        rows read and write only the cache's spare page, and their logits are dropped."""
+        """One token per sequence, every logit wanted: plan and run in one go."""
+        plan = self._plan_decode([e.slot for e in entries], extend=True)
+        return self._run_planned(plan, [e.tokens[0] for e in entries])
+
+    # ------------------------------------------------------------------ a one-token step in two halves
+    def plan_decode(self, slots: Sequence[int], extend: bool = True) -> "PlannedDecode | None":
+        """The half of a one-token step that does not depend on the tokens' values: checks, one more position for
+        every sequence, page tables, the packed metadata in pinned memory.  A caller that waits for the device to
+        hand over the previous step's tokens can do this meanwhile and call ``run_planned`` once it has them.
+
+        ``extend=False`` plans again for sequences that an abandoned plan has already given their next position
+        (a plan is abandoned by just not running it; sequences that end are released as usual).  Returns None
+        where one-token steps are not run at a fixed shape (CUDA graphs off, or too many sequences): use ``step``.
+        """
+        slots = list(slots)
+        if not slots or not self._graphs_enabled or len(slots) > min(self.max_graph_batch, self.max_step_tokens // 2):
+            return None
+        book = self.cache.book
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        targets = {}
+        for slot in slots:
+            if not book.is_live(slot):
+                raise ValueError(f"slot {slot} is not in use")
+            targets[slot] = book.length(slot) + (1 if extend else 0)
+            if targets[slot] > self.max_seq_len:
+                raise ValueError(f"slot {slot}: {targets[slot]} tokens exceed max_seq_len={self.max_seq_len}")
+        if extend and not book.can_hold(targets):
+            raise RuntimeError("the cache cannot hold this step: too many tokens are live (raise max_tokens)")
+        return self._plan_decode(slots, extend)
+
+    def run_planned(self, plan: "PlannedDecode", tokens: Sequence[int]) -> torch.Tensor:
+        """The other half: the tokens (one per planned sequence, in the plan's order) go in and the step runs.
+        Returns float logits [sequences, vocab]."""
+        tokens = [int(t) for t in tokens]
+        if len(tokens) != plan.count:
+            raise ValueError(f"{len(tokens)} tokens for a plan of {plan.count} sequences")
+        low, high = min(tokens), max(tokens)
+        if low < 0 or high >= self.spec.vocab_size:
+            raise ValueError(f"token id {low if low < 0 else high} is outside 0..{self.spec.vocab_size - 1}")
+        self.steps_run += 1
+        logits = self._run_planned(plan, tokens)
+        self._mirror_status()
+        return logits
+
+    def _plan_decode(self, slots: list[int], extend: bool) -> "PlannedDecode":
+        """Fixed shape of a one-token step: batch padded to a power of two, page tables to a multiple of 16 pages, so
+        that a captured CUDA graph can be replayed.  Padded rows read and write only the cache's spare page, and
+        their logits are dropped."""
         book, cache = self.cache.book, self.cache
-        count = len(entries)
+        count = len(slots)
         padded = 1
         while padded < count:
             padded *= 2
-        slots = [e.slot for e in entries]
-        past = [book.length(s) for s in slots]
-        for slot, before in zip(slots, past):
-            book.extend(slot, before + 1)
+        if extend:
+            past = [book.length(s) for s in slots]
+            for slot, before in zip(slots, past):
+                book.extend(slot, before + 1)
+        else:
+            past = [book.length(s) - 1 for s in slots]
         widths, tables = [], []
         for group in range(len(cache.groups)):
             need = max(len(book.pages(s, group)) for s in slots)
@@ -250,10 +326,14 @@ class Engine:
             tables.append(table)
         context = -(-(max(past) + 1) // 1024) * 1024
         pad = padded - count
-        self._ctx.fill(slots + [0] * pad, [e.tokens for e in entries] + [[0]] * pad, past + [0] * pad,
-                       list(range(padded)), tables, max_context=context)
+        prepared = self._ctx.prepare_decode(slots + [0] * pad, past + [0] * pad, tables)
+        return PlannedDecode(count=count, padded=padded, key=(padded, tuple(widths), context), context=context, prepared=prepared)
+
+    def _run_planned(self, plan: "PlannedDecode", tokens: list[int]) -> torch.Tensor:
+        cache, count, padded = self.cache, plan.count, plan.padded
+        self._ctx.commit_decode(plan.prepared, tokens + [0] * (padded - count), plan.context)
         self.last_meta_bytes = self._ctx.meta_bytes
-        key = (padded, tuple(widths), context)
+        key = plan.key
         state = self._graphs.get(key)
         if state is None:                      # first time at this shape: run the launches themselves
             logits = torch.empty((padded, self.spec.vocab_size), dtype=torch.float32, device=self.device)

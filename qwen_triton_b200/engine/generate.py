@@ -83,6 +83,7 @@ class BatchRun:
         self.active = list(indices)
         self.slot_of: dict[int, int] = {}
         self._entries: list[StepEntry] = []
+        self._plan = None           # the next one-token step, prepared while the device ran the last one
 
     @property
     def done(self) -> bool:
@@ -96,12 +97,38 @@ class BatchRun:
     def advance(self) -> list[int]:
         return self._run()
 
+    def _ends_whatever_it_emits(self, index: int) -> bool:
+        """True if the request's next token is its last by count or by the cache's length, stop token or not."""
+        result = self.results[index]
+        return bool(finish_reason(-1, len(result.tokens) + 1, len(self.prompts[index]) + len(result.tokens) + 1,
+                                  stop_ids=frozenset(), max_new_tokens=self.max_new_tokens,
+                                  max_seq_len=self.engine.max_seq_len))
+
     def _run(self) -> list[int]:
         """One step and one sampled token per active request; returns the tokens in the order of ``active``
-        as it was before the step."""
-        logits = self.engine.step(self._entries)
+        as it was before the step.
+
+        While the device runs the step and the choice of tokens, the host prepares the next one-token step for the
+        requests that can only end by a stop token (``plan_decode``, where the engine offers it): that is all of a
+        step's host work except putting the tokens in.  If a stop token then ends a request, the plan is dropped
+        and made again for those that go on."""
+        if self._plan is not None:
+            logits = self.engine.run_planned(self._plan, [self.results[i].tokens[-1] for i in self.active])
+        else:
+            logits = self.engine.step(self._entries)
+        self._plan = None
         steps = [len(self.results[i].tokens) for i in self.active]
-        tokens = self.sampler.sample(logits, self.sampling, self.active, steps)
+        launch = getattr(self.sampler, "launch", None)
+        planner = getattr(self.engine, "plan_decode", None)
+        plan, expected = None, None
+        if launch is not None and planner is not None:
+            pending = launch(logits, self.sampling, self.active, steps)
+            expected = [i for i in self.active if not self._ends_whatever_it_emits(i)]
+            if expected:
+                plan = planner([self.slot_of[i] for i in expected])
+            tokens = pending.tokens()
+        else:
+            tokens = self.sampler.sample(logits, self.sampling, self.active, steps)
         self.engine.check_kernels()                      # the tokens are on the host: the step has finished
         still: list[int] = []
         for index, token in zip(self.active, tokens):
@@ -116,6 +143,9 @@ class BatchRun:
             else:
                 still.append(index)
         self.active = still
+        if plan is not None and still != expected:       # a stop token: those that go on already have their next position
+            plan = planner([self.slot_of[i] for i in still], extend=False) if still else None
+        self._plan = plan
         self._entries = [StepEntry(self.slot_of[i], [self.results[i].tokens[-1]], [0]) for i in still]
         return tokens
 

@@ -62,6 +62,7 @@ class StepContext:
         self.token_ids = self.token_seq = self.token_pos = None
         self.seq_start = self.seq_past = self.seq_len = self.slots = self.want_rows = None
         self._tables: dict[int, torch.Tensor] = {}
+        self._decode_plans: dict[tuple, "_DecodePlan"] = {}
 
     def block_table(self, group: int) -> torch.Tensor:
         return self._tables[group]
@@ -109,3 +110,73 @@ class StepContext:
         self.max_q_len = max(q_lens) if q_lens else 0
         self.max_context = max_context if max_context is not None else (int(seq_len.max()) if n_seqs else 0)
         self.is_decode = bool(q_lens) and all(q == 1 for q in q_lens)
+
+    # ------------------------------------------------------------------ one token per sequence
+    def prepare_decode(self, slots: list[int], past: list[int], tables: list[np.ndarray]):
+        """The part of ``fill`` for a pass of one token per sequence (every row wanted) that does not need the
+        tokens: the same layout at the same addresses, written into pinned buffers that are kept (a small ring,
+        each guarded by an event, so that a caller who runs ahead of the device cannot overwrite a copy that has
+        not happened yet) with the parts that never change filled in once.  Returns what ``commit_decode`` takes."""
+        n = len(slots)
+        key = (n, tuple(t.shape[1] for t in tables))
+        plan = self._decode_plans.get(key)
+        if plan is None:
+            plan = self._decode_plans[key] = _DecodePlan(self._meta, n, key[1])
+        host, array, event = plan.next_buffer()
+        array[2 * n:3 * n] = past
+        array[plan.at_past:plan.at_past + n] = past
+        np.add(array[plan.at_past:plan.at_past + n], 1, out=array[plan.at_len:plan.at_len + n])
+        array[plan.at_slots:plan.at_slots + n] = slots
+        for offset, table in zip(plan.at_tables, tables):
+            array[offset:offset + table.size] = table.reshape(-1)
+        return plan, host, array, event
+
+    def commit_decode(self, prepared, tokens: list[int], max_context: int) -> None:
+        """Put the tokens in, copy the pass to the device in one transfer and make it the current pass."""
+        plan, host, array, event = prepared
+        n = plan.n
+        array[0:n] = tokens
+        self._meta[:plan.total].copy_(host, non_blocking=True)
+        event.record()
+        self.meta_bytes = 4 * plan.total
+        (self.token_ids, self.token_seq, self.token_pos, self.seq_start, self.seq_past, self.seq_len,
+         self.slots, self.want_rows) = plan.views[:8]
+        self._tables = plan.tables
+        self.n_tokens = self.n_seqs = self.n_want = n
+        self.max_q_len = 1
+        self.max_context = max_context
+        self.is_decode = True
+
+
+class _DecodePlan:
+    """Offsets, device views and pinned host buffers of ``prepare_decode`` for one batch size and table widths."""
+
+    RING = 4
+
+    def __init__(self, meta: torch.Tensor, n: int, widths: tuple[int, ...]) -> None:
+        self.n = n
+        sizes = [n, n, n, n + 1, n, n, n, n] + [n * w for w in widths]
+        offsets = np.concatenate(([0], np.cumsum(sizes))).tolist()
+        self.total = offsets[-1]
+        if self.total > meta.numel():
+            raise ValueError(f"step metadata of {self.total} words exceeds the buffer of {meta.numel()}")
+        self.at_past, self.at_len, self.at_slots = offsets[4], offsets[5], offsets[6]
+        self.at_tables = offsets[8:8 + len(widths)]
+        self.views = [meta[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
+        self.tables = {g: self.views[8 + g].view(n, w) for g, w in enumerate(widths)}
+        self.buffers = []
+        for _ in range(self.RING):
+            host = torch.zeros(self.total, dtype=torch.int32, pin_memory=True)
+            array = host.numpy()
+            array[offsets[1]:offsets[2]] = np.arange(n)              # token_seq
+            array[offsets[3]:offsets[4]] = np.arange(n + 1)          # seq_start
+            array[offsets[7]:offsets[8]] = np.arange(n)              # want_rows
+            self.buffers.append((host, array, torch.cuda.Event()))
+        self.turn = 0
+
+    def next_buffer(self):
+        host, array, event = self.buffers[self.turn % self.RING]
+        if self.turn >= self.RING:
+            event.synchronize()                                      # the copy that last used this buffer has happened
+        self.turn += 1
+        return host, array, event

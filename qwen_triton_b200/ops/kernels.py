@@ -401,6 +401,11 @@ def _status_word(device: torch.device) -> torch.Tensor:
     return _STATUS[index]
 
 
+def status_word(device: torch.device | str = "cuda") -> torch.Tensor:
+    """The device words the tensor-core kernels report into (word 0: the code of a wait that ran out, else 0)."""
+    return _status_word(torch.device(device))
+
+
 def check_status(device: torch.device | str = "cuda") -> None:
     """Raise if a bounded wait inside a tensor-core kernel ran out since the last check (synchronises)."""
     word = _status_word(torch.device(device))

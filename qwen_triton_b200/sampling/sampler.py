@@ -41,13 +41,30 @@ def uniform_for(seed: int, request: int, step: int) -> float:
     return (state >> 40) / float(1 << 24)
 
 
+class PendingTokens:
+    """Token ids on their way to the host: ``tokens()`` waits for the copy and returns them."""
+
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, rows: int) -> None:
+        self._host, self._event, self._rows = host, event, rows
+
+    def tokens(self) -> list[int]:
+        self._event.synchronize()
+        return self._host[:self._rows].tolist()
+
+
 class Sampler:
     """Chooses one token per logits row on the device and returns the ids to the host."""
 
+    _RING = 4
+
     def __init__(self, device: torch.device) -> None:
         self.device = torch.device(device)
+        self._hosts: list[torch.Tensor] = []     # pinned buffers the ids are copied into, used in turn
+        self._turn = 0
 
-    def sample(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], steps: list[int]) -> list[int]:
+    def launch(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], steps: list[int]) -> PendingTokens:
+        """Start the choice and the copy of the ids to pinned host memory; the caller may do other work before
+        it asks the returned object for the tokens."""
         rows = logits.shape[0]
         if rows != len(requests) or rows != len(steps):
             raise ValueError("one request index and one step number per logits row")
@@ -59,4 +76,14 @@ class Sampler:
                                    dtype=torch.float32).to(self.device)
             temperature = torch.full((rows,), params.temperature, dtype=torch.float32, device=self.device)
             kernels.sample(logits, temperature, uniform, out)
-        return out.tolist()
+        if not self._hosts or self._hosts[0].numel() < rows:
+            self._hosts = [torch.empty(max(rows, 64), dtype=torch.int32, pin_memory=True) for _ in range(self._RING)]
+        host = self._hosts[self._turn % self._RING]
+        self._turn += 1
+        host[:rows].copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens(host, event, rows)
+
+    def sample(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], steps: list[int]) -> list[int]:
+        return self.launch(logits, params, requests, steps).tokens()

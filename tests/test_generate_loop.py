@@ -70,6 +70,83 @@ def test_unequal_prompts_stop_tokens_and_early_finish():
     assert sampler.calls[0] == ([0, 1, 2], [0, 0, 0]) and sampler.calls[3] == ([0, 2], [3, 3])
 
 
+class PlanningEngine(ScriptedEngine):
+    """The scripted engine with the two halves of a one-token step: ``plan_decode`` gives every planned sequence
+    its next position, ``run_planned`` takes the tokens.  It checks that a position is given exactly once."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.plans: list[tuple[list[int], bool]] = []
+        self.fed: dict[int, int] = {}            # tokens fed per slot, which must equal its length after every step
+
+    def new_sequence(self):
+        slot = super().new_sequence()
+        self.fed[slot] = 0
+        return slot
+
+    def step(self, entries):
+        for entry in entries:
+            self.fed[entry.slot] += len(entry.tokens)
+        return super().step(entries)
+
+    def plan_decode(self, slots, extend=True):
+        self.plans.append((list(slots), extend))
+        for slot in slots:
+            assert slot in self.lengths, "planned for a slot that is not in use"
+            if extend:
+                self.lengths[slot] += 1
+            assert self.lengths[slot] == self.fed[slot] + 1, "a planned sequence has exactly one position it has not been fed"
+            assert self.lengths[slot] <= self.max_seq_len
+        return list(slots)
+
+    def run_planned(self, plan, tokens):
+        assert len(plan) == len(tokens)
+        self.steps.append([(slot, 1) for slot in plan])
+        logits = torch.zeros(len(plan), self.vocab)
+        for row, (slot, token) in enumerate(zip(plan, tokens)):
+            self.fed[slot] += 1
+            assert self.fed[slot] == self.lengths[slot]
+            logits[row, (token + 1) % self.vocab] = 1.0
+        return logits
+
+
+class LaunchSampler(ArgmaxSampler):
+    def launch(self, logits, params, requests, steps):
+        tokens = self.sample(logits, params, requests, steps)
+
+        class Pending:
+            def tokens(self):
+                return tokens
+
+        return Pending()
+
+
+def test_the_next_step_is_planned_ahead_and_replanned_after_a_stop_token():
+    plain_engine, engine = ScriptedEngine(), PlanningEngine()
+    prompts = [[10, 11, 12], [46], [20, 21]]
+    expected = generate(plain_engine, prompts, max_new_tokens=5, sampler=ArgmaxSampler())
+    results = generate(engine, prompts, max_new_tokens=5, sampler=LaunchSampler())
+    assert [(r.tokens, r.finish_reason) for r in results] == [(r.tokens, r.finish_reason) for r in expected]
+    assert engine.steps == plain_engine.steps            # the same sequences run at every step
+    # planned after the prompts and after every step while someone can go on; when slot 1 stops at its third token
+    # the plan for three is dropped and made again, without a second position, for the two that go on
+    assert engine.plans[:2] == [([0, 1, 2], True), ([0, 1, 2], True)]
+    assert ([0, 1, 2], True) == engine.plans[2] and engine.plans[3] == ([0, 2], False)
+    assert engine.plans[4] == ([0, 2], True) and len(engine.plans) == 5      # the last tokens end by count: nothing to plan
+    assert not engine.lengths and sorted(engine.free) == [0, 1, 2]
+
+
+def test_planning_stops_at_the_cache_end_and_survives_batches():
+    engine = PlanningEngine(max_seq_len=6, total_pages=10)
+    result = generate(engine, [[1, 2, 3, 4]], max_new_tokens=10, sampler=LaunchSampler(), ignore_eos=True)[0]
+    assert result.tokens == [5, 6, 7] and result.finish_reason == "max_seq_len"
+    assert engine.plans == [([0], True), ([0], True)]     # the third new token cannot be fed back: no plan for it
+    engine = PlanningEngine(num_slots=2, total_pages=100)
+    results = generate(engine, [[1], [2, 3], [4], [5, 6, 7], [8]], max_new_tokens=2, sampler=LaunchSampler(), ignore_eos=True)
+    assert [r.tokens for r in results] == [[2, 3], [4, 5], [5, 6], [8, 9], [9, 10]]
+    assert engine.slot_history == [0, 1, 0, 1, 0]
+
+
 def test_more_requests_than_slots_run_as_batches_and_reuse_slots():
     engine = ScriptedEngine(num_slots=2, total_pages=100)
     prompts = [[1], [2, 3], [4], [5, 6, 7], [8]]
