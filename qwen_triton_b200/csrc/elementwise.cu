@@ -537,19 +537,24 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
 }
 
 // ----------------------------------------------------------------------------- SiLU-gated product
-// out[t, i] = silu(g) * u with g = gate_up[t, i], u = gate_up[t, inter + i]; float inside.
+// out[t, i] = silu(g) * u; float inside.  Plain layout (group 0): g = gate_up[t, i], u = gate_up[t, inter + i].
+// Interleaved layout (group G, the fused weight's rows alternate G of gate and G of up, which is what lets a GEMM
+// epilogue see both in one warp): g = gate_up[t, (i / G) * 2G + i % G], u = the element G further on.
+__device__ __forceinline__ size_t gate_column(int i, int group) { return group ? (size_t)(i / group) * 2 * group + i % group : (size_t)i; }
+
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                              long long total, int inter) {
+                              long long total, int inter, int group) {
     pdl_launch_dependents();
     pdl_wait();
+    const int up_offset = group ? group : inter;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / inter;
         const int i = (int)(idx % inter);
-        const size_t base = (size_t)t * 2 * inter;
-        const float g = load_sum(gate_up, base + i, n_splits, split_stride);
-        const float u = load_sum(gate_up, base + inter + i, n_splits, split_stride);
+        const size_t base = (size_t)t * 2 * inter + gate_column(i, group);
+        const float g = load_sum(gate_up, base, n_splits, split_stride);
+        const float u = load_sum(gate_up, base + up_offset, n_splits, split_stride);
         out[idx] = from_float<TO>(g / (1.f + expf(-g)) * u);
     }
 }
@@ -583,10 +588,11 @@ template <typename TO> __device__ __forceinline__ float4 silu_mul4(const float4&
 // PT chunks per thread, all loads issued before the first store.
 template <typename TI, typename TO, int PT>
 __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                                  int inter) {
+                                  int inter, int group) {
     pdl_launch_dependents();
     pdl_wait();
     const int chunks = inter >> 3;
+    const int up_offset = group ? group : inter;
     const TI* row = gate_up + (size_t)blockIdx.x * 2 * inter;
     TO* orow = out + (size_t)blockIdx.x * inter;
     for (int c0 = blockIdx.y * blockDim.x * PT + threadIdx.x; c0 < chunks; c0 += gridDim.y * blockDim.x * PT) {
@@ -594,14 +600,15 @@ __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, 
 #pragma unroll
         for (int i = 0; i < PT; ++i) {
             const int c = c0 + i * blockDim.x;
-            if (c < chunks) { g[i] = load8(row + 8 * c); u[i] = load8(row + 8 * c + inter); }
+            if (c < chunks) { const size_t at = gate_column(8 * c, group); g[i] = load8(row + at); u[i] = load8(row + at + up_offset); }
         }
         for (int s = 1; s < n_splits; ++s) {
 #pragma unroll
             for (int i = 0; i < PT; ++i) {
                 const int c = c0 + i * blockDim.x;
                 if (c < chunks) {
-                    const Float8 dg = load8(row + 8 * c + (size_t)s * split_stride), du = load8(row + 8 * c + inter + (size_t)s * split_stride);
+                    const size_t at = gate_column(8 * c, group) + (size_t)s * split_stride;
+                    const Float8 dg = load8(row + at), du = load8(row + at + up_offset);
                     add4(g[i].a, dg.a); add4(g[i].b, dg.b); add4(u[i].a, du.a); add4(u[i].b, du.b);
                 }
             }
@@ -615,13 +622,14 @@ __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, 
 }
 
 extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long long split_stride, void* out, int out_dtype,
-                         int n_tokens, int inter, void* stream) {
+                         int n_tokens, int inter, int group, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && inter > 0 && n_splits >= 1, "swiglu: bad sizes T=%d I=%d", n_tokens, inter);
+    QT_REQUIRE(group >= 0 && (group == 0 || inter % group == 0), "swiglu: rows interleaved in groups of %d do not divide I=%d", group, inter);
     if (n_tokens == 0) return QT_OK;
     const long long total = (long long)n_tokens * inter;
     const int threads = 256;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = inter % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const bool vec = inter % 8 == 0 && group % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
     // few tokens (decode): one chunk per thread, most blocks; many tokens (prefill): two chunks per thread
@@ -631,11 +639,11 @@ extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long l
 #define QT_LAUNCH_SWIGLU(TI, TO)                                                                                              \
     do {                                                                                                                      \
         if (vec && per_thread == 2) launch_kernel(swiglu_vec_kernel<TI, TO, 2>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s, \
-                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter);                          \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group);                   \
         else if (vec) launch_kernel(swiglu_vec_kernel<TI, TO, 1>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s,     \
-                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter);                          \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group);                   \
         else launch_kernel(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up, n_splits,  \
-                           (size_t)split_stride, (TO*)out, total, inter);                                                     \
+                           (size_t)split_stride, (TO*)out, total, inter, group);                                              \
     } while (0)
     if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_SWIGLU(float, float);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_SWIGLU(float, __nv_bfloat16);

@@ -180,7 +180,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-template <typename TO>
+// SWIGLU: the weight's rows alternate 16 of a gate projection and 16 of an up projection (see swiglu in
+// elementwise.cu); a warp of the epilogue then holds both halves of 16 features in its 32 accumulator lanes, and the
+// kernel stores silu(gate) * up, [M, N / 2], instead of the product itself.
+constexpr int SWIGLU_GROUP = 16;
+
+template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
                                                                   int M, int N, int nkb, int* status) {
@@ -294,11 +299,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
             tc_fence_after();
             const int n = w_tile * 2 * BW + (int)rank * BW + quarter * 32 + lane;
             const int x0 = x_tile * PAIR_X;
+            // SWIGLU: lanes 0..15 hold the gate rows of 16 features, lanes 16..31 the up rows of the same features
+            const int feature = ((n - lane) >> 1) + (lane & 15), features = N >> 1;
+            const bool stores = SWIGLU ? ((lane & 16) == 0 && feature < features) : n < N;
 #pragma unroll 1
             for (int c = 0; c < PAIR_X; c += 16) {
                 uint32_t v[16];
                 tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * PAIR_X + c), v);
-                if (n < N) {
+                if (SWIGLU) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float g = __uint_as_float(v[j]);
+                        const float u = __shfl_xor_sync(0xffffffffu, g, 16);
+                        const int m = x0 + c + j;
+                        if (stores && m < M) out[(size_t)m * features + feature] = from_float<TO>(__fdividef(g, 1.f + __expf(-g)) * u);
+                    }
+                } else if (stores) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = x0 + c + j;
@@ -323,13 +339,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
     }
 }
 
-template <typename TO>
+template <typename TO, bool SWIGLU>
 int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int* status,
                 cudaStream_t stream) {
     const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + (2 * PAIR_STAGES + 4) * 8 + 16;
     static int resident_pairs = 0;                           // pairs the device runs at once (one per TPC that can host a cluster)
     if (resident_pairs == 0) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_pair_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_pair_kernel<TO, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc_pair: cannot raise shared memory: %s", cudaGetErrorString(err));
         cudaLaunchConfig_t config = {};
         config.gridDim = dim3(2 * 148);
@@ -343,14 +359,14 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
         config.attrs = attribute;
         config.numAttrs = 1;
         int clusters = 0;
-        err = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<TO>, &config);
+        err = cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<TO, SWIGLU>, &config);
         if (err != cudaSuccess || clusters < 1)
             QT_FAIL(QT_ERR_LAUNCH, "gemm_tc_pair: no cluster of two blocks fits the device (%s)", cudaGetErrorString(err));
         resident_pairs = clusters;
     }
     const long long tiles = (long long)((N + 2 * BW - 1) / (2 * BW)) * ((M + PAIR_X - 1) / PAIR_X);
     const unsigned pairs = (unsigned)(tiles < resident_pairs ? tiles : resident_pairs);
-    launch_kernel_cluster(gemm_tc_pair_kernel<TO>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total, status);
+    launch_kernel_cluster(gemm_tc_pair_kernel<TO, SWIGLU>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total, status);
     QT_CHECK_LAUNCH("gemm_tc_pair");
     return QT_OK;
 }
@@ -433,14 +449,16 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
 }
 
 // The same product by pairs of blocks (see gemm_tc_pair_kernel): bfloat16 or float output, no split-K; meant for
-// many tokens (a pair covers 256 weight rows x 256 tokens).  Codes in `status`: as above, 4 = the MMA issuer waiting
-// for the epilogues to free an accumulator.
-extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K,
+// many tokens (a pair covers 256 weight rows x 256 tokens).  With `swiglu` the weight's rows alternate 16 of a gate and
+// 16 of an up projection and `out` is [M, N / 2] = silu(gate) * up.  Codes in `status`: as above, 4 = the MMA issuer
+// waiting for the epilogues to free an accumulator.
+extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int swiglu,
                                int* status, void* stream) {
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc_pair: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc_pair: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc_pair: operands must be 16-byte aligned");
     QT_REQUIRE(status != nullptr, "gemm_tc_pair: a status word is required");
+    QT_REQUIRE(!swiglu || N % (2 * SWIGLU_GROUP) == 0, "gemm_tc_pair: N=%d is not gate and up rows in groups of %d", N, SWIGLU_GROUP);
     const int kb_total = (K + BK - 1) / BK;
     QT_REQUIRE((long long)((M + PAIR_X - 1) / PAIR_X) * ((N + 2 * BW - 1) / (2 * BW)) < (1ll << 30), "gemm_tc_pair: M=%d x N=%d is too large for one launch", M, N);
     CUtensorMap map_w, map_x;
@@ -449,9 +467,10 @@ extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_
     rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)PAIR_HALF);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, status, s);
-    if (out_dtype == QT_F32) return launch_pair<float>(map_w, map_x, (float*)out, M, N, kb_total, status, s);
-    QT_FAIL(QT_ERR_ARG, "gemm_tc_pair: unknown output type %d", out_dtype);
+    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, status, s);
+    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, status, s);
+    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, status, s);
+    QT_FAIL(QT_ERR_ARG, "gemm_tc_pair: output type %d%s is not offered", out_dtype, swiglu ? " with the SiLU-gated epilogue" : "");
 }
 
 QT_DEFINE_LAST_ERROR(gemm_tc)

@@ -28,7 +28,7 @@ _SIGNATURES = {
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
@@ -53,7 +53,7 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
-        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -235,14 +235,28 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
           1 if write_kv else 0, 1 if kv_in_proj else 0, _stream())
 
 
-def swiglu(gate_up: GemmOut, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid out for the GEMM's SiLU-gated epilogue
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tensor:
+    """[gate; up] with the rows alternating ``group`` of gate and ``group`` of up (``group`` 0: gate, then up)."""
+    if group == 0:
+        return torch.cat((gate, up), dim=0)
+    inter, hidden = gate.shape
+    if inter % group:
+        raise KernelError(f"rows in groups of {group} do not divide {inter}")
+    return torch.stack((gate.view(inter // group, group, hidden), up.view(inter // group, group, hidden)), dim=1).reshape(2 * inter, hidden)
+
+
+def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0) -> None:
+    """out[t, i] = silu(gate[t, i]) * up[t, i] where gate_up[t] holds gate then up (``group`` 0) or alternates
+    ``group`` elements of gate and ``group`` of up."""
     tokens, inter = out.shape
     _need(out, "out")
     if (gate_up.rows, gate_up.cols) != (tokens, 2 * inter):
         raise KernelError(f"swiglu: input {tuple(gate_up.tensor.shape)} does not match output {tuple(out.shape)}")
     _call("elementwise", "qt_swiglu", _ptr(gate_up.tensor), _code(gate_up.tensor, "gate_up"), gate_up.n_splits,
-          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, _stream())
+          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, int(group), _stream())
 
 
 # ----------------------------------------------------------------------------- attention
@@ -455,28 +469,37 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
           out.n_splits, out.split_stride, int(stages), _ptr(_status_word(a.device)), _stream())
 
 
-def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False) -> None:
     """The same product by pairs of blocks on the two SMs of a TPC (tcgen05 cta_group::2): 256 weight rows x
     256 tokens per tile, each block staging half of both operands; one persistent pair per TPC with two
-    accumulators in tensor memory.  No split-K; meant for many tokens."""
+    accumulators in tensor memory.  No split-K; meant for many tokens.
+
+    With ``swiglu`` the rows of ``w`` alternate SWIGLU_GROUP of a gate and of an up projection
+    (``interleave_gate_up``) and ``out`` [1, M, N / 2] receives silu(gate) * up from the epilogue."""
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     rows, k = a.shape
-    if k != w.shape[1] or (out.rows, out.cols) != (rows, w.shape[0]) or out.n_splits != 1:
+    cols = w.shape[0] // 2 if swiglu else w.shape[0]
+    if k != w.shape[1] or (out.rows, out.cols) != (rows, cols) or out.n_splits != 1 or (swiglu and w.shape[0] % (2 * SWIGLU_GROUP)):
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.tensor.shape)} do not fit")
     if rows == 0:
         return
     if not out.tensor.is_cuda or out.tensor.dtype not in _CODES:
         raise KernelError("gemm_tc_pair: the output must be a bfloat16 or float32 CUDA tensor")
     _call("gemm_tc", "qt_gemm_tc_pair", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k,
-          _ptr(_status_word(a.device)), _stream())
+          1 if swiglu else 0, _ptr(_status_word(a.device)), _stream())
+
+
+def gemm_uses_pairs(a: torch.Tensor, w: torch.Tensor, n_splits: int = 1) -> bool:
+    """Whether ``gemm`` gives this product to the pair kernel (a static choice by element type and shape)."""
+    return gemm_tc_supported(a, w) and a.shape[0] > _TC_TILES[-1] and n_splits == 1
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
     """out = a @ w^T with the kernel that fits the element type and shape (a static choice):
     tensor cores for bfloat16 with 16-byte aligned rows, the FMA kernel for float32 and the rest."""
     if gemm_tc_supported(a, w):
-        if a.shape[0] > _TC_TILES[-1] and out.n_splits == 1:
+        if gemm_uses_pairs(a, w, out.n_splits):
             gemm_tc_pair(a, w, out)         # more tokens than one block's tile: pairs of blocks, a third less operand traffic
         else:
             gemm_tc(a, w, out)

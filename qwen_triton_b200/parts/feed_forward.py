@@ -1,6 +1,9 @@
 """Dense gated feed-forward: down(act(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:10-22).
 
-gate and up run as one product over the row-concatenated weight [gate; up].
+gate and up run as one product over the fused weight [gate; up].  In bfloat16 its rows alternate 16 of gate and
+16 of up, so that the GEMM for many tokens can apply the SiLU gate in its epilogue (one warp then holds both halves
+of 16 features) and write the activation directly; few tokens take the split-K product and the separate kernel,
+which reads the same layout.
 """
 from __future__ import annotations
 
@@ -26,6 +29,8 @@ class GatedMLP:
         if activation != "silu":
             raise ValueError(f"{prefix}: the gated feed-forward kernel computes SiLU, not {activation!r}")
         self.names = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
+        fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0
+        self.group = kernels.SWIGLU_GROUP if fused else 0
         self.gate_up = Linear("mlp.gate_up", 2 * self.inter, self.hidden, runtime)
         self.down = Linear("mlp.down", self.hidden, self.inter, runtime)
         runtime.workspace.declare("mlp.act", runtime.max_step_tokens * self.inter, runtime.dtype)
@@ -41,12 +46,14 @@ class GatedMLP:
     def load(self, source) -> None:
         n, p = self.names, self.prefix
         gate, up = source(f"{p}.{n['gate']}.weight"), source(f"{p}.{n['up']}.weight")
-        self.gate_up.set_weight(torch.cat((gate.to(self.runtime.dtype), up.to(self.runtime.dtype)), dim=0))
+        self.gate_up.set_weight(kernels.interleave_gate_up(gate.to(self.runtime.dtype), up.to(self.runtime.dtype), self.group))
         self.down.set_weight(source(f"{p}.{n['down']}.weight"))
 
     def forward(self, x: torch.Tensor, ctx) -> GemmOut:
         tokens = x.shape[0]
-        gate_up = self.gate_up(x)
         act = self.runtime.workspace.view("mlp.act", tokens, self.inter)
-        kernels.swiglu(gate_up, act)
+        if self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
+            kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True)
+        else:
+            kernels.swiglu(self.gate_up(x), act, self.group)
         return self.down(act)

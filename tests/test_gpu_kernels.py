@@ -150,15 +150,20 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits, lengths):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("tokens, inter", [(5, 336), (3, 301), (300, 2056)])     # vector form, scalar form, several blocks a row
-def test_swiglu(dtype, tokens, inter):
+@pytest.mark.parametrize("tokens, inter, group", [(5, 336, 0), (3, 301, 0), (300, 2056, 0), (5, 336, 16), (300, 2064, 16), (4, 300, 4)])
+def test_swiglu(dtype, tokens, inter, group):      # vector form, scalar form, several blocks a row; gate and up rows interleaved
     for splits in (1, 3):
         in_dtype = torch.float32 if splits > 1 else dtype
-        gate_up = rand(splits, tokens, 2 * inter, seed=9, scale=2.0, dtype=in_dtype)
+        gate = rand(splits, tokens, inter, seed=9, scale=2.0, dtype=in_dtype)
+        up = rand(splits, tokens, inter, seed=10, scale=2.0, dtype=in_dtype)
+        if group:
+            gate_up = torch.stack((gate.view(splits, tokens, inter // group, group), up.view(splits, tokens, inter // group, group)),
+                                  dim=3).reshape(splits, tokens, 2 * inter).contiguous()
+        else:
+            gate_up = torch.cat((gate, up), dim=-1).contiguous()
         out = torch.empty(tokens, inter, dtype=dtype, device=DEV)
-        kernels.swiglu(GemmOut(gate_up), out)
-        total = gate_up.float().sum(0)
-        close(out, torch.nn.functional.silu(total[:, :inter]) * total[:, inter:], dtype, f"splits={splits}")
+        kernels.swiglu(GemmOut(gate_up), out, group)
+        close(out, torch.nn.functional.silu(gate.float().sum(0)) * up.float().sum(0), dtype, f"splits={splits}")
 
 
 # ----------------------------------------------------------------------------- matrix product
@@ -377,6 +382,22 @@ def test_gemm_tensor_cores_block_pairs(m, n, k, out_dtype):
     kernels.gemm_tc_pair(a, w, GemmOut(out))
     kernels.check_status(DEV)
     close(out[0], expected, out_dtype, f"{m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("m, inter, k", [(300, 48, 72), (1000, 560, 1024), (2048, 1536, 256), (513, 4096 + 16, 64)])
+def test_gemm_block_pairs_with_the_silu_gate_in_the_epilogue(m, inter, k):
+    """gate and up rows interleaved in groups of 16: the pair kernel stores silu(x G^T) * (x U^T)."""
+    a = rand(m, k, seed=116, dtype=torch.bfloat16)
+    gate, up = rand(inter, k, seed=117, scale=0.1, dtype=torch.bfloat16), rand(inter, k, seed=118, scale=0.1, dtype=torch.bfloat16)
+    w = kernels.interleave_gate_up(gate, up, kernels.SWIGLU_GROUP).contiguous()
+    assert torch.equal(w[:16], gate[:16]) and torch.equal(w[16:32], up[:16]) and torch.equal(w[32:48], gate[16:32])
+    out = torch.full((1, m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc_pair(a, w, GemmOut(out), swiglu=True)
+    kernels.check_status(DEV)
+    expected = torch.nn.functional.silu(a.double() @ gate.double().T) * (a.double() @ up.double().T)
+    close(out[0], expected, torch.bfloat16, f"{m} tokens, {inter} features, K={k}")
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tc_pair(a, w[:-8], GemmOut(out[:, :, :-4].contiguous()), swiglu=True)
 
 
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])

@@ -115,14 +115,15 @@ def test_attention_part(dtype, window):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-def test_feed_forward_part(dtype):
-    rt = runtime(dtype)
-    params = {"hidden_size": 72, "intermediate_size": 200, "activation": "silu", "gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
+@pytest.mark.parametrize("inter, tokens", [(200, 11), (208, 11), (208, 300)])    # 208: gate and up interleaved in bfloat16; 300 tokens: gated in the GEMM
+def test_feed_forward_part(dtype, inter, tokens):
+    rt = runtime(dtype, max_tokens=512)
+    params = {"hidden_size": 72, "intermediate_size": inter, "activation": "silu", "gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
     ff = part_class("feed_forward", PartSpec("gated_mlp"))(params, "m", rt)
     w = weights_for(ff.expected_tensors(params, "m"), dtype, seed=5)
     ff.load(w.__getitem__)
     rt.workspace.allocate()
-    x = (torch.randn(11, 72, generator=torch.Generator().manual_seed(6))).to(DTYPES[dtype])
+    x = (torch.randn(tokens, 72, generator=torch.Generator().manual_seed(6))).to(DTYPES[dtype])
     out = ff.forward(x.to(DEV), None).value()
     assert_close(out, plain.gated_mlp(x.float(), {k: v.float() for k, v in w.items()}, "m"), dtype, "feed-forward part")
     with pytest.raises(ValueError, match="SiLU"):
