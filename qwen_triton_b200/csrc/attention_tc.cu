@@ -4,20 +4,25 @@
 // A block takes 128 query rows of one head and walks the keys in tiles of 128 (two pages):
 //
 //   S = Q K^T        tcgen05.mma, Q and K tiles in shared memory (TMA, 128-byte swizzle), S in tensor memory
-//   P = softmax(S)   four warps, one thread per query row: a row of S is read with tcgen05.ld, so the row
-//                    maximum and sum need no shuffles; P goes to shared memory as bfloat16 in the MMA's
-//                    swizzled K-major layout
-//   O += P V         tcgen05.mma with V as an MN-major operand (V is stored [key][dim]); the product lands in
-//                    tensor memory and is folded into the float accumulator O that each thread keeps for its row
+//   P = softmax(S)   four warps, one thread per query row: the row of S is read once with tcgen05.ld into
+//                    registers, so the row maximum and sum need no shuffles and no exchange; P goes to shared
+//                    memory as bfloat16 in the MMA's swizzled K-major layout
+//   O += P V         tcgen05.mma with V as an MN-major operand (V is stored [key][dim]), accumulated in tensor
+//                    memory over all tiles
 //
-// Warp roles (352 threads): warp 0 lane 0 = TMA producer of Q and of the K tiles, warp 10 lane 0 = TMA producer of
+// O stays in tensor memory, so the softmax threads touch it only when a row's maximum has to move: a row keeps
+// the maximum it scaled by until the true one is more than 2^8 above it (P then holds values up to 2^8, which
+// bfloat16 and the float accumulator carry; the row sum uses the same maximum, so the quotient is exact), and
+// only then is that row of O read, scaled and written back (tcgen05.ld / tcgen05.st).  After the first tiles of
+// a causal row this is rare.
+//
+// Warp roles (224 threads): warp 0 lane 0 = TMA producer of Q and of the K tiles, warp 6 lane 0 = TMA producer of
 // the V tiles (two-stage rings each; separate producers so that a key tile is requested as soon as its stage is
-// free, not behind a value tile), warp 1 = tensor-memory allocation and (lane 0) MMA issue, warps 2..9 = softmax
-// and output: two threads per
-// query row, each on 64 of the tile's 128 keys and on half of the output columns.  S is double
-// buffered: Q K^T of tile j+1 runs while the softmax of tile j is computed, and P V of tile j runs while the
-// maximum of tile j+1 is taken.  Key j is visible to the query at absolute position p iff j <= p and, in a
-// windowed group, j > p - window.  Every mbarrier wait is bounded and reports through a status word.
+// free, not behind a value tile), warp 1 = tensor-memory allocation and (lane 0) MMA issue, warps 2..5 = softmax
+// and output.  S is double buffered: Q K^T of tile j+1 runs while the softmax of tile j is computed, and P V of
+// tile j runs while the scores of tile j+1 are read and their maximum is taken.  Key j is visible to the query at
+// absolute position p iff j <= p and, in a windowed group, j > p - window.  Every mbarrier wait is bounded and
+// reports through a status word.
 //
 // Counterpart in luozoupi/Qwen-Triton: kernels/flash_attention.py:54-152 (32 x 32 tl.dot tiles) and the masked
 // SDPA branch of modules/attention.py:110-123.
@@ -33,7 +38,8 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int BQ = 128;            // query rows per block = MMA M
 constexpr int BKEY = 128;          // keys per tile = two pages
-constexpr int THREADS = 352;        // warp 0: TMA of Q and K, warp 1: MMA + tensor-memory allocation, warps 2..9: softmax, warp 10: TMA of V
+constexpr int THREADS = 224;        // warp 0: TMA of Q and K, warp 1: MMA + tensor-memory allocation, warps 2..5: softmax, warp 6: TMA of V
+constexpr float RESCALE_STEP = 8.f; // a row's scaling maximum moves only when the true one is more than 2^8 above it
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr uint32_t HALF_BYTES = 128 * 64 * 2;   // a [128 rows][64 columns] bfloat16 half tile: 16 KB
 
@@ -60,6 +66,28 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_load32_start(uint32_t taddr, uint32_t (&v)[32]) {     // results are valid after tmem_wait_ld()
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -98,7 +126,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
     constexpr uint32_t KV_BYTES = HALVES * HALF_BYTES;    // [128 keys][HD]
     constexpr uint32_t P_BYTES = 2 * HALF_BYTES;          // [128 rows][128 keys]
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t S_COL0 = 0, S_COL1 = 128, PV_COL = 256;
+    constexpr uint32_t S_COL0 = 0, S_COL1 = 128, O_COL = 256;
     // S = Q K^T: M 128, N 128 keys, both operands K-major.  O = P V: M 128, N HD, A K-major, B MN-major.
     constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKEY >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
     constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
@@ -124,12 +152,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
     uint8_t* smem = smem_raw + (base - raw);
     const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
     const uint32_t bars = p_s + P_BYTES;
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_full, x_bar[2], l_bar
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_full
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56;
     const uint32_t s_full = bars + 72, s_empty = bars + 88, p_full = bars + 104, pv_full = bars + 112;
-    const uint32_t x_bar = bars + 120, l_bar = bars + 136;   // the softmax threads' own exchanges: x_bar[2], l_bar
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + 144);
-    float* exchange = reinterpret_cast<float*>(smem + (bars - base) + 160);      // [2 parities][2 halves][128 rows]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + 128);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int* status = p.status;
@@ -139,11 +165,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
         for (int i = 0; i < 2; ++i) {
             mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
             mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
-            mbar_init(s_full + 8 * i, 1); mbar_init(s_empty + 8 * i, 8);
+            mbar_init(s_full + 8 * i, 1); mbar_init(s_empty + 8 * i, 4);
         }
-        mbar_init(p_full, 8);
+        mbar_init(p_full, 4);
         mbar_init(pv_full, 1);
-        mbar_init(x_bar, 8); mbar_init(x_bar + 8, 8); mbar_init(l_bar, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -173,7 +198,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                 }
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 6) {
         if (lane == 0) {
             pdl_wait();
             for (int j = 0; j < n_tiles; ++j) {
@@ -218,138 +243,121 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc_kernel(const __g
                 for (int ks = 0; ks < BKEY / 16; ++ks) {  // 16 keys per MMA
                     const uint64_t a_desc = operand_desc(p_s + (uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32u);
                     const uint64_t b_desc = operand_desc_mn(v_s + s * KV_BYTES + (uint32_t)ks * (16 * 128), HALF_BYTES);
-                    umma_bf16(tmem_base + PV_COL, a_desc, b_desc, IDESC_PV, ks > 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + O_COL, a_desc, b_desc, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);    // O accumulates over the tiles
                 }
                 umma_commit(pv_full);
                 umma_commit(v_empty + 8 * s);
             }
         }
-    } else if (warp < 10) {
-        constexpr int HC = HD / 2;                         // output columns of this thread
+    } else if (warp < 6) {
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;                  // which 64 keys of a tile, and which half of the output columns
         const int r = quarter * 32 + lane;                 // this thread's query row = its tensor-memory lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int qpos = min(past + q0 + r, p_last);       // rows beyond the sequence act as its last row
         const float scale2 = p.scale * LOG2E;
-        float o[HC];
-#pragma unroll
-        for (int c = 0; c < HC; ++c) o[c] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_pending = 1.f;
+        float m_run = -INFINITY, l_run = 0.f;              // the maximum this row scales by (scaled base-2 domain) and its sum
         pdl_wait();                                        // the output may still be read by an earlier kernel
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int s = j & 1;
             if (!mbar_wait(s_full + 8 * s, (uint32_t)(j >> 1) & 1u, status, 3)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + (s ? S_COL1 : S_COL0) + (uint32_t)(half * 64);
-            const int pos0 = (tile_begin + j) * BKEY + half * 64;
+            const uint32_t s_addr = lane_addr + (s ? S_COL1 : S_COL0);
+            const int pos0 = (tile_begin + j) * BKEY;
+            // the whole row of scores, once
+            uint32_t v[4][32];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tmem_load32_start(s_addr + (uint32_t)(q * 32), v[q]);
+            tmem_wait_ld();
+            // S is in registers: the buffer may take the scores of tile j + 2
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + 8 * s);
             // mask only where some row of the block cannot see the whole tile
-            const bool masked = (tile_begin + j) * BKEY + BKEY - 1 > p_first || (p.window > 0 && (tile_begin + j) * BKEY <= p_last - p.window);
-            // pass 1: the maximum of this thread's 64 scores, then of the whole row through shared memory
-            float mx = -INFINITY;
-            if (!masked) {                                 // the common case: one max per score
+            const bool masked = pos0 + BKEY - 1 > p_first || (p.window > 0 && pos0 <= p_last - p.window);
+            if (masked) {
 #pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_load32(s_addr + (uint32_t)c0, v);
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(v[c]));
-                }
-            } else {
-#pragma unroll 1
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_load32(s_addr + (uint32_t)c0, v);
+                for (int q = 0; q < 4; ++q)
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        const int pos = pos0 + c0 + c;
-                        const bool visible = pos <= qpos && (p.window <= 0 || pos > qpos - p.window);
-                        mx = fmaxf(mx, visible ? __uint_as_float(v[c]) : -INFINITY);
+                        const int pos = pos0 + q * 32 + c;
+                        if (!(pos <= qpos && (p.window <= 0 || pos > qpos - p.window))) v[q][c] = 0xff800000u;   // -inf
                     }
-                }
             }
-            exchange[(s * 2 + half) * 128 + r] = mx;
-            __syncwarp();                                  // the warp's values are written; one arrival per warp releases them
-            if (lane == 0) mbar_arrive(x_bar + 8 * s);
-            if (!mbar_wait(x_bar + 8 * s, (uint32_t)(j >> 1) & 1u, status, 3)) { ok = false; break; }
-            mx = fmaxf(mx, exchange[(s * 2 + (half ^ 1)) * 128 + r]);
-            const float m_new = fmaxf(m_run, mx * scale2);
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int c = 0; c < 32; ++c) mx[q] = fmaxf(mx[q], __uint_as_float(v[q][c]));
+            const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
+            // the row's maximum moves only when the true one has run away from it
+            const bool moves = m_tile > m_run + RESCALE_STEP;
+            const float m_new = moves ? m_tile : m_run;
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = fast_exp2(m_run - m_use);
-            // the product of the previous tile: fold it into O (this also frees P and the product buffer)
+            const float alpha = moves ? fast_exp2(m_run - m_use) : 1.f;
             if (j > 0) {
+                // P V of the tile before: P may be overwritten after it, and O may be scaled
                 if (!mbar_wait(pv_full, (uint32_t)(j - 1) & 1u, status, 3)) { ok = false; break; }
                 tc_fence_after();
+                if (__any_sync(0xffffffffu, moves)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t o[32];
+                        tmem_load32(lane_addr + O_COL + (uint32_t)c0, o);
 #pragma unroll
-                for (int c0 = 0; c0 < HC; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_load32(lane_addr + PV_COL + (uint32_t)(half * HC + c0), v);
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) o[c0 + c] = fmaf(o[c0 + c], alpha_pending, __uint_as_float(v[c]));
+                        for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                        tmem_store32(lane_addr + O_COL + (uint32_t)c0, o);
+                    }
+                    tmem_wait_st();
                 }
             }
-            // pass 2: P = 2^(s * scale2 - m), as bfloat16 into the swizzled K-major tile; the row sum
-            float sum = 0.f;
-            const uint32_t p_row = p_s + (uint32_t)half * HALF_BYTES + (uint32_t)r * 128u;
+            // P = 2^(s * scale2 - m) as bfloat16 into the swizzled K-major tile (two 64-key halves); the row sum
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = -m_use;
-#pragma unroll 1
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                uint32_t v[32];
-                tmem_load32(s_addr + (uint32_t)c0, v);
-                if (masked) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int pos = pos0 + c0 + c;
-                        if (!(pos <= qpos && (p.window <= 0 || pos > qpos - p.window))) v[c] = 0xff800000u;   // -inf
-                    }
-                }
+            for (int q = 0; q < 4; ++q) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float e0 = fast_exp2(fmaf(__uint_as_float(v[c]), scale2, neg_m));
-                    const float e1 = fast_exp2(fmaf(__uint_as_float(v[c + 1]), scale2, neg_m));
-                    sum += e0 + e1;
+                    const float e0 = fast_exp2(fmaf(__uint_as_float(v[q][c]), scale2, neg_m));
+                    const float e1 = fast_exp2(fmaf(__uint_as_float(v[q][c + 1]), scale2, neg_m));
+                    sum[c & 2 ? 1 : 0] += e0;
+                    sum[c & 2 ? 3 : 2] += e1;
                     packed[c >> 1] = pack_bf16(e0, e1);
                 }
                 // 32 keys = four 16-byte chunks of this row; the chunk index inside the 64-key half is XORed with row % 8
+                const uint32_t p_row = p_s + (uint32_t)(q >> 1) * HALF_BYTES + (uint32_t)r * 128u;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t chunk = (uint32_t)((c0 >> 3) + q4) ^ (uint32_t)(r & 7);
+                    const uint32_t chunk = (uint32_t)((q & 1) * 4 + q4) ^ (uint32_t)(r & 7);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + chunk * 16u), "r"(packed[4 * q4]),
                                  "r"(packed[4 * q4 + 1]), "r"(packed[4 * q4 + 2]), "r"(packed[4 * q4 + 3]) : "memory");
                 }
             }
-            // S is read: the buffer may take the scores of tile j + 2; P is written: hand it to the MMA
+            // P is written (and O scaled where it had to be): hand both to the MMA
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) { mbar_arrive(s_empty + 8 * s); mbar_arrive(p_full); }
-            l_run = l_run * alpha + sum;
+            if (lane == 0) mbar_arrive(p_full);
+            l_run = l_run * alpha + (sum[0] + sum[1]) + (sum[2] + sum[3]);
             m_run = m_new;
-            alpha_pending = alpha;
         }
         if (ok && mbar_wait(pv_full, (uint32_t)(n_tiles - 1) & 1u, status, 3)) {
             tc_fence_after();
-            // the two threads of a row add up their sums
-            exchange[half * 128 + r] = l_run;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(l_bar);
-            const bool both = mbar_wait(l_bar, 0, status, 3);
-            const float inv = both ? 1.f / (l_run + exchange[(half ^ 1) * 128 + r]) : 0.f;
-            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + q0 + r) * p.nq + head) * HD + half * HC;
-#pragma unroll
-            for (int c0 = 0; c0 < HC; c0 += 32) {
-                uint32_t v[32];
-                tmem_load32(lane_addr + PV_COL + (uint32_t)(half * HC + c0), v);
+            const float inv = 1.f / l_run;
+            __nv_bfloat16* dst = p.out + ((size_t)(q_begin + q0 + r) * p.nq + head) * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tmem_load32(lane_addr + O_COL + (uint32_t)c0, o);
                 if (r < rows) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint4 w;
-                        w.x = pack_bf16(fmaf(o[c0 + c], alpha_pending, __uint_as_float(v[c])) * inv, fmaf(o[c0 + c + 1], alpha_pending, __uint_as_float(v[c + 1])) * inv);
-                        w.y = pack_bf16(fmaf(o[c0 + c + 2], alpha_pending, __uint_as_float(v[c + 2])) * inv, fmaf(o[c0 + c + 3], alpha_pending, __uint_as_float(v[c + 3])) * inv);
-                        w.z = pack_bf16(fmaf(o[c0 + c + 4], alpha_pending, __uint_as_float(v[c + 4])) * inv, fmaf(o[c0 + c + 5], alpha_pending, __uint_as_float(v[c + 5])) * inv);
-                        w.w = pack_bf16(fmaf(o[c0 + c + 6], alpha_pending, __uint_as_float(v[c + 6])) * inv, fmaf(o[c0 + c + 7], alpha_pending, __uint_as_float(v[c + 7])) * inv);
+                        w.x = pack_bf16(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
                         *reinterpret_cast<uint4*>(dst + c0 + c) = w;
                     }
                 }
@@ -371,7 +379,7 @@ template <int HD>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcAttnParams& p, int n_seqs,
            int max_q_len, cudaStream_t stream) {
     constexpr uint32_t HALVES = HD / 64;
-    const size_t smem = (size_t)HALVES * HALF_BYTES * 5 + 2 * HALF_BYTES + 1024 + 160 + 2 * 2 * 128 * 4 + 64;
+    const size_t smem = (size_t)HALVES * HALF_BYTES * 5 + 2 * HALF_BYTES + 1024 + 128 + 64;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
