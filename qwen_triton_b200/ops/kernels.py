@@ -426,7 +426,8 @@ def check_status(device: torch.device | str = "cuda") -> None:
     code = int(word[0].item())
     if code != 0:
         word.zero_()
-        role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer (for a free accumulator)"}.get(code, f"role {code}")
+        role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer (for a free accumulator)",
+                5: "a kernel whose shared memory was less aligned than its launch allowed for"}.get(code, f"role {code}")
         raise KernelError(f"gemm_tc: a wait of {role} ran out; the result of that launch is invalid")
 
 
