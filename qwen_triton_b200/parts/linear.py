@@ -21,21 +21,27 @@ _MAX_SPLITS = 16
 _SPLIT_PLANS = ((16, 4 * _SM_COUNT), (64, 2 * _SM_COUNT))
 
 
-def pick_splits(out_features: int, in_features: int, target_blocks: int = 2 * _SM_COUNT) -> int:
-    """Split count for a product with few rows: the one whose blocks (128-row weight tiles x splits) fill
-    whole waves of ``target_blocks`` best, each split keeping at least four 64-wide K blocks; fewer splits win ties."""
+def pick_splits(out_features: int, in_features: int, target_blocks: int = 2 * _SM_COUNT, rows: int = 16) -> int:
+    """Split count for a product with few rows, by a cost in bytes: the weight, read at the rate its blocks
+    (128-row weight tiles x splits) keep ``target_blocks`` slots busy, plus the float partial sums of ``rows``
+    rows, written once and read once.  Each split keeps at least four 64-wide K blocks; fewer splits win near-ties.
+    (Filling waves alone would cut a product that already has blocks for several waves into many splits, whose
+    partial sums then cost more than the weight: 14 splits for a 51,200 x 5,120 weight at 64 rows.)"""
     tiles = -(-out_features // 128)
     blocks_k = -(-in_features // 64)
-    best, best_fill = 1, 0.0
+    weight_bytes = 2.0 * out_features * in_features
+    best, best_cost = 1, float("inf")
     for splits in range(1, _MAX_SPLITS + 1):
         if splits > 1 and blocks_k // splits < 4:
             break
         if kernels.tc_normalise_splits(in_features, splits) != splits:
             continue
-        blocks = tiles * splits
-        fill = blocks / (-(-blocks // target_blocks) * target_blocks)
-        if fill > best_fill + 0.03:
-            best, best_fill = splits, fill
+        waves = tiles * splits / target_blocks
+        fill = waves if waves <= 1.0 else waves / (waves + 0.35)     # under one wave: idle slots; over: a tail of about a third of a wave
+        partial_bytes = 2.0 * 4 * splits * rows * out_features if splits > 1 else 0.0
+        cost = weight_bytes / fill + partial_bytes
+        if cost < best_cost * 0.99:
+            best, best_cost = splits, cost
     return best
 
 
@@ -54,7 +60,7 @@ class Linear:
         # few rows (decode): split K over more blocks so that every SM streams weights; partial sums are float
         self.split_plans: list[tuple[int, int]] = []          # (most rows, splits), fewest rows first
         if runtime.dtype == torch.bfloat16 and in_features % 8 == 0:
-            self.split_plans = [(rows, pick_splits(out_features, in_features, target)) for rows, target in _SPLIT_PLANS]
+            self.split_plans = [(rows, pick_splits(out_features, in_features, target, rows)) for rows, target in _SPLIT_PLANS]
         words = max((rows * splits for rows, splits in self.split_plans if splits > 1), default=0)
         if words:
             runtime.workspace.declare(f"{key}.partial", words * out_features, torch.float32)
