@@ -68,3 +68,56 @@ def test_benchmark_layer_shapes_against_the_plain_implementation(big, dtype):
             assert engine_error <= 4 * plain_error + 1e-6, (i, engine_error, plain_error)
         else:
             assert engine_error <= 2e-2 * scale, (i, engine_error, scale)
+
+
+@pytest.fixture(scope="module")
+def mid():
+    """Sizes at which the kernels for many tokens and for wide rows take over: hidden 1,024 (a cluster of blocks per
+    row in the norms of a decode step), 8/2 heads of 128 (tcgen05 attention, rotation pairs in registers),
+    intermediate 2,832 = 16 x 177 (gate and up rows interleaved, the SiLU gate in the GEMM's epilogue)."""
+    full = load_preset("qwen3-8b")
+    config = dataclasses.replace(full, num_hidden_layers=2, layer_types=full.layer_types[:2], vocab_size=5003, hidden_size=1024,
+                                 num_attention_heads=8, num_key_value_heads=2, intermediate_size=2832, eos_token_id=())
+    with tempfile.TemporaryDirectory(prefix="qt_mid_") as folder:
+        write_random_model(folder, config, seed=6, dtype=torch.bfloat16)
+        checkpoint = Checkpoint(folder)
+        weights = {name: checkpoint.read(name).float() for name in checkpoint.names()}
+        yield config, folder, weights
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_long_prompts_take_the_kernels_for_many_tokens(mid, dtype):
+    """Two prompts of 300 and 290 tokens in one step (more than 256 tokens: block pairs in the products, the gated
+    epilogue, the tcgen05 attention), then one token each, against the plain implementation in float64."""
+    config, folder, weights = mid
+    raw = config.to_hf_dict()
+    engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=2048)
+    requests = [tokens_for(config, 306, 3), tokens_for(config, 293, 4)]
+    truth = [plain.forward(raw, weights, r, dtype=torch.float64) for r in requests]
+    plain32 = [plain.forward(raw, weights, r) for r in requests]
+    slots = [engine.new_sequence() for _ in requests]
+    prompt = [300, 290]
+    want = [[0, 1, 128, 255, 256, 299], [0, 63, 64, 289]]
+    first = engine.step([StepEntry(s, r[:p], w) for s, r, p, w in zip(slots, requests, prompt, want)])
+    got = {0: [first[:len(want[0])]], 1: [first[len(want[0]):]]}
+    places = {0: list(want[0]), 1: list(want[1])}
+    at = list(prompt)
+    while any(a < len(r) for a, r in zip(at, requests)):
+        live = [i for i in (0, 1) if at[i] < len(requests[i])]
+        out = engine.step([StepEntry(slots[i], [requests[i][at[i]]], [0]) for i in live])
+        for row, i in enumerate(live):
+            got[i].append(out[row:row + 1])
+            places[i].append(at[i])
+            at[i] += 1
+    for slot in slots:
+        engine.release(slot)
+    engine.check_kernels()
+    for i in (0, 1):
+        reference = truth[i][places[i]]
+        engine_error = float((torch.cat(got[i]).double().cpu() - reference).abs().max())
+        scale = float(reference.abs().max())
+        if dtype == "fp32":
+            plain_error = float((plain32[i].double()[places[i]] - reference).abs().max())
+            assert engine_error <= 4 * plain_error + 1e-6, (i, engine_error, plain_error)
+        else:
+            assert engine_error <= 2e-2 * scale, (i, engine_error, scale)
