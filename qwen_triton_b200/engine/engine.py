@@ -55,6 +55,8 @@ def require_gpu(device: torch.device) -> None:
 class PlannedDecode:
     """A one-token step that has been prepared up to the tokens' values (``Engine.plan_decode``)."""
 
+    slots: tuple            # the sequences, in the order their tokens are given
+    lengths: tuple          # their lengths once the step has run; checked again when it runs
     count: int              # sequences
     padded: int             # rows the step runs (a power of two)
     key: tuple              # shape the CUDA graph is kept under
@@ -294,6 +296,10 @@ class Engine:
         low, high = min(tokens), max(tokens)
         if low < 0 or high >= self.spec.vocab_size:
             raise ValueError(f"token id {low if low < 0 else high} is outside 0..{self.spec.vocab_size - 1}")
+        book = self.cache.book
+        for slot, length in zip(plan.slots, plan.lengths):
+            if not book.is_live(slot) or book.length(slot) != length:
+                raise ValueError(f"slot {slot} has changed since this step was planned (released, or stepped in between)")
         self.steps_run += 1
         logits = self._run_planned(plan, tokens)
         self._mirror_status()
@@ -327,7 +333,8 @@ class Engine:
         context = -(-(max(past) + 1) // 1024) * 1024
         pad = padded - count
         prepared = self._ctx.prepare_decode(slots + [0] * pad, past + [0] * pad, tables)
-        return PlannedDecode(count=count, padded=padded, key=(padded, tuple(widths), context), context=context, prepared=prepared)
+        return PlannedDecode(slots=tuple(slots), lengths=tuple(p + 1 for p in past), count=count, padded=padded,
+                             key=(padded, tuple(widths), context), context=context, prepared=prepared)
 
     def _run_planned(self, plan: "PlannedDecode", tokens: list[int]) -> torch.Tensor:
         cache, count, padded = self.cache, plan.count, plan.padded

@@ -217,6 +217,36 @@ def test_stop_token_ends_a_sequence_early():
     assert model.engine.cache.book.live_slots() == []
 
 
+def test_a_planned_step_equals_a_plain_one_and_refuses_a_changed_slot(case):
+    preset, dtype, engine = case
+    prompts = [random_tokens(preset, 7, 910), random_tokens(preset, 3, 911)]
+    nexts = [5, 9]
+    outs = []
+    for planned in (False, True):
+        slots = [engine.new_sequence() for _ in prompts]
+        engine.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+        for _ in range(3):                         # a shape is launched, then captured, then replayed
+            if planned:
+                plan = engine.plan_decode(slots)
+                logits = engine.run_planned(plan, nexts) if plan is not None else engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nexts)])
+            else:
+                logits = engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, nexts)])
+            outs.append(logits.clone())
+        if planned and engine.plan_decode(slots[:1]) is not None:
+            dropped = engine.plan_decode(slots, extend=True)      # an abandoned plan leaves the extra position behind ...
+            again = engine.plan_decode(slots, extend=False)       # ... which a new plan for the same sequences must not take twice
+            assert again.lengths == dropped.lengths
+            engine.release(slots[1])
+            with pytest.raises(ValueError, match="changed since"):
+                engine.run_planned(again, nexts)
+            engine.release(slots[0])
+        else:
+            for slot in slots:
+                engine.release(slot)
+    for a, b in zip(outs[:3], outs[3:]):
+        assert_close(b, a, dtype, "planned against plain one-token steps")
+
+
 def test_errors_are_loud(case):
     preset, dtype, engine = case
     slot = engine.new_sequence()
