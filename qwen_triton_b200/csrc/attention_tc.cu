@@ -228,6 +228,10 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // This thread's instructions are the tensor pipe's critical path: operand descriptors are formed once and
+            // stepped by additions (their address field counts 16-byte units).
+            const uint64_t q_desc0 = operand_desc(q_s), k_desc0 = operand_desc(k_s), p_desc0 = operand_desc(p_s);
+            const uint64_t v_desc0 = operand_desc_mn(v_s, KEY_HALF_BYTES);
             bool ok = mbar_wait(q_full, 0, status, 2);
             auto issue_qk = [&](int i) {
                 const int s = i & 1;
@@ -236,11 +240,12 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
                 if (!mbar_wait(s_empty + 8 * s, phase ^ 1u, status, 2)) return false;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (s ? S_COL1 : S_COL0);
+                const uint64_t k_desc = k_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {    // 16 dims per MMA; 4 MMAs per 64-column half
                     const uint32_t in_half = (uint32_t)(ks & 3) * 32u;
-                    umma_bf16(acc, operand_desc(q_s + (uint32_t)(ks >> 2) * HALF_BYTES + in_half),
-                              operand_desc(k_s + s * KV_BYTES + (uint32_t)(ks >> 2) * KEY_HALF_BYTES + in_half), IDESC_QK, ks > 0 ? 1u : 0u);
+                    umma_bf16(acc, q_desc0 + (uint64_t)(((uint32_t)(ks >> 2) * HALF_BYTES + in_half) >> 4),
+                              k_desc + (uint64_t)(((uint32_t)(ks >> 2) * KEY_HALF_BYTES + in_half) >> 4), IDESC_QK, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(s_full + 8 * s);
                 umma_commit(k_empty + 8 * s);
@@ -253,10 +258,11 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
                 if (!mbar_wait(p_full, (uint32_t)j & 1u, status, 2)) break;
                 if (!mbar_wait(v_full + 8 * s, (uint32_t)(j >> 1) & 1u, status, 2)) break;
                 tc_fence_after();
+                const uint64_t v_desc = v_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
 #pragma unroll
                 for (int ks = 0; ks < BKEY / 16; ++ks) {  // 16 keys per MMA
-                    const uint64_t a_desc = operand_desc(p_s + (uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32u);
-                    const uint64_t b_desc = operand_desc_mn(v_s + s * KV_BYTES + (uint32_t)ks * (16 * 128), KEY_HALF_BYTES);
+                    const uint64_t a_desc = p_desc0 + (uint64_t)(((uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32u) >> 4);
+                    const uint64_t b_desc = v_desc + (uint64_t)(((uint32_t)ks * (16 * 128)) >> 4);
                     umma_bf16(tmem_base + O_COL, a_desc, b_desc, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);    // O accumulates over the tiles
                 }
                 umma_commit(pv_full);

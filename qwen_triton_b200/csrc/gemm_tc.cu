@@ -108,17 +108,21 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            // This thread's instructions are the tensor pipe's critical path: descriptors are formed once and
+            // stepped by additions (the address field counts 16-byte units), stage and phase by counters.
+            const uint64_t a_desc0 = operand_desc(base), b_desc0 = operand_desc(base + W_BYTES);
+            int s = 0;
+            uint32_t phase = 0;
             for (int i = 0; i < nkb; ++i) {
-                const int s = i % stages;
-                const uint32_t phase = (uint32_t)(i / stages) & 1u;
                 if (!mbar_wait(full0 + 8 * s, phase, status, 2)) break;
                 tc_fence_after();
-                const uint64_t a_desc = operand_desc(base + s * STAGE_BYTES);
-                const uint64_t b_desc = operand_desc(base + s * STAGE_BYTES + W_BYTES);
+                const uint64_t a_desc = a_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+                const uint64_t b_desc = b_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
 #pragma unroll
                 for (int k = 0; k < BK / UMMA_K; ++k)      // 32 bytes further along K inside the swizzled row
                     umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(empty0 + 8 * s);               // the stage is free once these MMAs have read it
+                if (++s == stages) { s = 0; phase ^= 1u; }
             }
             umma_commit(tmem_full);                        // the accumulator is complete
         }
@@ -263,7 +267,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
-            int g = 0, it = 0;
+            // This thread's instructions are the tensor pipe's critical path (four MMAs of 128 cycles per K slice): the
+            // descriptors are formed once and stepped by additions, stage and phase are counters, and a barrier that
+            // is already complete costs one probe.
+            const uint64_t a_desc0 = operand_desc(base), b_desc0 = operand_desc(base + W_BYTES);
+            int it = 0, s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
                 const int b = it & 1;
@@ -271,17 +280,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
                 if (!mbar_wait(acc_empty0 + 8 * b, (((uint32_t)it >> 1) & 1u) ^ 1u, status, 4)) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b * PAIR_X);
-                for (int kb = 0; kb < nkb; ++kb, ++g) {
-                    const int s = g % S;
-                    const uint32_t phase = (uint32_t)(g / S) & 1u;
+                for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(full0 + 8 * s, phase, status, 2)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t a_desc = operand_desc(base + s * PAIR_STAGE_BYTES);
-                    const uint64_t b_desc = operand_desc(base + s * PAIR_STAGE_BYTES + W_BYTES);
+                    const uint64_t a_desc = a_desc0 + (uint64_t)(s * (PAIR_STAGE_BYTES >> 4));
+                    const uint64_t b_desc = b_desc0 + (uint64_t)(s * (PAIR_STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
                         umma_bf16_pair(tmem_d, a_desc + 2 * k, b_desc + 2 * k, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(empty0 + 8 * s);        // the stage is free in both blocks once these MMAs have read it
+                    if (++s == S) { s = 0; phase ^= 1u; }
                 }
                 if (ok) umma_commit_pair(acc_full0 + 8 * b); // both halves of this accumulator are complete
             }

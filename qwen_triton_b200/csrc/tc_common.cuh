@@ -40,8 +40,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false if the limit ran out or another role already reported a fault.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+// Bounded wait.  Returns false if the limit ran out or another role already reported a fault.  The first probe is
+// inline: for the single thread that issues the MMAs every instruction is on the critical path of the tensor pipe,
+// and a barrier that is already complete (the common case for it) must cost one probe, not a call.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* status, int code) {
     unsigned long long start = 0;
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -52,6 +54,10 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* statu
             else if (now - start > WAIT_LIMIT_NS) { atomicCAS(status, 0, code); return false; }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, status, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c_inner, int c_outer) {
