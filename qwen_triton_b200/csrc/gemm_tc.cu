@@ -307,19 +307,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
             tc_fence_after();
             const int n = w_tile * 2 * BW + (int)rank * BW + quarter * 32 + lane;
             const int x0 = x_tile * PAIR_X;
-            // SWIGLU: lanes 0..15 hold the gate rows of 16 features, lanes 16..31 the up rows of the same features
+            // SWIGLU: lanes 0..15 hold the gate rows of 16 features, lanes 16..31 the up rows of the same features.
+            // Of every two tokens the lower lanes finish the first and the upper lanes the second: one exchange
+            // gives each half the value it lacks, and all 32 lanes compute and store.
             const int feature = ((n - lane) >> 1) + (lane & 15), features = N >> 1;
-            const bool stores = SWIGLU ? ((lane & 16) == 0 && feature < features) : n < N;
+            const bool upper = (lane & 16) != 0;
+            const bool stores = SWIGLU ? feature < features : n < N;
 #pragma unroll 1
             for (int c = 0; c < PAIR_X; c += 16) {
                 uint32_t v[16];
                 tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * PAIR_X + c), v);
                 if (SWIGLU) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float g = __uint_as_float(v[j]);
-                        const float u = __shfl_xor_sync(0xffffffffu, g, 16);
-                        const int m = x0 + c + j;
+                    for (int j = 0; j < 16; j += 2) {
+                        const float mine0 = __uint_as_float(v[j]), mine1 = __uint_as_float(v[j + 1]);
+                        const float got = __shfl_xor_sync(0xffffffffu, upper ? mine0 : mine1, 16);
+                        const float g = upper ? got : mine0;          // lower lanes: token j (their gate, the partner's up)
+                        const float u = upper ? mine1 : got;          // upper lanes: token j + 1 (the partner's gate, their up)
+                        const int m = x0 + c + j + (upper ? 1 : 0);
                         if (stores && m < M) out[(size_t)m * features + feature] = from_float<TO>(__fdividef(g, 1.f + __expf(-g)) * u);
                     }
                 } else if (stores) {
