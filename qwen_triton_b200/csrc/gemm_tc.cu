@@ -96,14 +96,15 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             pdl_wait();
             for (int i = 0; i < ahead; ++i)
                 tma_load_2d(base + i * STAGE_BYTES + W_BYTES, &map_x, full0 + 8 * i, (kb_begin + i) * BK, x0);
+            int s = ahead == stages ? 0 : ahead;            // stage and phase of K slice `ahead`, then counted on
+            uint32_t phase = ahead == stages ? 1u : 0u;
             for (int i = ahead; i < nkb; ++i) {
-                const int s = i % stages;
-                const uint32_t phase = (uint32_t)(i / stages) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) break;
                 mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                 const uint32_t dst = base + s * STAGE_BYTES;
                 tma_load_2d(dst, &map_w, full0 + 8 * s, (kb_begin + i) * BK, w0);
                 tma_load_2d(dst + W_BYTES, &map_x, full0 + 8 * s, (kb_begin + i) * BK, x0);
+                if (++s == stages) { s = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -232,7 +233,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
     if (warp == 0) {
         if (lane == 0) {
             const uint32_t leader_full0 = map_to_cta(full0, 0);
-            int g = 0;                                       // K slices staged so far, over all tiles
+            int s = 0;                                       // stage and phase of the next K slice, over all tiles
+            uint32_t phase = 0;
             bool ok = true;
             for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
                 int w_tile, x_tile;
@@ -251,16 +253,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
                     for (int i = 0; i < ahead; ++i)
                         tma_load_2d_pair(base + i * PAIR_STAGE_BYTES + W_BYTES, &map_x, leader_full0 + 8 * i, i * BK, x_stage0);
                     kb = ahead;
-                    g = ahead;
+                    if (ahead == S) phase = 1u; else s = ahead;
                 }
-                for (; kb < nkb; ++kb, ++g) {
-                    const int s = g % S;
-                    const uint32_t phase = (uint32_t)(g / S) & 1u;
+                for (; kb < nkb; ++kb) {
                     if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) { ok = false; break; }
                     if (leader) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
                     const uint32_t dst = base + s * PAIR_STAGE_BYTES;
                     tma_load_2d_pair(dst, &map_w, leader_full0 + 8 * s, kb * BK, w0);
                     tma_load_2d_pair(dst + W_BYTES, &map_x, leader_full0 + 8 * s, kb * BK, x_stage0);
+                    if (++s == S) { s = 0; phase ^= 1u; }
                 }
             }
             if (pair >= n_tiles) pdl_wait();
