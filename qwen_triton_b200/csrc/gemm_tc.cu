@@ -3,7 +3,7 @@
 // The weight is the MMA's A operand (128 weight rows fill the instruction's M), the activations
 // are its B operand (16 to 256 tokens on the instruction's N), so one kernel serves a decode step
 // of a few tokens and a prefill of thousands.  Both operands are K-major in global memory, as the
-// checkpoint stores them; TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) stages
+// checkpoint stores them; TMA (cp.async.bulk.tensor, 128-byte swizzle; every block fetches its own tiles) stages
 // 64-element K slices in shared memory, one elected thread issues tcgen05.mma with the float
 // accumulator in tensor memory, and four warps read it back with tcgen05.ld and store Y
 // (transposed back to [M, N]) as bfloat16 or float.  Split-K writes float partial sums
