@@ -113,4 +113,27 @@ extern "C" int qt_sample(const float* logits, const float* temperature, const fl
     return QT_OK;
 }
 
+// ----------------------------------------------------------------------------- chosen tokens as the next step's input
+// ids[i] holds a row number of `chosen` (or a negative number); it is replaced by the token chosen for that row
+// (0 for a negative number or a row that does not exist).  With this the next step can be launched before the host
+// has seen the tokens.  Tokens outside the vocabulary (the sampling kernels produce none) are clamped into it.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ chosen, int n, int n_chosen, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int row = ids[i];
+    int token = (row >= 0 && row < n_chosen) ? chosen[row] : 0;
+    token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);
+    ids[i] = token;
+}
+
+extern "C" int qt_feed_tokens(int* ids, const int* chosen, int n, int n_chosen, int vocab, void* stream) {
+    QT_REQUIRE(n >= 0 && n_chosen >= 0 && vocab > 0, "feed_tokens: bad sizes n=%d rows=%d V=%d", n, n_chosen, vocab);
+    if (n == 0) return QT_OK;
+    launch_kernel(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, ids, chosen, n, n_chosen, vocab);
+    QT_CHECK_LAUNCH("feed_tokens");
+    return QT_OK;
+}
+
 QT_DEFINE_LAST_ERROR(sampling)

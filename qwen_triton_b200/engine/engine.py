@@ -163,13 +163,17 @@ class Engine:
     def can_hold(self, lengths_by_slot: dict[int, int]) -> bool:
         return self.cache.book.can_hold(lengths_by_slot)
 
-    def check_kernels(self) -> None:
+    accepts_chosen_tokens = True       # run_planned(plan, rows, chosen=...) takes token ids that are still on the device
+
+    def check_kernels(self, wait: bool = True) -> None:
         """Raise if a bounded wait inside a tensor-core kernel ran out during a step (its results are then invalid).
         Every step ends with a copy of the status word into pinned memory; this waits for the latest of those
-        copies (no wait at all where the caller has already read the step's results) and looks at the host's copy."""
+        copies and looks at the host's copy.  ``wait=False`` only looks: enough for a caller that has read a step's
+        results (the copy of that step has then happened) and must not wait for a later step that is already queued."""
         if self._status_event is None:
             return
-        self._status_event.synchronize()
+        if wait:
+            self._status_event.synchronize()
         if int(self._status_host[0]) != 0:
             kernels.check_status(self.device)            # reads the word itself, clears it and raises with the role that gave up
 
@@ -287,21 +291,27 @@ class Engine:
             raise RuntimeError("the cache cannot hold this step: too many tokens are live (raise max_tokens)")
         return self._plan_decode(slots, extend)
 
-    def run_planned(self, plan: "PlannedDecode", tokens: Sequence[int]) -> torch.Tensor:
+    def run_planned(self, plan: "PlannedDecode", tokens: Sequence[int], chosen: torch.Tensor | None = None) -> torch.Tensor:
         """The other half: the tokens (one per planned sequence, in the plan's order) go in and the step runs.
-        Returns float logits [sequences, vocab]."""
+        Returns float logits [sequences, vocab].
+
+        With ``chosen`` (int32 on the device, as a sampling kernel leaves it) ``tokens`` are row numbers of it: the
+        step is then queued behind that kernel without the host having seen the tokens."""
         tokens = [int(t) for t in tokens]
         if len(tokens) != plan.count:
             raise ValueError(f"{len(tokens)} tokens for a plan of {plan.count} sequences")
         low, high = min(tokens), max(tokens)
-        if low < 0 or high >= self.spec.vocab_size:
+        if chosen is not None:
+            if chosen.dtype != torch.int32 or chosen.device != self.device or low < 0 or high >= chosen.numel():
+                raise ValueError("chosen tokens must be int32 on the engine's device, and every row number within them")
+        elif low < 0 or high >= self.spec.vocab_size:
             raise ValueError(f"token id {low if low < 0 else high} is outside 0..{self.spec.vocab_size - 1}")
         book = self.cache.book
         for slot, length in zip(plan.slots, plan.lengths):
             if not book.is_live(slot) or book.length(slot) != length:
                 raise ValueError(f"slot {slot} has changed since this step was planned (released, or stepped in between)")
         self.steps_run += 1
-        logits = self._run_planned(plan, tokens)
+        logits = self._run_planned(plan, tokens, chosen)
         self._mirror_status()
         return logits
 
@@ -336,9 +346,10 @@ class Engine:
         return PlannedDecode(slots=tuple(slots), lengths=tuple(p + 1 for p in past), count=count, padded=padded,
                              key=(padded, tuple(widths), context), context=context, prepared=prepared)
 
-    def _run_planned(self, plan: "PlannedDecode", tokens: list[int]) -> torch.Tensor:
+    def _run_planned(self, plan: "PlannedDecode", tokens: list[int], chosen: torch.Tensor | None = None) -> torch.Tensor:
         cache, count, padded = self.cache, plan.count, plan.padded
-        self._ctx.commit_decode(plan.prepared, tokens + [0] * (padded - count), plan.context)
+        fill = -1 if chosen is not None else 0                  # padded rows: token 0 either way
+        self._ctx.commit_decode(plan.prepared, tokens + [fill] * (padded - count), plan.context, chosen, self.spec.vocab_size)
         self.last_meta_bytes = self._ctx.meta_bytes
         key = plan.key
         state = self._graphs.get(key)

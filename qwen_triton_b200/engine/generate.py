@@ -11,6 +11,8 @@ rectangular batch with no stop condition.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Sequence
 
@@ -84,6 +86,8 @@ class BatchRun:
         self.slot_of: dict[int, int] = {}
         self._entries: list[StepEntry] = []
         self._plan = None           # the next one-token step, prepared while the device ran the last one
+        self._ahead = None          # (logits, request per row) of a step that is already queued on the device
+        self.pipelined = bool(getattr(engine, "accepts_chosen_tokens", False)) and os.environ.get("QT_B200_PIPELINE", "1") != "0"
 
     @property
     def done(self) -> bool:
@@ -110,28 +114,47 @@ class BatchRun:
 
         While the device runs the step and the choice of tokens, the host prepares the next one-token step for the
         requests that can only end by a stop token (``plan_decode``, where the engine offers it): that is all of a
-        step's host work except putting the tokens in.  If a stop token then ends a request, the plan is dropped
-        and made again for those that go on."""
-        if self._plan is not None:
-            logits = self.engine.run_planned(self._plan, [self.results[i].tokens[-1] for i in self.active])
+        step's host work except putting the tokens in.  Where the engine takes the chosen tokens on the device
+        (``accepts_chosen_tokens``) that next step is queued at once, behind the sampling kernel, and only then does
+        the host wait for the tokens: the device never waits for the host.  A request that a stop token ends is then
+        still a row of the step that is already queued; that row's result is dropped.  Without that, a stop token
+        drops the plan, which is made again for those that go on."""
+        engine = self.engine
+        if self._ahead is not None:                      # queued before the last tokens were read
+            logits, order = self._ahead
+            self._ahead = None
         else:
-            logits = self.engine.step(self._entries)
+            order = list(self.active)
+            if self._plan is not None:
+                logits = engine.run_planned(self._plan, [self.results[i].tokens[-1] for i in order])
+            else:
+                logits = engine.step(self._entries)
         self._plan = None
-        steps = [len(self.results[i].tokens) for i in self.active]
+        alive = set(self.active)
+        steps = [len(self.results[i].tokens) for i in order]
         launch = getattr(self.sampler, "launch", None)
-        planner = getattr(self.engine, "plan_decode", None)
+        planner = getattr(engine, "plan_decode", None)
         plan, expected = None, None
         if launch is not None and planner is not None:
-            pending = launch(logits, self.sampling, self.active, steps)
-            expected = [i for i in self.active if not self._ends_whatever_it_emits(i)]
+            pending = launch(logits, self.sampling, order, steps)
+            expected = [i for i in order if i in alive and not self._ends_whatever_it_emits(i)]
             if expected:
                 plan = planner([self.slot_of[i] for i in expected])
+            chosen = getattr(pending, "device", None)
+            if plan is not None and chosen is not None and self.pipelined:
+                row_of = {index: row for row, index in enumerate(order)}
+                self._ahead = (engine.run_planned(plan, [row_of[i] for i in expected], chosen=chosen), list(expected))
+                plan = None
             tokens = pending.tokens()
         else:
-            tokens = self.sampler.sample(logits, self.sampling, self.active, steps)
-        self.engine.check_kernels()                      # the tokens are on the host: the step has finished
+            tokens = self.sampler.sample(logits, self.sampling, order, steps)
+        engine.check_kernels(wait=False)                 # the tokens are on the host: their step has finished
         still: list[int] = []
-        for index, token in zip(self.active, tokens):
+        emitted: list[int] = []
+        for index, token in zip(order, tokens):
+            if index not in alive:                       # ended by a stop token while this step was already queued
+                continue
+            emitted.append(int(token))
             result = self.results[index]
             result.tokens.append(int(token))
             reason = finish_reason(int(token), len(result.tokens), len(self.prompts[index]) + len(result.tokens),
@@ -143,11 +166,12 @@ class BatchRun:
             else:
                 still.append(index)
         self.active = still
-        if plan is not None and still != expected:       # a stop token: those that go on already have their next position
-            plan = planner([self.slot_of[i] for i in still], extend=False) if still else None
-        self._plan = plan
-        self._entries = [StepEntry(self.slot_of[i], [self.results[i].tokens[-1]], [0]) for i in still]
-        return tokens
+        if self._ahead is None:
+            if plan is not None and still != expected:   # a stop token: those that go on already have their next position
+                plan = planner([self.slot_of[i] for i in still], extend=False) if still else None
+            self._plan = plan
+            self._entries = [StepEntry(self.slot_of[i], [self.results[i].tokens[-1]], [0]) for i in still]
+        return emitted
 
     def close(self) -> None:
         """Give back whatever the batch still holds (after an error, or when the caller stops early)."""
@@ -155,6 +179,7 @@ class BatchRun:
             self.engine.release(slot)
         self.slot_of = {}
         self.active = []
+        self._plan = self._ahead = None
 
 
 def stop_set(engine, stop_token_ids: Sequence[int] | None, ignore_eos: bool) -> frozenset[int]:

@@ -131,13 +131,19 @@ class StepContext:
             array[offset:offset + table.size] = table.reshape(-1)
         return plan, host, array, event
 
-    def commit_decode(self, prepared, tokens: list[int], max_context: int) -> None:
-        """Put the tokens in, copy the pass to the device in one transfer and make it the current pass."""
+    def commit_decode(self, prepared, tokens: list[int], max_context: int, chosen: torch.Tensor | None = None,
+                      vocab: int = 0) -> None:
+        """Put the tokens in, copy the pass to the device in one transfer and make it the current pass.
+        With ``chosen`` (int32 on the device) ``tokens`` are row numbers of it (negative: token 0): the ids are then
+        filled in on the device, from what a sampling kernel has written or is about to write."""
         plan, host, array, event = prepared
         n = plan.n
         array[0:n] = tokens
         self._meta[:plan.total].copy_(host, non_blocking=True)
         event.record()
+        if chosen is not None:
+            from ..ops import kernels
+            kernels.feed_tokens(plan.views[0], chosen, vocab)
         self.meta_bytes = 4 * plan.total
         (self.token_ids, self.token_seq, self.token_pos, self.seq_start, self.seq_past, self.seq_len,
          self.slots, self.want_rows) = plan.views[:8]

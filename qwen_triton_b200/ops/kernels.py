@@ -58,6 +58,7 @@ _SIGNATURES = {
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_sample": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_feed_tokens": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
     },
 }
 _BOUND: dict[str, ctypes._CFuncPtr] = {}
@@ -392,6 +393,13 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     _need(logits, "logits", torch.float32)
     _need(out, "out", torch.int32, (logits.shape[0],))
     _call("sampling", "qt_argmax", _ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream())
+
+
+def feed_tokens(ids: torch.Tensor, chosen: torch.Tensor, vocab: int) -> None:
+    """ids[i] (a row number of ``chosen``, or negative) becomes the token chosen for that row (0 if negative)."""
+    _need(ids, "ids", torch.int32)
+    _need(chosen, "chosen", torch.int32)
+    _call("sampling", "qt_feed_tokens", _ptr(ids), _ptr(chosen), ids.numel(), chosen.numel(), int(vocab), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor, out: torch.Tensor) -> None:

@@ -44,8 +44,9 @@ def uniform_for(seed: int, request: int, step: int) -> float:
 class PendingTokens:
     """Token ids on their way to the host: ``tokens()`` waits for the copy and returns them."""
 
-    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, rows: int) -> None:
+    def __init__(self, host: torch.Tensor, event: torch.cuda.Event, rows: int, device: torch.Tensor | None = None) -> None:
         self._host, self._event, self._rows = host, event, rows
+        self.device = device        # the ids on the device (int32 [rows]), for a step that is queued before the host reads them
 
     def tokens(self) -> list[int]:
         self._event.synchronize()
@@ -83,7 +84,7 @@ class Sampler:
         host[:rows].copy_(out, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        return PendingTokens(host, event, rows)
+        return PendingTokens(host, event, rows, out)
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], steps: list[int]) -> list[int]:
         return self.launch(logits, params, requests, steps).tokens()

@@ -31,7 +31,7 @@ class ScriptedEngine:
         del self.lengths[slot]
         self.free.append(slot)
 
-    def check_kernels(self):
+    def check_kernels(self, wait=True):
         pass
 
     def step(self, entries):
@@ -119,6 +119,56 @@ class LaunchSampler(ArgmaxSampler):
                 return tokens
 
         return Pending()
+
+
+class PipelinedEngine(PlanningEngine):
+    """Takes the chosen tokens as a tensor and row numbers, as the engine does when the next step is queued before
+    the host has read them."""
+
+    accepts_chosen_tokens = True
+
+    def run_planned(self, plan, tokens, chosen=None):
+        if chosen is not None:
+            tokens = [int(chosen[row]) for row in tokens]
+        return super().run_planned(plan, tokens)
+
+
+class DeviceSampler(LaunchSampler):
+    def launch(self, logits, params, requests, steps):
+        pending = super().launch(logits, params, requests, steps)
+        pending.device = torch.tensor(pending.tokens(), dtype=torch.int32)
+        return pending
+
+
+def test_steps_queued_ahead_give_the_same_tokens_and_drop_the_rows_of_stopped_requests():
+    plain_engine, engine = ScriptedEngine(), PipelinedEngine()
+    prompts = [[10, 11, 12], [46], [20, 21]]
+    expected = generate(plain_engine, prompts, max_new_tokens=5, sampler=ArgmaxSampler())
+    sampler = DeviceSampler()
+    results = generate(engine, prompts, max_new_tokens=5, sampler=sampler)
+    assert [(r.tokens, r.finish_reason) for r in results] == [(r.tokens, r.finish_reason) for r in expected]
+    # every plan is run at once (no plan is made twice); slot 1 stops at its third token, when the step for its fourth
+    # is already queued: it runs with three rows and the row of slot 1 is dropped
+    assert engine.plans == [([0, 1, 2], True)] * 3 + [([0, 2], True)]
+    assert engine.steps == [[(0, 3), (1, 1), (2, 2)], [(0, 1), (1, 1), (2, 1)], [(0, 1), (1, 1), (2, 1)], [(0, 1), (1, 1), (2, 1)],
+                            [(0, 1), (2, 1)]]
+    assert sampler.calls[3] == ([0, 1, 2], [3, 3, 3]) and sampler.calls[4] == ([0, 2], [4, 4])
+    assert not engine.lengths and sorted(engine.free) == [0, 1, 2]
+    # the same through several batches, the cache's end, and with the pipeline switched off by the environment
+    engine = PipelinedEngine(num_slots=2, total_pages=100)
+    results = generate(engine, [[1], [2, 3], [4], [5, 6, 7], [8]], max_new_tokens=2, sampler=DeviceSampler(), ignore_eos=True)
+    assert [r.tokens for r in results] == [[2, 3], [4, 5], [5, 6], [8, 9], [9, 10]] and engine.slot_history == [0, 1, 0, 1, 0]
+    engine = PipelinedEngine(max_seq_len=6, total_pages=10)
+    result = generate(engine, [[1, 2, 3, 4]], max_new_tokens=10, sampler=DeviceSampler(), ignore_eos=True)[0]
+    assert result.tokens == [5, 6, 7] and result.finish_reason == "max_seq_len"
+
+
+def test_the_pipeline_can_be_switched_off(monkeypatch):
+    monkeypatch.setenv("QT_B200_PIPELINE", "0")
+    engine = PipelinedEngine()
+    results = generate(engine, [[10, 11, 12], [46], [20, 21]], max_new_tokens=5, sampler=DeviceSampler())
+    assert [r.tokens for r in results] == [[13, 14, 15, 16, 17], [47, 48, 49], [22, 23, 24, 25, 26]]
+    assert engine.plans[3] == ([0, 2], False)              # planned again after the stop token, as without a pipeline
 
 
 def test_the_next_step_is_planned_ahead_and_replanned_after_a_stop_token():
