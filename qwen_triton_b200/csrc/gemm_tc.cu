@@ -165,7 +165,11 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 // The same product with two blocks (a cluster on the two SMs of a TPC) per 256 x 256 output tile: each block stages
 // 128 weight rows and 128 of the tile's 256 tokens per K slice (32 KB instead of 48 KB for the same MMA work, so a
 // third less traffic from L2 and a six-stage ring), the even-ranked block issues tcgen05.mma.cta_group::2 with
-// M = 256, N = 256, and each block reads its own 128 accumulator rows back and stores them.  No split-K.
+// M = 256, N = 256, and each block reads its own 128 accumulator rows back and stores them.
+//
+// Split-K for a few hundred tokens, where the tiles alone do not fill the TPCs: a work item is (tile, K range), the
+// items of one K range come first, and each range's sums go to a float plane of their own, out[split, M, N], which
+// the consuming kernel adds up in a fixed order.
 //
 // One pair per TPC, persistent: a pair walks the tiles pair, pair + pairs, ... with two accumulators in tensor memory
 // (all 512 columns), so that the epilogue of a tile runs under the MMAs of the next.  One block per SM is also what
@@ -193,7 +197,8 @@ constexpr int SWIGLU_GROUP = 16;
 template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
-                                                                  int M, int N, int nkb, int* status) {
+                                                                  int M, int N, int kb_total, int kb_per_split, int splits,
+                                                                  size_t split_stride, int* status) {
     // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = 256, M = 256 over the pair
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PAIR_X >> 3) << 17) | ((uint32_t)((2 * BW) >> 4) << 24);
     constexpr int S = PAIR_STAGES;
@@ -211,8 +216,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int w_tiles = (N + 2 * BW - 1) / (2 * BW), x_tiles = (M + PAIR_X - 1) / PAIR_X;
-    const int n_tiles = w_tiles * x_tiles;
+    const int n_tiles = w_tiles * x_tiles, n_items = n_tiles * splits;
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    // work item -> its tile, the plane of its K range, the first K block and the number of K blocks
+    auto item_range = [&](int item, int& tile, int& split, int& kb0, int& nkb) {
+        split = splits == 1 ? 0 : item / n_tiles;
+        tile = item - split * n_tiles;
+        kb0 = split * kb_per_split;
+        nkb = min(kb_total, kb0 + kb_per_split) - kb0;
+    };
 
     if (threadIdx.x == 0) {
         prefetch_tensor_map(&map_w);
@@ -236,22 +248,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
             int s = 0;                                       // stage and phase of the next K slice, over all tiles
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-                int w_tile, x_tile;
+            for (int item = pair; item < n_items && ok; item += n_pairs) {
+                int tile, split, kb0, nkb, w_tile, x_tile;
+                item_range(item, tile, split, kb0, nkb);
                 tile_coords(tile, w_tiles, x_tiles, w_tile, x_tile);
                 const int w0 = w_tile * 2 * BW + (int)rank * BW, x_stage0 = x_tile * PAIR_X + (int)rank * PAIR_HALF;
                 int kb = 0;
-                if (tile == pair) {
+                if (item == pair) {
                     // the weight depends on no earlier kernel: fill the ring with weight tiles first, then wait for
                     // the kernel that produces the activations, then fetch their tiles
                     const int ahead = min(nkb, S);
                     for (int i = 0; i < ahead; ++i) {
                         if (leader) mbar_expect_tx(full0 + 8 * i, 2 * PAIR_STAGE_BYTES);
-                        tma_load_2d_pair(base + i * PAIR_STAGE_BYTES, &map_w, leader_full0 + 8 * i, i * BK, w0);
+                        tma_load_2d_pair(base + i * PAIR_STAGE_BYTES, &map_w, leader_full0 + 8 * i, (kb0 + i) * BK, w0);
                     }
                     pdl_wait();
                     for (int i = 0; i < ahead; ++i)
-                        tma_load_2d_pair(base + i * PAIR_STAGE_BYTES + W_BYTES, &map_x, leader_full0 + 8 * i, i * BK, x_stage0);
+                        tma_load_2d_pair(base + i * PAIR_STAGE_BYTES + W_BYTES, &map_x, leader_full0 + 8 * i, (kb0 + i) * BK, x_stage0);
                     kb = ahead;
                     if (ahead == S) phase = 1u; else s = ahead;
                 }
@@ -259,12 +272,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
                     if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) { ok = false; break; }
                     if (leader) mbar_expect_tx(full0 + 8 * s, 2 * PAIR_STAGE_BYTES);
                     const uint32_t dst = base + s * PAIR_STAGE_BYTES;
-                    tma_load_2d_pair(dst, &map_w, leader_full0 + 8 * s, kb * BK, w0);
-                    tma_load_2d_pair(dst + W_BYTES, &map_x, leader_full0 + 8 * s, kb * BK, x_stage0);
+                    tma_load_2d_pair(dst, &map_w, leader_full0 + 8 * s, (kb0 + kb) * BK, w0);
+                    tma_load_2d_pair(dst + W_BYTES, &map_x, leader_full0 + 8 * s, (kb0 + kb) * BK, x_stage0);
                     if (++s == S) { s = 0; phase ^= 1u; }
                 }
             }
-            if (pair >= n_tiles) pdl_wait();
+            if (pair >= n_items) pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0 && leader) {
@@ -275,7 +288,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
             int it = 0, s = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+            for (int item = pair; item < n_items && ok; item += n_pairs, ++it) {
+                int tile, split, kb0, nkb;
+                item_range(item, tile, split, kb0, nkb);
                 const int b = it & 1;
                 // the epilogues of both blocks have read this accumulator's previous tile (passes at once the first time)
                 if (!mbar_wait(acc_empty0 + 8 * b, (((uint32_t)it >> 1) & 1u) ^ 1u, status, 4)) break;
@@ -300,9 +315,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
         const uint32_t leader_acc_empty0 = map_to_cta(acc_empty0, 0);
         pdl_wait();                                          // the output may still be read by an earlier kernel
         int it = 0;
-        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++it) {
-            int w_tile, x_tile;
+        for (int item = pair; item < n_items; item += n_pairs, ++it) {
+            int tile, split, kb0, nkb, w_tile, x_tile;
+            item_range(item, tile, split, kb0, nkb);
             tile_coords(tile, w_tiles, x_tiles, w_tile, x_tile);
+            TO* __restrict__ plane = out + (size_t)split * split_stride;
             const int b = it & 1;
             if (!mbar_wait(acc_full0 + 8 * b, ((uint32_t)it >> 1) & 1u, status, 3)) break;
             tc_fence_after();
@@ -326,13 +343,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
                         const float g = upper ? got : mine0;          // lower lanes: token j (their gate, the partner's up)
                         const float u = upper ? mine1 : got;          // upper lanes: token j + 1 (the partner's gate, their up)
                         const int m = x0 + c + j + (upper ? 1 : 0);
-                        if (stores && m < M) out[(size_t)m * features + feature] = from_float<TO>(__fdividef(g, 1.f + __expf(-g)) * u);
+                        if (stores && m < M) plane[(size_t)m * features + feature] = from_float<TO>(__fdividef(g, 1.f + __expf(-g)) * u);
                     }
                 } else if (stores) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = x0 + c + j;
-                        if (m < M) out[(size_t)m * N + n] = from_float<TO>(__uint_as_float(v[j]));
+                        if (m < M) plane[(size_t)m * N + n] = from_float<TO>(__uint_as_float(v[j]));
                     }
                 }
             }
@@ -354,8 +371,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
 }
 
 template <typename TO, bool SWIGLU>
-int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int* status,
-                cudaStream_t stream) {
+int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
+                size_t split_stride, int* status, cudaStream_t stream) {
     const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + (2 * PAIR_STAGES + 4) * 8 + 16;
     static int resident_pairs = 0;                           // pairs the device runs at once (one per TPC that can host a cluster)
     if (resident_pairs == 0) {
@@ -378,9 +395,11 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
             QT_FAIL(QT_ERR_LAUNCH, "gemm_tc_pair: no cluster of two blocks fits the device (%s)", cudaGetErrorString(err));
         resident_pairs = clusters;
     }
-    const long long tiles = (long long)((N + 2 * BW - 1) / (2 * BW)) * ((M + PAIR_X - 1) / PAIR_X);
-    const unsigned pairs = (unsigned)(tiles < resident_pairs ? tiles : resident_pairs);
-    launch_kernel_cluster(gemm_tc_pair_kernel<TO, SWIGLU>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total, status);
+    const long long items = (long long)((N + 2 * BW - 1) / (2 * BW)) * ((M + PAIR_X - 1) / PAIR_X) * splits;
+    const unsigned pairs = (unsigned)(items < resident_pairs ? items : resident_pairs);
+    const int kb_per_split = (kb_total + splits - 1) / splits;
+    launch_kernel_cluster(gemm_tc_pair_kernel<TO, SWIGLU>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total,
+                          kb_per_split, splits, split_stride, status);
     QT_CHECK_LAUNCH("gemm_tc_pair");
     return QT_OK;
 }
@@ -462,28 +481,31 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
     QT_FAIL(QT_ERR_ARG, "gemm_tc: unknown output type %d", out_dtype);
 }
 
-// The same product by pairs of blocks (see gemm_tc_pair_kernel): bfloat16 or float output, no split-K; meant for
-// many tokens (a pair covers 256 weight rows x 256 tokens).  With `swiglu` the weight's rows alternate 16 of a gate and
+// The same product by pairs of blocks (see gemm_tc_pair_kernel): bfloat16 or float output, meant for many tokens (a
+// pair covers 256 weight rows x 256 tokens); out[splits, M, N] in float when `splits` > 1, under the rule above.  With `swiglu` the weight's rows alternate 16 of a gate and
 // 16 of an up projection and `out` is [M, N / 2] = silu(gate) * up.  Codes in `status`: as above, 4 = the MMA issuer
 // waiting for the epilogues to free an accumulator.
 extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int swiglu,
-                               int* status, void* stream) {
+                               int splits, long long split_stride, int* status, void* stream) {
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc_pair: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc_pair: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc_pair: operands must be 16-byte aligned");
     QT_REQUIRE(status != nullptr, "gemm_tc_pair: a status word is required");
     QT_REQUIRE(!swiglu || N % (2 * SWIGLU_GROUP) == 0, "gemm_tc_pair: N=%d is not gate and up rows in groups of %d", N, SWIGLU_GROUP);
     const int kb_total = (K + BK - 1) / BK;
-    QT_REQUIRE((long long)((M + PAIR_X - 1) / PAIR_X) * ((N + 2 * BW - 1) / (2 * BW)) < (1ll << 30), "gemm_tc_pair: M=%d x N=%d is too large for one launch", M, N);
+    QT_REQUIRE(splits >= 1 && splits <= kb_total, "gemm_tc_pair: splits=%d for %d K blocks", splits, kb_total);
+    QT_REQUIRE((splits - 1) * ((kb_total + splits - 1) / splits) < kb_total, "gemm_tc_pair: splits=%d would leave a split without K blocks (%d blocks)", splits, kb_total);
+    QT_REQUIRE(splits == 1 || (out_dtype == QT_F32 && !swiglu), "gemm_tc_pair: split-K partial sums are float and ungated");
+    QT_REQUIRE((long long)((M + PAIR_X - 1) / PAIR_X) * ((N + 2 * BW - 1) / (2 * BW)) * splits < (1ll << 30), "gemm_tc_pair: M=%d x N=%d is too large for one launch", M, N);
     CUtensorMap map_w, map_x;
     int rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
     if (rc) return rc;
     rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)PAIR_HALF);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, status, s);
-    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, status, s);
-    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, status, s);
+    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, status, s);
+    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, status, s);
+    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc_pair: output type %d%s is not offered", out_dtype, swiglu ? " with the SiLU-gated epilogue" : "");
 }
 

@@ -53,7 +53,7 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
-        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
     },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -481,7 +481,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
 def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False) -> None:
     """The same product by pairs of blocks on the two SMs of a TPC (tcgen05 cta_group::2): 256 weight rows x
     256 tokens per tile, each block staging half of both operands; one persistent pair per TPC with two
-    accumulators in tensor memory.  No split-K; meant for many tokens.
+    accumulators in tensor memory.  Meant for many tokens; ``out`` may be [splits, M, N] float partial sums, which
+    pays for a few hundred tokens whose tiles alone do not fill the TPCs.
 
     With ``swiglu`` the rows of ``w`` alternate SWIGLU_GROUP of a gate and of an up projection
     (``interleave_gate_up``) and ``out`` [1, M, N / 2] receives silu(gate) * up from the epilogue."""
@@ -489,26 +490,26 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = 
     _need(w, "w", torch.bfloat16)
     rows, k = a.shape
     cols = w.shape[0] // 2 if swiglu else w.shape[0]
-    if k != w.shape[1] or (out.rows, out.cols) != (rows, cols) or out.n_splits != 1 or (swiglu and w.shape[0] % (2 * SWIGLU_GROUP)):
+    if k != w.shape[1] or (out.rows, out.cols) != (rows, cols) or (swiglu and (out.n_splits != 1 or w.shape[0] % (2 * SWIGLU_GROUP))):
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.tensor.shape)} do not fit")
     if rows == 0:
         return
     if not out.tensor.is_cuda or out.tensor.dtype not in _CODES:
         raise KernelError("gemm_tc_pair: the output must be a bfloat16 or float32 CUDA tensor")
     _call("gemm_tc", "qt_gemm_tc_pair", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k,
-          1 if swiglu else 0, _ptr(_status_word(a.device)), _stream())
+          1 if swiglu else 0, out.n_splits, out.split_stride, _ptr(_status_word(a.device)), _stream())
 
 
-def gemm_uses_pairs(a: torch.Tensor, w: torch.Tensor, n_splits: int = 1) -> bool:
+def gemm_uses_pairs(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether ``gemm`` gives this product to the pair kernel (a static choice by element type and shape)."""
-    return gemm_tc_supported(a, w) and a.shape[0] > _TC_TILES[-1] and n_splits == 1
+    return gemm_tc_supported(a, w) and a.shape[0] > _TC_TILES[-1]
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
     """out = a @ w^T with the kernel that fits the element type and shape (a static choice):
     tensor cores for bfloat16 with 16-byte aligned rows, the FMA kernel for float32 and the rest."""
     if gemm_tc_supported(a, w):
-        if gemm_uses_pairs(a, w, out.n_splits):
+        if gemm_uses_pairs(a, w):
             gemm_tc_pair(a, w, out)         # more tokens than one block's tile: pairs of blocks, a third less operand traffic
         else:
             gemm_tc(a, w, out)

@@ -45,6 +45,32 @@ def pick_splits(out_features: int, in_features: int, target_blocks: int = 2 * _S
     return best
 
 
+_PAIRS = _SM_COUNT // 2                # pairs of blocks the pair kernel keeps resident (one per TPC)
+_PAIR_TILE = 256                       # weight rows and tokens of one pair tile
+
+
+def pick_pair_splits(out_features: int, in_features: int, rows: int) -> int:
+    """Split count for a product of a few hundred rows by the pair kernel, whose 256 x 256 tiles alone leave TPCs
+    idle or end in a nearly empty wave: waves of work items (tiles x splits over 74 pairs) times the time of one item at the pair's share of the
+    tensor throughput plus a fixed cost per item, plus the float partial sums written and read once (they stay
+    in L2).  Every split keeps at least eight 64-wide K blocks; fewer splits win near-ties."""
+    tiles = -(-out_features // _PAIR_TILE) * -(-rows // _PAIR_TILE)
+    blocks_k = -(-in_features // 64)
+    pair_flops, item_overhead, partial_rate = 1.45e15 / _PAIRS, 2e-6, 1e13
+    best, best_cost = 1, float("inf")
+    for splits in range(1, 5):
+        if splits > 1 and blocks_k // splits < 8:
+            break
+        if kernels.tc_normalise_splits(in_features, splits) != splits:
+            continue
+        item = 2.0 * _PAIR_TILE * _PAIR_TILE * in_features / splits / pair_flops + item_overhead
+        partial = 2.0 * 4 * splits * rows * out_features / partial_rate if splits > 1 else 0.0
+        cost = -(-tiles * splits // _PAIRS) * item + partial
+        if cost < best_cost * 0.97:
+            best, best_cost = splits, cost
+    return best
+
+
 class Linear:
     def __init__(self, key: str, out_features: int, in_features: int, runtime: Runtime, max_rows: int | None = None,
                  float_out: bool = False) -> None:
@@ -61,6 +87,15 @@ class Linear:
         self.split_plans: list[tuple[int, int]] = []          # (most rows, splits), fewest rows first
         if runtime.dtype == torch.bfloat16 and in_features % 8 == 0:
             self.split_plans = [(rows, pick_splits(out_features, in_features, target, rows)) for rows, target in _SPLIT_PLANS]
+            # a few hundred rows: the pair kernel with split K where its tiles alone would not fill the TPCs
+            if not float_out and self.max_rows > _PAIR_TILE:
+                self.split_plans.append((_PAIR_TILE, 1))          # up to one tile of tokens: single blocks, no split
+                for tiles_x in range(2, -(-self.max_rows // _PAIR_TILE) + 1):
+                    rows = min(tiles_x * _PAIR_TILE, self.max_rows)
+                    if rows > self.split_plans[-1][0]:
+                        self.split_plans.append((rows, pick_pair_splits(out_features, in_features, rows)))
+                    if -(-out_features // _PAIR_TILE) * tiles_x >= 4 * _PAIRS:      # several waves of tiles: no split pays
+                        break
         words = max((rows * splits for rows, splits in self.split_plans if splits > 1), default=0)
         if words:
             runtime.workspace.declare(f"{key}.partial", words * out_features, torch.float32)

@@ -384,6 +384,24 @@ def test_gemm_tensor_cores_block_pairs(m, n, k, out_dtype):
     close(out[0], expected, out_dtype, f"{m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("m, n, k, splits", [(300, 384, 1024, 2), (512, 4096, 4096, 2), (700, 1000, 3000, 4), (513, 257, 200, 3),
+                                             (1100, 5000, 640, 3)])   # the last: more work items than resident pairs
+def test_gemm_block_pairs_split_k(m, n, k, splits):
+    """Work items of the pair kernel that are (tile, K range): each range's sums land in a float plane of their own,
+    a last range shorter than the others included."""
+    a, w = rand(m, k, seed=119, dtype=torch.bfloat16), rand(n, k, seed=120, scale=0.1, dtype=torch.bfloat16)
+    splits = kernels.tc_normalise_splits(k, splits)
+    assert splits > 1
+    out = torch.full((splits, m, n), float("nan"), dtype=torch.float32, device=DEV)
+    kernels.gemm_tc_pair(a, w, GemmOut(out))
+    kernels.check_status(DEV)
+    close(GemmOut(out).value(), a.double() @ w.double().T, torch.float32, f"{m}x{n}x{k} splits={splits}")
+    per = -(-(-(-k // 64)) // splits) * 64
+    close(out[0], a[:, :per].double() @ w[:, :per].double().T, torch.float32, "first K range")
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tc_pair(a, w, GemmOut(torch.empty(splits, m, n, dtype=torch.bfloat16, device=DEV)))
+
+
 @pytest.mark.parametrize("m, inter, k", [(300, 48, 72), (1000, 560, 1024), (2048, 1536, 256), (513, 4096 + 16, 64)])
 def test_gemm_block_pairs_with_the_silu_gate_in_the_epilogue(m, inter, k):
     """gate and up rows interleaved in groups of 16: the pair kernel stores silu(x G^T) * (x U^T)."""
