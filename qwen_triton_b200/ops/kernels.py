@@ -101,7 +101,15 @@ def _call(library: str, name: str, *args, launches: int = 1) -> None:
         raise KernelError(f"{name} failed ({code}): {_build.last_error(library)}")
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current stream's handle.  Asked for at every launch, so by torch's two direct calls where it has them:
+    building a Stream object costs as much host time as the rest of a launch."""
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return _RAW_STREAM(_RAW_DEVICE())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -414,6 +422,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
 
 _STATUS: dict[int, torch.Tensor] = {}
 _TC_TILES = (16, 32, 64, 128, 256)
+TC_MAX_BLOCK_TOKENS = 128      # tokens per block that ``gemm`` gives the one-block kernel (256 measured slower at every split count)
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -442,8 +451,8 @@ def check_status(device: torch.device | str = "cuda") -> None:
 def tc_token_tile(rows: int) -> int:
     for tile in _TC_TILES:
         if rows <= tile:
-            return tile
-    return _TC_TILES[-1]
+            return min(tile, TC_MAX_BLOCK_TOKENS)
+    return TC_MAX_BLOCK_TOKENS
 
 
 def tc_normalise_splits(k: int, wanted: int) -> int:

@@ -93,6 +93,7 @@ class Workspace:
         self.device = device
         self._need: dict[str, tuple[int, torch.dtype]] = {}
         self._buffers: dict[str, torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}
 
     def declare(self, name: str, numel: int, dtype: torch.dtype) -> None:
         old = self._need.get(name)
@@ -105,8 +106,21 @@ class Workspace:
             current = self._buffers.get(name)
             if current is None or current.numel() < numel:
                 self._buffers[name] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+        self._views.clear()
 
     def view(self, name: str, *shape: int) -> torch.Tensor:
+        """The leading elements of a buffer in ``shape``.  Views are kept by (name, shape): a step asks for the same
+        few dozen again and again, and making one costs two tensor operations on the host."""
+        key = (name, shape)
+        found = self._views.get(key)
+        if found is not None:
+            return found
+        if len(self._views) >= 4096:
+            self._views.clear()
+        found = self._views[key] = self._make_view(name, shape)
+        return found
+
+    def _make_view(self, name: str, shape: tuple[int, ...]) -> torch.Tensor:
         count = 1
         for dim in shape:
             count *= dim

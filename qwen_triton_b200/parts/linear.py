@@ -17,19 +17,22 @@ _SM_COUNT = 148
 _MAX_SPLITS = 16
 # (most rows, blocks wanted in flight) for products bound by reading the weight.  Up to 16 rows the kernel's ring is
 # three stages deep and four blocks share an SM, which also lets the next product's blocks move in and fetch their
-# first weight tiles while this one drains; up to 64 rows two blocks with deeper rings measured better.
-_SPLIT_PLANS = ((16, 4 * _SM_COUNT), (64, 2 * _SM_COUNT))
+# first weight tiles while this one drains; up to 64 rows two blocks with deeper rings measured better.  Up to 256
+# rows (a large decode batch, a short prompt) the weight still bounds the product: blocks of 128 tokens, split
+# (alone, 256 rows of the 8B shapes: 16.6 us against 54 us for q/k/v, 32 against 158 us for the down projection).
+_SPLIT_PLANS = ((16, 4 * _SM_COUNT), (64, 2 * _SM_COUNT), (128, 2 * _SM_COUNT), (256, 2 * _SM_COUNT))
 
 
 def pick_splits(out_features: int, in_features: int, target_blocks: int = 2 * _SM_COUNT, rows: int = 16) -> int:
     """Split count for a product with few rows, by a cost in bytes: the weight, read at the rate its blocks
-    (128-row weight tiles x splits) keep ``target_blocks`` slots busy, plus the float partial sums of ``rows``
-    rows, written once and read once.  Each split keeps at least four 64-wide K blocks; fewer splits win near-ties.
+    (128-row weight tiles x token tiles of at most 128 x splits) keep ``target_blocks`` slots busy (a second token
+    tile reads it again, from L2), plus the float partial sums of ``rows`` rows, written once and read once.  Each split keeps at least four 64-wide K blocks; fewer splits win near-ties.
     (Filling waves alone would cut a product that already has blocks for several waves into many splits, whose
     partial sums then cost more than the weight: 14 splits for a 51,200 x 5,120 weight at 64 rows.)"""
-    tiles = -(-out_features // 128)
+    token_tiles = -(-rows // kernels.TC_MAX_BLOCK_TOKENS)
+    tiles = -(-out_features // 128) * token_tiles
     blocks_k = -(-in_features // 64)
-    weight_bytes = 2.0 * out_features * in_features
+    weight_bytes = 2.0 * out_features * in_features * (1.0 + 0.3 * (token_tiles - 1))
     best, best_cost = 1, float("inf")
     for splits in range(1, _MAX_SPLITS + 1):
         if splits > 1 and blocks_k // splits < 4:
@@ -53,19 +56,20 @@ def pick_pair_splits(out_features: int, in_features: int, rows: int) -> int:
     """Split count for a product of a few hundred rows by the pair kernel, whose 256 x 256 tiles alone leave TPCs
     idle or end in a nearly empty wave: waves of work items (tiles x splits over 74 pairs) times the time of one item at the pair's share of the
     tensor throughput plus a fixed cost per item, plus the float partial sums written and read once (they stay
-    in L2).  Every split keeps at least eight 64-wide K blocks; fewer splits win near-ties."""
+    in L2); the constants are fitted to products of 300 to 768 rows timed alone.  Every split keeps at least eight 64-wide K blocks; fewer splits win near-ties."""
     tiles = -(-out_features // _PAIR_TILE) * -(-rows // _PAIR_TILE)
     blocks_k = -(-in_features // 64)
-    pair_flops, item_overhead, partial_rate = 1.45e15 / _PAIRS, 2e-6, 1e13
+    pair_flops, first_overhead, later_overhead, partial_rate = 1.45e15 / _PAIRS, 2e-6, 0.5e-6, 2e13
     best, best_cost = 1, float("inf")
     for splits in range(1, 5):
         if splits > 1 and blocks_k // splits < 8:
             break
         if kernels.tc_normalise_splits(in_features, splits) != splits:
             continue
-        item = 2.0 * _PAIR_TILE * _PAIR_TILE * in_features / splits / pair_flops + item_overhead
+        item = 2.0 * _PAIR_TILE * _PAIR_TILE * in_features / splits / pair_flops
+        waves = -(-tiles * splits // _PAIRS)                  # a pair's later items start under the epilogue of the one before
         partial = 2.0 * 4 * splits * rows * out_features / partial_rate if splits > 1 else 0.0
-        cost = -(-tiles * splits // _PAIRS) * item + partial
+        cost = waves * item + first_overhead + (waves - 1) * later_overhead + partial
         if cost < best_cost * 0.97:
             best, best_cost = splits, cost
     return best
@@ -89,7 +93,6 @@ class Linear:
             self.split_plans = [(rows, pick_splits(out_features, in_features, target, rows)) for rows, target in _SPLIT_PLANS]
             # a few hundred rows: the pair kernel with split K where its tiles alone would not fill the TPCs
             if not float_out and self.max_rows > _PAIR_TILE:
-                self.split_plans.append((_PAIR_TILE, 1))          # up to one tile of tokens: single blocks, no split
                 for tiles_x in range(2, -(-self.max_rows // _PAIR_TILE) + 1):
                     rows = min(tiles_x * _PAIR_TILE, self.max_rows)
                     if rows > self.split_plans[-1][0]:

@@ -85,19 +85,20 @@ def mid():
         yield config, folder, weights
 
 
+@pytest.mark.parametrize("prompt", [[300, 290], [150, 97]])
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-def test_long_prompts_take_the_kernels_for_many_tokens(mid, dtype):
-    """Two prompts of 300 and 290 tokens in one step (more than 256 tokens: block pairs in the products, the gated
-    epilogue, the tcgen05 attention), then one token each, against the plain implementation in float64."""
+def test_long_prompts_take_the_kernels_for_many_tokens(mid, dtype, prompt):
+    """Two prompts of 300 and 290 tokens in one step (more than 256 tokens: block pairs in the products with split K,
+    the gated epilogue, the tcgen05 attention), or of 150 and 97 (two token tiles of single blocks, split K), then
+    one token each, against the plain implementation in float64."""
     config, folder, weights = mid
     raw = config.to_hf_dict()
     engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=2048)
-    requests = [tokens_for(config, 306, 3), tokens_for(config, 293, 4)]
+    requests = [tokens_for(config, prompt[0] + 6, 3), tokens_for(config, prompt[1] + 3, 4)]
     truth = [plain.forward(raw, weights, r, dtype=torch.float64) for r in requests]
     plain32 = [plain.forward(raw, weights, r) for r in requests]
     slots = [engine.new_sequence() for _ in requests]
-    prompt = [300, 290]
-    want = [[0, 1, 128, 255, 256, 299], [0, 63, 64, 289]]
+    want = [[p for p in (0, 1, 128, 255, 256) if p < prompt[0]] + [prompt[0] - 1], [0, 63, 64, prompt[1] - 1]]
     first = engine.step([StepEntry(s, r[:p], w) for s, r, p, w in zip(slots, requests, prompt, want)])
     got = {0: [first[:len(want[0])]], 1: [first[len(want[0]):]]}
     places = {0: list(want[0]), 1: list(want[1])}

@@ -359,7 +359,8 @@ def test_kernels_refuse_what_they_cannot_run():
     (16, 130, 264, 1, torch.bfloat16), (37, 130, 264, 1, torch.bfloat16), (64, 4096, 1536, 4, torch.float32),
     (100, 200, 160, 1, torch.bfloat16), (300, 1000, 1024, 1, torch.bfloat16), (2048, 512, 4096, 1, torch.bfloat16),
     (513, 257, 72, 1, torch.float32), (5, 129, 8, 1, torch.float32),
-    (1000, 5000, 256, 1, torch.bfloat16), (4096, 2560, 192, 1, torch.float32), (129, 19000, 64, 1, torch.bfloat16)])
+    (1000, 5000, 256, 1, torch.bfloat16), (4096, 2560, 192, 1, torch.float32), (129, 19000, 64, 1, torch.bfloat16),
+    (200, 384, 1024, 3, torch.float32), (256, 520, 2048, 4, torch.float32), (129, 130, 4096, 9, torch.float32)])   # split K over two token tiles
 def test_gemm_tensor_cores(m, n, k, splits, out_dtype):
     a, w = rand(m, k, seed=110, dtype=torch.bfloat16), rand(n, k, seed=111, scale=0.1, dtype=torch.bfloat16)
     expected = a.double() @ w.double().T
