@@ -422,6 +422,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
 
 _STATUS: dict[int, torch.Tensor] = {}
 _TC_TILES = (16, 32, 64, 128, 256)
+_SM_COUNT = 148
 TC_MAX_BLOCK_TOKENS = 128      # tokens per block that ``gemm`` gives the one-block kernel (256 measured slower at every split count)
 
 
@@ -511,7 +512,11 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = 
 
 def gemm_uses_pairs(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether ``gemm`` gives this product to the pair kernel (a static choice by element type and shape)."""
-    return gemm_tc_supported(a, w) and a.shape[0] > _TC_TILES[-1]
+    if not gemm_tc_supported(a, w):
+        return False
+    # more than 256 tokens; or more than one block's 128 with a weight whose tiles fill the machine unsplit (the fused
+    # gate/up projection, the head), which single blocks would read once per token tile
+    return a.shape[0] > _TC_TILES[-1] or (a.shape[0] > TC_MAX_BLOCK_TOKENS and w.shape[0] >= 128 * _SM_COUNT)
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
