@@ -1,0 +1,57 @@
+"""The split plans of ``Linear`` (host decisions, no device): every plan is one the kernels accept."""
+import itertools
+
+import pytest
+import torch
+
+from qwen_triton_b200.ops import kernels
+from qwen_triton_b200.parts import linear
+
+
+class _Workspace:
+    def __init__(self):
+        self.declared = {}
+
+    def declare(self, name, numel, dtype):
+        self.declared[name] = (numel, dtype)
+
+
+class _Runtime:
+    def __init__(self, dtype, max_step_tokens):
+        self.dtype, self.max_step_tokens, self.workspace, self.device = dtype, max_step_tokens, _Workspace(), "cpu"
+
+
+SHAPES = [(6144, 4096), (4096, 12288), (24576, 4096), (151936, 4096), (1024, 2048), (130, 72), (5003, 1000), (200, 8), (51200, 5120)]
+
+
+@pytest.mark.parametrize("out_features, in_features", SHAPES)
+def test_every_split_count_leaves_no_split_without_k_blocks(out_features, in_features):
+    for rows, target in linear._SPLIT_PLANS:
+        splits = linear.pick_splits(out_features, in_features, target, rows)
+        assert 1 <= splits <= 16 and kernels.tc_normalise_splits(in_features, splits) == splits
+    for rows in (257, 300, 512, 1000, 2048, 4096):
+        splits = linear.pick_pair_splits(out_features, in_features, rows)
+        assert 1 <= splits <= 4 and kernels.tc_normalise_splits(in_features, splits) == splits
+        blocks = -(-in_features // 64)
+        assert (splits - 1) * -(-blocks // splits) < blocks
+
+
+def test_a_product_with_many_tiles_is_not_split():
+    assert linear.pick_splits(151936, 4096, 296, 64) == 1
+    assert linear.pick_pair_splits(24576, 4096, 2048) == 1
+    assert linear.pick_pair_splits(4096, 4096, 512) > 1          # 32 tiles on 74 pairs
+
+
+@pytest.mark.parametrize("max_rows", [40, 256, 300, 4096])
+def test_plans_are_sorted_and_the_partial_buffer_holds_every_plan(max_rows):
+    runtime = _Runtime(torch.bfloat16, max_rows)
+    layer = linear.Linear("x", 4096, 12288, runtime)
+    most = [rows for rows, _ in layer.split_plans]
+    assert most == sorted(set(most))
+    words = max((rows * splits for rows, splits in layer.split_plans if splits > 1), default=0)
+    assert runtime.workspace.declared["x.partial"][0] == words * 4096
+    for rows, splits in layer.split_plans:
+        assert kernels.tc_normalise_splits(12288, splits) == splits
+    # float32 models and rows that TMA cannot address take no split plan at all
+    assert linear.Linear("y", 4096, 12288, _Runtime(torch.float32, max_rows)).split_plans == []
+    assert linear.Linear("z", 4096, 12284, _Runtime(torch.bfloat16, max_rows)).split_plans == []
