@@ -6,10 +6,10 @@
 //
 //   S = Q K^T        tcgen05.mma, Q and K tiles in shared memory (TMA, 128-byte swizzle), S in tensor memory
 //   P = softmax(S)   four warps, one thread per query row: the row of S is read once with tcgen05.ld into
-//                    registers, so the row maximum and sum need no shuffles and no exchange; P goes to shared
-//                    memory as bfloat16 in the MMA's swizzled K-major layout
-//   O += P V         tcgen05.mma with V as an MN-major operand (V is stored [key][dim]), accumulated in tensor
-//                    memory over all tiles
+//                    registers, so the row maximum and sum need no shuffles and no exchange; P goes back into
+//                    tensor memory as bfloat16 pairs (tcgen05.st) over the scores it came from
+//   O += P V         tcgen05.mma with P as the A operand from tensor memory and V as an MN-major operand from
+//                    shared memory (V is stored [key][dim]), accumulated in tensor memory over all tiles
 //
 // O stays in tensor memory, so the softmax threads touch it only when a row's maximum has to move: a row keeps
 // the maximum it scaled by until the true one is more than 2^8 above it (P then holds values up to 2^8, which
@@ -21,7 +21,9 @@
 // the V tiles (two-stage rings each; separate producers so that a key tile is requested as soon as its stage is
 // free, not behind a value tile), warp 1 = tensor-memory allocation and (lane 0) MMA issue, warps 2..5 = softmax
 // and output.  S is double buffered: Q K^T of tile j+1 runs while the softmax of tile j is computed, and P V of
-// tile j runs while the scores of tile j+1 are read and their maximum is taken.  Key j is visible to the query at
+// tile j runs under the whole softmax of tile j+1 (P of tile j+1 goes to the other buffer; a softmax warp waits
+// for P V only when it has to scale O, and at the end).  The buffer of tile j is overwritten by Q K^T of tile j+2,
+// which the MMA thread issues after P V of tile j: the tensor pipe runs one thread's instructions in order.  Key j is visible to the query at
 // absolute position p iff j <= p and, in a windowed group, j > p - window.  Every mbarrier wait is bounded and
 // reports through a status word.
 //
@@ -39,9 +41,8 @@ namespace {
 constexpr int PAGE = 64;
 constexpr int BQ = 128;            // query rows per block = MMA M
 constexpr int THREADS = 224;        // warp 0: TMA of Q and K, warp 1: MMA + tensor-memory allocation, warps 2..5: softmax, warp 6: TMA of V
-constexpr uint32_t ALIGN_SLACK = 768;   // shared memory asked for beyond the tiles, to round their base up to 1,024 bytes (with two
-                                        // blocks of 113 KB per SM there is no room for a full 1,023; the base is aligned in practice,
-                                        // and the kernel refuses to run if it ever is not)
+constexpr uint32_t ALIGN_SLACK = 1024;  // shared memory asked for beyond the tiles, to round their base up to 1,024 bytes (the
+                                        // kernel refuses to run if the base ever needs more)
 constexpr float RESCALE_STEP = 8.f; // a row's scaling maximum moves only when the true one is more than 2^8 above it
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr uint32_t HALF_BYTES = 128 * 64 * 2;   // a [128 rows][64 columns] bfloat16 half tile: 16 KB
@@ -90,6 +91,15 @@ __device__ __forceinline__ void tmem_store32(uint32_t taddr, const uint32_t (&v)
           "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
+// d[tmem] (+)= a[tmem] * b[smem]: the A operand comes from tensor memory, row i in lane i, K elements packed two to
+// a 32-bit column (K-major), B from shared memory through its descriptor.
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -131,7 +141,6 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
     constexpr int PAGES = BKEY / PAGE;                    // pages per key tile
     constexpr uint32_t KEY_HALF_BYTES = BKEY * 64 * 2;    // a [BKEY keys][64 columns] half of a key or value tile
     constexpr uint32_t KV_BYTES = HALVES * KEY_HALF_BYTES;   // [BKEY keys][HD]
-    constexpr uint32_t P_BYTES = (BKEY / 64) * HALF_BYTES;   // [128 rows][BKEY keys]
     constexpr uint32_t TMEM_COLS = BKEY == 64 ? 256 : 512;
     constexpr uint32_t S_COL0 = 0, S_COL1 = BKEY, O_COL = 2 * BKEY;
     // S = Q K^T: M 128, N 128 keys, both operands K-major.  O = P V: M 128, N HD, A K-major, B MN-major.
@@ -163,11 +172,11 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
         return;
     }
     uint8_t* smem = smem_raw + (base - raw);
-    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES, p_s = v_s + 2 * KV_BYTES;
-    const uint32_t bars = p_s + P_BYTES;
-    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, pv_full
+    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES;
+    const uint32_t bars = v_s + 2 * KV_BYTES;
+    // barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], pv_full[2]
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56;
-    const uint32_t s_full = bars + 72, s_empty = bars + 88, p_full = bars + 104, pv_full = bars + 112;
+    const uint32_t s_full = bars + 72, p_full = bars + 88, pv_full = bars + 104;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + 128);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -178,10 +187,9 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
         for (int i = 0; i < 2; ++i) {
             mbar_init(k_full + 8 * i, 1); mbar_init(k_empty + 8 * i, 1);
             mbar_init(v_full + 8 * i, 1); mbar_init(v_empty + 8 * i, 1);
-            mbar_init(s_full + 8 * i, 1); mbar_init(s_empty + 8 * i, 4);
+            mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 4);
+            mbar_init(pv_full + 8 * i, 1);
         }
-        mbar_init(p_full, 4);
-        mbar_init(pv_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -230,14 +238,15 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
         if (lane == 0) {
             // This thread's instructions are the tensor pipe's critical path: operand descriptors are formed once and
             // stepped by additions (their address field counts 16-byte units).
-            const uint64_t q_desc0 = operand_desc(q_s), k_desc0 = operand_desc(k_s), p_desc0 = operand_desc(p_s);
+            const uint64_t q_desc0 = operand_desc(q_s), k_desc0 = operand_desc(k_s);
             const uint64_t v_desc0 = operand_desc_mn(v_s, KEY_HALF_BYTES);
             bool ok = mbar_wait(q_full, 0, status, 2);
             auto issue_qk = [&](int i) {
                 const int s = i & 1;
                 const uint32_t phase = (uint32_t)(i >> 1) & 1u;
                 if (!mbar_wait(k_full + 8 * s, phase, status, 2)) return false;
-                if (!mbar_wait(s_empty + 8 * s, phase ^ 1u, status, 2)) return false;
+                // this buffer held the scores and then P of tile i - 2: its P V was issued before this, and the tensor
+                // pipe runs its instructions in order
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (s ? S_COL1 : S_COL0);
                 const uint64_t k_desc = k_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
@@ -255,17 +264,17 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
                 const int s = j & 1;
-                if (!mbar_wait(p_full, (uint32_t)j & 1u, status, 2)) break;
+                if (!mbar_wait(p_full + 8 * s, (uint32_t)(j >> 1) & 1u, status, 2)) break;
                 if (!mbar_wait(v_full + 8 * s, (uint32_t)(j >> 1) & 1u, status, 2)) break;
                 tc_fence_after();
                 const uint64_t v_desc = v_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
+                const uint32_t p_tmem = tmem_base + (s ? S_COL1 : S_COL0);     // P lies over the scores it came from
 #pragma unroll
-                for (int ks = 0; ks < BKEY / 16; ++ks) {  // 16 keys per MMA
-                    const uint64_t a_desc = p_desc0 + (uint64_t)(((uint32_t)(ks >> 2) * HALF_BYTES + (uint32_t)(ks & 3) * 32u) >> 4);
+                for (int ks = 0; ks < BKEY / 16; ++ks) {  // 16 keys per MMA = 8 columns of packed pairs
                     const uint64_t b_desc = v_desc + (uint64_t)(((uint32_t)ks * (16 * 128)) >> 4);
-                    umma_bf16(tmem_base + O_COL, a_desc, b_desc, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);    // O accumulates over the tiles
+                    umma_bf16_a_tmem(tmem_base + O_COL, p_tmem + (uint32_t)(ks * 8), b_desc, IDESC_PV, (j > 0 || ks > 0) ? 1u : 0u);    // O accumulates over the tiles
                 }
-                umma_commit(pv_full);
+                umma_commit(pv_full + 8 * s);
                 umma_commit(v_empty + 8 * s);
             }
         }
@@ -290,10 +299,6 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
 #pragma unroll
             for (int q = 0; q < QUARTERS; ++q) tmem_load32_start(s_addr + (uint32_t)(q * 32), v[q]);
             tmem_wait_ld();
-            // S is in registers: the buffer may take the scores of tile j + 2
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty + 8 * s);
             // mask only where some row of the block cannot see the whole tile
             const bool masked = pos0 + BKEY - 1 > p_first || (p.window > 0 && pos0 <= p_last - p.window);
             if (masked) {
@@ -316,11 +321,13 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
             const float m_new = moves ? m_tile : m_run;
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = moves ? fast_exp2(m_run - m_use) : 1.f;
-            if (j > 0) {
-                // P V of the tile before: P may be overwritten after it, and O may be scaled
-                if (!mbar_wait(pv_full, (uint32_t)(j - 1) & 1u, status, 3)) { ok = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, moves)) {
+                // O may be scaled once P V of the tile before is complete.  A softmax warp waits for P V only here and at
+                // the end, so it can be behind: the barriers alternate by tile, and since the scores of tile j exist,
+                // every P V up to tile j - 2 is complete, so the barrier of tile j - 1 is in that tile's phase or the next.
+                if (!mbar_wait(pv_full + 8 * ((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, status, 3)) { ok = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, moves)) {
+                {
 #pragma unroll 1
                     for (int c0 = 0; c0 < HD; c0 += 32) {
                         uint32_t o[32];
@@ -332,38 +339,34 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
                     tmem_wait_st();
                 }
             }
-            // P = 2^(s * scale2 - m) as bfloat16 into the swizzled K-major tile (two 64-key halves); the row sum
+            // P = 2^(s * scale2 - m) as bfloat16, two keys to a 32-bit column, over this row's scores in tensor memory
+            // (they are in registers); the row sum
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = -m_use;
 #pragma unroll
-            for (int q = 0; q < QUARTERS; ++q) {
-                uint32_t packed[16];
+            for (int h = 0; h < QUARTERS / 2; ++h) {       // 64 keys = 32 columns per store
+                uint32_t packed[32];
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float e0 = fast_exp2(fmaf(__uint_as_float(v[q][c]), scale2, neg_m));
-                    const float e1 = fast_exp2(fmaf(__uint_as_float(v[q][c + 1]), scale2, neg_m));
-                    sum[c & 2 ? 1 : 0] += e0;
-                    sum[c & 2 ? 3 : 2] += e1;
-                    packed[c >> 1] = pack_bf16(e0, e1);
-                }
-                // 32 keys = four 16-byte chunks of this row; the chunk index inside the 64-key half is XORed with row % 8
-                const uint32_t p_row = p_s + (uint32_t)(q >> 1) * HALF_BYTES + (uint32_t)r * 128u;
+                for (int q = 0; q < 2; ++q)
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const uint32_t chunk = (uint32_t)((q & 1) * 4 + q4) ^ (uint32_t)(r & 7);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + chunk * 16u), "r"(packed[4 * q4]),
-                                 "r"(packed[4 * q4 + 1]), "r"(packed[4 * q4 + 2]), "r"(packed[4 * q4 + 3]) : "memory");
-                }
+                    for (int c = 0; c < 32; c += 2) {
+                        const float e0 = fast_exp2(fmaf(__uint_as_float(v[2 * h + q][c]), scale2, neg_m));
+                        const float e1 = fast_exp2(fmaf(__uint_as_float(v[2 * h + q][c + 1]), scale2, neg_m));
+                        sum[c & 2 ? 1 : 0] += e0;
+                        sum[c & 2 ? 3 : 2] += e1;
+                        packed[q * 16 + (c >> 1)] = pack_bf16(e0, e1);
+                    }
+                tmem_store32(s_addr + (uint32_t)(h * 32), packed);
             }
+            tmem_wait_st();
             // P is written (and O scaled where it had to be): hand both to the MMA
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full + 8 * s);
             l_run = l_run * alpha + (sum[0] + sum[1]) + (sum[2] + sum[3]);
             m_run = m_new;
         }
-        if (ok && mbar_wait(pv_full, (uint32_t)(n_tiles - 1) & 1u, status, 3)) {
+        if (ok && mbar_wait(pv_full + 8 * ((n_tiles - 1) & 1), (uint32_t)((n_tiles - 1) >> 1) & 1u, status, 3)) {
             tc_fence_after();
             const float inv = 1.f / l_run;
             __nv_bfloat16* dst = p.out + ((size_t)(q_begin + q0 + r) * p.nq + head) * HD;
@@ -400,8 +403,8 @@ template <int HD, int BKEY>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcAttnParams& p, int n_seqs,
            int max_q_len, cudaStream_t stream) {
     constexpr uint32_t HALVES = HD / 64;
-    // Q, two key and two value tiles, P, alignment slack, barriers
-    const size_t smem = (size_t)HALVES * HALF_BYTES + 4 * (size_t)HALVES * BKEY * 128 + (size_t)(BKEY / 64) * HALF_BYTES + ALIGN_SLACK + 128 + 64;
+    // Q, two key and two value tiles, alignment slack, barriers
+    const size_t smem = (size_t)HALVES * HALF_BYTES + 4 * (size_t)HALVES * BKEY * 128 + ALIGN_SLACK + 128 + 64;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, BKEY>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -441,7 +444,7 @@ extern "C" int qt_attention_prefill_tc(const void* q, const void* k_cache, const
     if (rc) return rc;
     TcAttnParams p{(__nv_bfloat16*)out, block_table, max_blocks, seq_start, seq_past, nq, nkv, ring_tokens, window, scale, status};
     cudaStream_t s = (cudaStream_t)stream;
-    // key tiles of one page, two blocks per SM: measured 8-12 % faster than tiles of two pages with one block per SM
+    // key tiles of one page, two blocks per SM: measured 12-22 % faster than tiles of two pages with one block per SM
     if (d == 64) return launch<64, 64>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
     return launch<128, 64>(map_q, map_k, map_v, p, n_seqs, max_q_len, s);
 }
