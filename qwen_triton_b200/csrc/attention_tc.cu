@@ -106,6 +106,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Three-input maximum and two-wide float arithmetic (sm_100): half the instructions of the softmax's maximum, scaling
+// and row sum; every lane rounds as the one-wide form does.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ uint64_t pair_u32(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpair_f32(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -314,7 +344,7 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
 #pragma unroll
             for (int q = 0; q < QUARTERS; ++q)
 #pragma unroll
-                for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], __uint_as_float(v[q][c]));
+                for (int c = 0; c < 32; c += 2) mx[(c >> 1) & 3] = max3(mx[(c >> 1) & 3], __uint_as_float(v[q][c]), __uint_as_float(v[q][c + 1]));
             const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;
             // the row's maximum moves only when the true one has run away from it
             const bool moves = m_tile > m_run + RESCALE_STEP;
@@ -341,8 +371,8 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
             }
             // P = 2^(s * scale2 - m) as bfloat16, two keys to a 32-bit column, over this row's scores in tensor memory
             // (they are in registers); the row sum
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
-            const float neg_m = -m_use;
+            uint64_t sum2[2] = {0ull, 0ull};               // two pairs of partial sums
+            const uint64_t scale22 = pair_f32(scale2, scale2), neg_m2 = pair_f32(-m_use, -m_use);
 #pragma unroll
             for (int h = 0; h < QUARTERS / 2; ++h) {       // 64 keys = 32 columns per store
                 uint32_t packed[32];
@@ -350,10 +380,10 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
                 for (int q = 0; q < 2; ++q)
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        const float e0 = fast_exp2(fmaf(__uint_as_float(v[2 * h + q][c]), scale2, neg_m));
-                        const float e1 = fast_exp2(fmaf(__uint_as_float(v[2 * h + q][c + 1]), scale2, neg_m));
-                        sum[c & 2 ? 1 : 0] += e0;
-                        sum[c & 2 ? 3 : 2] += e1;
+                        float x0, x1;
+                        unpair_f32(fma2(pair_u32(v[2 * h + q][c], v[2 * h + q][c + 1]), scale22, neg_m2), x0, x1);
+                        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+                        sum2[(c >> 1) & 1] = add2(sum2[(c >> 1) & 1], pair_f32(e0, e1));
                         packed[q * 16 + (c >> 1)] = pack_bf16(e0, e1);
                     }
                 tmem_store32(s_addr + (uint32_t)(h * 32), packed);
@@ -363,6 +393,9 @@ __global__ void __launch_bounds__(THREADS, BKEY == 64 ? 2 : 1) attention_prefill
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + 8 * s);
+            float sum[4];
+            unpair_f32(sum2[0], sum[0], sum[2]);
+            unpair_f32(sum2[1], sum[1], sum[3]);
             l_run = l_run * alpha + (sum[0] + sum[1]) + (sum[2] + sum[3]);
             m_run = m_new;
         }
