@@ -185,7 +185,7 @@ def time_e2e(model, prompts, steps: int, warmup: int):
     return ms, h2d, 4 * len(prompts)
 
 
-def time_prefill(model, tokens: int, vocab: int, repeats: int = 5, warmup: int = 2):
+def time_prefill(model, tokens: int, vocab: int, repeats: int = 5, warmup: int = 3):
     import torch
     from qwen_triton_b200 import StepEntry
     engine = model.engine
