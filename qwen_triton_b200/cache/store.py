@@ -4,7 +4,7 @@ Layers whose mixers ask for the same thing (kv heads, head size, all keys or a w
 form a *group* with storage of its own: one key and one value pool
 ``[entries, pages, kv_heads, page_tokens, head_dim]`` shared by the group's entries, one page list
 per sequence for the whole group.  Beside the pools each mixer that asks for it has a fixed-size
-state block per slot, ``[num_slots, *shape]``, zeroed when a slot is handed out; the architecture
+state block per slot, ``[num_slots + 1, *shape]`` (the last row is a spare for padded rows), zeroed when a slot is handed out; the architecture
 built here asks for none, and the plumbing is exercised by a toy mixer in the tests.
 """
 from __future__ import annotations
@@ -27,7 +27,7 @@ class CacheView:
     page_tokens: int = 0
     ring_tokens: int = 0              # 0: position p sits at element p; else at p % ring_tokens
     writable: bool = True             # False: this call reads an entry that another call writes
-    state: torch.Tensor | None = None  # [num_slots, *shape]
+    state: torch.Tensor | None = None  # [num_slots + 1, *shape]; the last row belongs to no sequence (padded rows of a fixed-shape step)
 
 
 @dataclass
@@ -85,15 +85,17 @@ class SequenceCache:
         geometry = [GroupGeometry(total_pages, g.ring_tokens // page_tokens) for g in self.groups]
         self.book = CacheBook(self.num_slots, page_tokens, geometry, max_seq_len)
         self.has_window = any(g.ring_tokens for g in self.groups)
-        # one page beyond the book's pool: padded rows of a fixed-shape decode step read and write only this page
+        # one page beyond the book's pool and one state row beyond the slots: padded rows of a fixed-shape decode
+        # step read and write only these, never what a live sequence holds
         self.dummy_page = total_pages
+        self.dummy_slot = self.num_slots
         if allocate:
             for group in self.groups:
                 shape = (len(group.owners), total_pages + 1, group.request.kv_heads, page_tokens, group.request.head_dim)
                 group.k = torch.zeros(shape, dtype=dtype, device=device)
                 group.v = torch.zeros(shape, dtype=dtype, device=device)
             for position, request in self._state_requests.items():
-                self._state_of[position] = torch.zeros((self.num_slots, *request.shape), dtype=request.dtype, device=device)
+                self._state_of[position] = torch.zeros((self.num_slots + 1, *request.shape), dtype=request.dtype, device=device)
 
     # ------------------------------------------------------------------ views
     def view(self, position: int) -> CacheView:

@@ -52,6 +52,7 @@ extern "C" int qt_attention_decode_static(const void* q, const void* k_cache, co
     QT_REQUIRE(ring_tokens >= 0 && ring_tokens % PAGE == 0, "attention_decode_static: the ring of %d tokens is not a whole number of pages", ring_tokens);
     QT_REQUIRE(ring_tokens == 0 || (window > 0 && ring_tokens >= window), "attention_decode_static: a ring of %d tokens cannot hold a window of %d", ring_tokens, window);
     QT_REQUIRE(n_seqs <= 65535 && n_splits >= 1 && n_splits <= 65535, "attention_decode_static: n_seqs=%d, n_splits=%d", n_seqs, n_splits);
+    QT_REQUIRE((long long)nkv * ((nq / nkv + 15) / 16) <= 65535, "attention_decode_static: nkv=%d with groups of %d heads is more than one launch takes", nkv, nq / nkv);
     const long long slots = (long long)n_seqs * nq * n_splits;
     const long long needed = slots * (d + 2);
     QT_REQUIRE(needed <= (long long)QT_STATIC_SCRATCH_FLOATS,

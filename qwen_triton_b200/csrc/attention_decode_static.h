@@ -26,8 +26,9 @@
 //
 // Arguments and result are those of qt_attention_decode_mma without the two scratch pointers:
 // bfloat16 q [n_seqs, nq, d], paged bfloat16 caches [pages, nkv, 64, d], int32 block_table
-// [n_seqs, max_blocks], int32 seq_len [n_seqs], bfloat16 out [n_seqs, nq, d]; head_dim a multiple of
-// 16 up to 128.  Returns 0, or a negative code with the text available from
+// [n_seqs, max_blocks], int32 seq_len [n_seqs] (every entry at least 1: the query's own key is among
+// those it sees; a sequence with no keys has no softmax and its output row would be 0/0), bfloat16 out
+// [n_seqs, nq, d]; head_dim a multiple of 16 up to 128; nkv * ceil((nq / nkv) / 16) at most 65,535.  Returns 0, or a negative code with the text available from
 // qt_last_error_attention_decode_static().
 #pragma once
 

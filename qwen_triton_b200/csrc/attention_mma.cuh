@@ -358,6 +358,8 @@ struct WarpTileCopy {
 template <int DMAX, bool EXACT>
 __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(const MmaParams p) {
     pdl_launch_dependents();
+    const bool merges_in_cluster = p.cluster_merge && gridDim.x > 1;
+    if (merges_in_cluster) cluster_arrive_started();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int d = EXACT ? DMAX : p.d, lds = d + PAD, dsteps = d >> 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -524,6 +526,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
     // use), and after the cluster barrier the first block merges the inboxes and stores the result.
     float* inbox = reinterpret_cast<float*>(smem_raw + q_bytes + (size_t)warps * 4 * tile_bytes);   // [blocks][rows * d + 2 * rows] in block 0
     const int inbox_stride = rows * d + 2 * rows;
+    if (merges_in_cluster) cluster_wait_started();                   // the first block runs (a block with no keys gets here early)
     for (int i = tid; i < rows * d; i += blockDim.x) {
         const int r = i / d, c = i % d;
         float m_all = -INFINITY;
@@ -548,7 +551,7 @@ __global__ void __launch_bounds__(32 * WS_MAX_WARPS) attention_decode_ws_kernel(
             if (c == 0) { p.part_ml[slot * 2] = m_all * LN2; p.part_ml[slot * 2 + 1] = l_all; }   // natural-log domain for the combine kernel
         }
     }
-    if (p.cluster_merge && gridDim.x > 1) {
+    if (merges_in_cluster) {
         cluster_barrier();
         if (split == 0) {
             const int blocks = gridDim.x;

@@ -115,6 +115,12 @@ __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// A block may touch another block's shared memory only once that block has started.  Every thread arrives here at
+// kernel entry and waits just before its block's first remote access; by then every block of the cluster has arrived,
+// so it runs.  (A second, release/acquire barrier still has to follow the remote stores before they are read.)
+__device__ __forceinline__ void cluster_arrive_started() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_started() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

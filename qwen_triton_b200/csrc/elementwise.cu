@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(1024, 1) add_rmsnorm_cluster_kernel(float* __r
                                                                    size_t split_stride, const float* __restrict__ weight, float eps,
                                                                    TO* __restrict__ out, const int* __restrict__ rows, int hidden) {
     pdl_launch_dependents();
+    cluster_arrive_started();
     pdl_wait();
     __shared__ float scratch[32];
     __shared__ float shares[NORM_CLUSTER];
@@ -170,6 +171,7 @@ __global__ void __launch_bounds__(1024, 1) add_rmsnorm_cluster_kernel(float* __r
     }
     const float4 w = c < chunks ? load4(weight + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);   // in flight under the reductions
     const float share = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, scratch);
+    cluster_wait_started();                                    // every block of the cluster runs: its shared memory may be written
     if (threadIdx.x < NORM_CLUSTER) cluster_store_float(&shares[rank], threadIdx.x, share);
     cluster_barrier();
     float total = 0.f;

@@ -12,6 +12,7 @@ length (qwen_triton/modules/cache.py:21), correct for unequal lengths only in pr
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Sequence
@@ -68,7 +69,7 @@ class Engine:
     def __init__(self, spec: ModelSpec, source, *, dtype=torch.bfloat16, max_tokens: int = 8192,
                  max_seq_len: int | None = None, max_step_tokens: int = 4096, device: str | torch.device = "cuda:0",
                  page_tokens: int = 64, chunk_tokens: int = 256, options: dict | None = None,
-                 cuda_graphs: bool = True, max_graph_batch: int = 256) -> None:
+                 cuda_graphs: bool = True, max_graph_batch: int = 256, max_graphs: int = 48) -> None:
         self.device = torch.device(device)
         require_gpu(self.device)
         torch.cuda.set_device(self.device)
@@ -100,7 +101,12 @@ class Engine:
         # launches its kernels one by one.
         stepped = [self.model.embedding, *self.model.blocks, self.model.final_norm, self.model.head]
         self._graphs_enabled = bool(cuda_graphs) and all(getattr(part, "graph_safe", False) for part in stepped)
-        self._graphs: dict[tuple, object] = {}
+        # captured steps by shape, least recently used first; at most ``max_graphs`` are kept (a long generation at
+        # many batch sizes and context buckets would otherwise grow device memory without limit), and all of them
+        # write their logits into one buffer, made at the first one-token step
+        self._graphs: OrderedDict[tuple, object] = OrderedDict()
+        self.max_graphs = max(1, int(max_graphs))
+        self._graph_logits: torch.Tensor | None = None
         self._status_host = torch.zeros(4, dtype=torch.int32, pin_memory=True)
         self._status_event: torch.cuda.Event | None = None
         self.max_graph_batch = max_graph_batch
@@ -188,6 +194,8 @@ class Engine:
         """Run the given tokens; return float logits [sum of wanted places, vocab] in the order of
         the entries and, within an entry, of its ``want`` list."""
         entries = list(entries)
+        if not entries:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         book = self.cache.book
         seen: set[int] = set()
         targets: dict[int, int] = {}
@@ -317,8 +325,8 @@ class Engine:
 
     def _plan_decode(self, slots: list[int], extend: bool) -> "PlannedDecode":
         """Fixed shape of a one-token step: batch padded to a power of two, page tables to a multiple of 16 pages, so
-        that a captured CUDA graph can be replayed.  Padded rows read and write only the cache's spare page, and
-        their logits are dropped."""
+        that a captured CUDA graph can be replayed.  Padded rows read and write only the cache's spare page and
+        spare state row, and their logits are dropped."""
         book, cache = self.cache.book, self.cache
         count = len(slots)
         padded = 1
@@ -342,7 +350,7 @@ class Engine:
             tables.append(table)
         context = -(-(max(past) + 1) // 1024) * 1024
         pad = padded - count
-        prepared = self._ctx.prepare_decode(slots + [0] * pad, past + [0] * pad, tables)
+        prepared = self._ctx.prepare_decode(slots + [cache.dummy_slot] * pad, past + [0] * pad, tables)
         return PlannedDecode(slots=tuple(slots), lengths=tuple(p + 1 for p in past), count=count, padded=padded,
                              key=(padded, tuple(widths), context), context=context, prepared=prepared)
 
@@ -352,21 +360,29 @@ class Engine:
         self._ctx.commit_decode(plan.prepared, tokens + [fill] * (padded - count), plan.context, chosen, self.spec.vocab_size)
         self.last_meta_bytes = self._ctx.meta_bytes
         key = plan.key
+        if self._graph_logits is None:         # one buffer for every shape: a replay's rows are copied out of it anyway
+            most = min(self.max_graph_batch, self.max_step_tokens // 2)
+            rows = 1
+            while rows < most:
+                rows *= 2
+            self._graph_logits = torch.empty((rows, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        logits = self._graph_logits[:padded]
         state = self._graphs.get(key)
         if state is None:                      # first time at this shape: run the launches themselves
-            logits = torch.empty((padded, self.spec.vocab_size), dtype=torch.float32, device=self.device)
             self.model.forward(self._ctx, cache, logits)
             self._graphs[key] = "warm"
-            return logits[:count]
+            while len(self._graphs) > self.max_graphs:
+                self._graphs.popitem(last=False)
+            return logits[:count].clone()
+        self._graphs.move_to_end(key)
         if state == "warm":                    # second time: capture (nothing runs during capture), then replay
-            logits = torch.empty((padded, self.spec.vocab_size), dtype=torch.float32, device=self.device)
             graph = torch.cuda.CUDAGraph()
             before = kernels.launch_count()
             with torch.cuda.graph(graph):
                 self.model.forward(self._ctx, cache, logits)
-            state = (graph, logits, kernels.launch_count() - before)
+            state = (graph, kernels.launch_count() - before)
             self._graphs[key] = state
-        graph, logits, launches = state
+        graph, launches = state
         graph.replay()
         kernels.count_launches(launches)
         self.graph_replays += 1

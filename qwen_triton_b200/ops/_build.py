@@ -116,6 +116,9 @@ def compile_library(name: str, verbose: bool = True) -> Path:
         tmp.unlink(missing_ok=True)
         raise BuildError(f"nvcc failed on {source.name} (exit {proc.returncode}):\n{output}")
     os.replace(tmp, target)
+    for stale in target.parent.glob(f"libqt_{name}-*.so"):      # libraries of earlier versions of this source
+        if stale != target and ".tmp" not in stale.name:
+            stale.unlink(missing_ok=True)
     if verbose:
         print(f"[qwen_triton_b200] built {target.name} in {time.time() - started:.1f} s", file=sys.stderr, flush=True)
     return target

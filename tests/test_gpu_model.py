@@ -259,4 +259,9 @@ def test_errors_are_loud(case):
     engine.release(slot)
     with pytest.raises(ValueError, match="not in use"):
         engine.step([StepEntry(slot, [1], [0])])
-    assert engine.length is not None
+    # the refused steps changed nothing: a fresh sequence starts at length 0 and a step of 3 tokens makes it 3
+    slot = engine.new_sequence()
+    assert engine.length(slot) == 0
+    engine.step([StepEntry(slot, [1, 2, 3], [])])
+    assert engine.length(slot) == 3
+    engine.release(slot)

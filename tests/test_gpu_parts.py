@@ -208,7 +208,7 @@ class ToyConfig:
         norm = PartSpec("rmsnorm", {"size": hidden, "eps": r["eps"]})
         block = PartSpec("pre_norm", {"mixer": "mixer", "feed_forward": "ff", "mixer_norm": "norm1", "feed_forward_norm": "norm2"})
         ff = PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": r["inter"], "activation": "silu"})
-        toy = PartSpec("toy_decay", {"hidden_size": hidden, "decay": r["decay"]})
+        toy = PartSpec(r.get("mixer_kind", "toy_decay"), {"hidden_size": hidden, "decay": r["decay"]})
         attn = PartSpec("attention", {"hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "window": None,
                                       "qk_norm": False, "position": PartSpec("none"),
                                       "q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"})
@@ -306,4 +306,55 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype):
             rows[i].append(out[row:row + 1])
     for i in (0, 1):
         assert_close(torch.cat(rows[i]), toy_oracle(raw, wf, requests[i]), dtype, f"toy model, request {i} step by step")
+        engine.release(slots[i])
+
+
+class ToyDecayMixerOnDevice(ToyDecayMixer):
+    """The same recurrence with a one-token step that only launches device work (gather the state rows of the
+    step's slots, update, scatter back), so that it may say ``graph_safe`` and its steps are captured in CUDA graphs."""
+
+    graph_safe = True
+
+    def forward(self, x, ctx, cache):
+        if not ctx.is_decode:
+            return super().forward(x, ctx, cache)
+        slots = ctx.slots.long()
+        state = self.decay * cache.state.index_select(0, slots) + x.float() @ self.weight.T
+        cache.state.index_copy_(0, slots, state)
+        return GemmOut(state.to(self.runtime.dtype)[None].contiguous())
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_padded_rows_of_a_captured_step_leave_every_live_state_alone(dtype):
+    """Three sequences run as a captured step of four rows; the padded row must not touch the state of the
+    sequence in slot 0 (it has a spare state row of its own, as it has a spare cache page)."""
+    register_mixer("toy_decay_device", ToyDecayMixerOnDevice)
+    register_architecture("ToyForCausalLM", ToyConfig)
+    raw = {"architectures": ["ToyForCausalLM"], "hidden_size": 40, "inter": 56, "vocab": 97, "eps": 1e-5, "decay": 0.8,
+           "mixer_kind": "toy_decay_device"}
+    from qwen_triton_b200.config import config_from_dict
+    from qwen_triton_b200.engine.model import expected_tensors
+    import json
+    config = config_from_dict(raw)
+    weights = weights_for(expected_tensors(config.model_spec()), dtype, seed=10)
+    with tempfile.TemporaryDirectory() as folder:
+        write_safetensors(f"{folder}/model.safetensors", weights)
+        with open(f"{folder}/config.json", "w") as handle:
+            json.dump(raw, handle)
+        engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
+    assert engine._graphs_enabled
+    wf = {k: v.float() for k, v in weights.items()}
+    requests = [[5, 9, 2, 77, 30, 11, 4, 8, 60], [96, 0, 41, 7, 7, 19, 3], [1, 2, 3, 4, 5, 6, 7, 8]]
+    slots = [engine.new_sequence() for _ in requests]
+    assert 0 in slots
+    prompt = 3
+    first = engine.step([StepEntry(slot, tokens[:prompt], [prompt - 1]) for slot, tokens in zip(slots, requests)])
+    rows = {i: [first[i:i + 1]] for i in range(3)}
+    for at in range(prompt, 7):                                  # four one-token steps: launched, captured, replayed twice
+        out = engine.step([StepEntry(slot, [tokens[at]], [0]) for slot, tokens in zip(slots, requests)])
+        for i in range(3):
+            rows[i].append(out[i:i + 1])
+    assert engine.graph_replays >= 2
+    for i, tokens in enumerate(requests):
+        assert_close(torch.cat(rows[i]), toy_oracle(raw, wf, tokens)[prompt - 1:7], dtype, f"request {i} in slot {slots[i]}")
         engine.release(slots[i])

@@ -3,9 +3,10 @@
 Some hosts of this kernel cannot allocate device memory when they need it: a plug-in inside another
 program's CUDA context with a fixed budget, a loop whose buffers are frozen after set-up, code inside
 a stream capture.  For them ``qt_attention_decode_static`` keeps the split-KV scratch in a fixed array
-inside the library.  The test calls it twice in a row (the second call finds the first call's leftovers
-in the shared scratch) and compares both results with the regular entry point, which takes scratch
-from the caller.  It is collected last so that a failure here cannot hide another test's result, and
+inside the library.  The test calls it several times in a row (each later call finds the leftovers of the
+one before in the shared scratch) and compares every result with a plain float32 statement of the
+attention (so a wrong kernel fails here too) and, bit for bit, with the regular entry point, which runs
+the same kernels on scratch from the caller.  It is collected last so that a failure here cannot hide another test's result, and
 it sets up everything it needs itself, so it also passes alone in a fresh process.
 """
 import ctypes
@@ -32,6 +33,21 @@ def _paged_case(seed, n_seqs, nq, nkv, d, lengths):
         cursor += count
     q = torch.randn(n_seqs, nq, d, generator=generator).bfloat16().cuda()
     return q, k_cache, v_cache, table.cuda(), torch.tensor(lengths, dtype=torch.int32).cuda()
+
+
+def _plain_attention(q, k_cache, v_cache, table, seq_len, nkv):
+    """softmax(q k^T / sqrt(d)) v per sequence in float32, from the keys and values the page table names."""
+    out = torch.empty(q.shape, dtype=torch.float32)
+    n_seqs, nq, d = q.shape
+    for b in range(n_seqs):
+        n = int(seq_len[b])
+        pages = table[b, :math.ceil(n / PAGE)].long().cpu()
+        k = k_cache.cpu()[pages].float().permute(0, 2, 1, 3).reshape(-1, nkv, d)[:n]      # [n, nkv, d]
+        v = v_cache.cpu()[pages].float().permute(0, 2, 1, 3).reshape(-1, nkv, d)[:n]
+        k, v = k.repeat_interleave(nq // nkv, dim=1), v.repeat_interleave(nq // nkv, dim=1)
+        scores = torch.einsum("hd,khd->hk", q[b].float().cpu(), k) * d ** -0.5
+        out[b] = torch.einsum("hk,khd->hd", torch.softmax(scores, dim=-1), v)
+    return out
 
 
 def test_static_scratch_entry_point_matches_the_regular_one():
@@ -68,9 +84,10 @@ def test_static_scratch_entry_point_matches_the_regular_one():
         code, out = call(*case, nkv, splits)
         assert code == 0, _build.last_error("attention_decode_static")
         torch.cuda.synchronize()
-        expected = regular(*case, nkv, splits)
-        # the tolerance of the bfloat16 kernel tests; the two entry points run the same kernels
-        torch.testing.assert_close(out.float(), expected.float(), atol=2e-2, rtol=2e-2)
+        # the tolerance of the bfloat16 kernel tests against the plain statement; the two entry points run the same
+        # kernels in the same order, so their results are the same bits
+        torch.testing.assert_close(out.float().cpu(), _plain_attention(*case, nkv), atol=2e-2, rtol=2e-2)
+        assert torch.equal(out, regular(*case, nkv, splits))
 
     # a request beyond the built-in scratch is refused, and says so
     q, k_cache, v_cache, table, seq_len = _paged_case(3, 64, 32, 8, 128, [64] * 64)
@@ -78,3 +95,8 @@ def test_static_scratch_entry_point_matches_the_regular_one():
     assert code != 0
     message = _build.last_error("attention_decode_static")
     assert "scratch" in message and str(64 * 32 * 64 * 130) in message
+    # so are more (kv head, 16-head chunk) pairs than one launch takes
+    q, k_cache, v_cache, table, seq_len = _paged_case(4, 1, 1, 1, 16, [64])
+    code = fn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q.data_ptr(), table.data_ptr(), 1, seq_len.data_ptr(),
+              1, 70000, 70000, 16, PAGE, 0, 0, 0.25, 1, stream)
+    assert code != 0 and "one launch" in _build.last_error("attention_decode_static")
