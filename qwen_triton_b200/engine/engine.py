@@ -124,12 +124,16 @@ class Engine:
         return engine
 
     @classmethod
-    def from_config(cls, config, seed: int = 0, **kwargs) -> "Engine":
-        """Seeded random weights drawn on the device (no model folder is written)."""
+    def from_config(cls, config, seed: int = 0, weights_dtype=None, **kwargs) -> "Engine":
+        """Seeded random weights drawn on the device (no model folder is written): the same values that
+        ``write_random_model`` writes for this seed.  ``weights_dtype`` is the element type a model folder would
+        store them in (by default the compute type): a float32 engine with ``weights_dtype="bf16"`` runs the very
+        weights of the bfloat16 model in true 32-bit arithmetic."""
         spec = config.model_spec()
         dtype = parse_dtype(kwargs.get("dtype", torch.bfloat16))
         device = kwargs.get("device", "cuda:0")
-        engine = cls(spec, random_source(expected_tensors(spec), seed, dtype, device), **kwargs)
+        stored = parse_dtype(weights_dtype) if weights_dtype is not None else None
+        engine = cls(spec, random_source(expected_tensors(spec), seed, dtype, device, stored), **kwargs)
         engine.config = config
         return engine
 

@@ -5,8 +5,8 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from gpu_util import PRESETS, assert_close, make_engine, model_folder, oracle, plain_logits, random_tokens, run_whole
-from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset
+from gpu_util import PRESETS, SEEDS, assert_close, make_engine, model_folder, oracle, plain_logits, random_tokens, run_whole
+from qwen_triton_b200 import Engine, QwenB200ForCausalLM, StepEntry, load_preset
 
 pytestmark = pytest.mark.gpu
 DTYPES = ("fp32", "bf16")
@@ -265,3 +265,18 @@ def test_errors_are_loud(case):
     engine.step([StepEntry(slot, [1, 2, 3], [])])
     assert engine.length(slot) == 3
     engine.release(slot)
+
+
+def test_random_weights_are_the_same_bits_on_the_device_and_on_the_host():
+    """``Engine.from_config(seed)`` draws on the device what ``write_random_model(seed)`` writes from the host."""
+    from qwen_triton_b200.weights import random_tensor
+    from qwen_triton_b200.weights.tensors import TensorSpec
+    for name, spec in (("a.weight", TensorSpec((301, 77), init_std=0.02)),
+                       ("b.weight", TensorSpec((513,), role="vector", init_std=0.1, init_mean=1.0))):
+        for dtype in (torch.float32, torch.bfloat16):
+            assert torch.equal(random_tensor(name, spec, 3, dtype, "cuda:0").cpu(), random_tensor(name, spec, 3, dtype))
+    preset, dtype = "tiny-b", "bf16"
+    tokens = random_tokens(preset, 29, 77)
+    drawn = Engine.from_config(load_preset(preset), seed=SEEDS[preset], dtype=dtype, max_tokens=256)
+    loaded = make_engine(preset, dtype, max_tokens=256)
+    assert torch.equal(run_whole(drawn, tokens), run_whole(loaded, tokens))

@@ -6,6 +6,7 @@ import torch
 
 from qwen_triton_b200.config import load_preset
 from qwen_triton_b200.engine.model import expected_tensors
+from qwen_triton_b200.weights.tensors import TensorSpec
 from qwen_triton_b200.weights import (Checkpoint, WeightsError, kept_dtype, open_checkpoint, random_tensor,
                                       write_random_model, write_safetensors)
 
@@ -108,3 +109,35 @@ def test_missing_folder_and_kept_precisions(tmp_path):
     assert kept_dtype(expected["model.norm.weight"], torch.bfloat16) == torch.float32       # vectors stay 32-bit
     assert kept_dtype(expected["model.embed_tokens.weight"], torch.bfloat16) == torch.bfloat16
     assert kept_dtype(expected["model.embed_tokens.weight"], torch.float32) == torch.float32
+
+
+def test_random_draw_is_the_stated_integer_recipe():
+    """Element i = (sum of the twelve 16-bit fields of splitmix64 outputs 3i+1..3i+3 of the tensor's stream - 393210) / 65536,
+    restated here in plain Python integers."""
+    from qwen_triton_b200.weights.random_init import _tensor_seed, standard_normal
+    mask = (1 << 64) - 1
+
+    def mix(v):
+        v = ((v ^ (v >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        v = ((v ^ (v >> 27)) * 0x94D049BB133111EB) & mask
+        return v ^ (v >> 31)
+
+    def element(stream, i):
+        total = 0
+        for j in range(3):
+            word = mix(((3 * i + j + 1) * 0x9E3779B97F4A7C15 + stream) & mask)
+            total += sum((word >> (16 * f)) & 0xFFFF for f in range(4))
+        return (total - 393210) / 65536.0
+
+    stream = _tensor_seed(4, "model.norm.weight")
+    drawn = standard_normal(stream, 1000, 64)
+    assert drawn.tolist() == [element(stream, i) for i in range(1000, 1064)]
+    many = standard_normal(stream, 0, 1 << 18)
+    assert abs(float(many.mean())) < 0.01 and abs(float(many.std()) - 1.0) < 0.01
+    # a tensor is the same whether it is drawn in one piece or in several
+    spec = TensorSpec((3, 50), init_std=0.02)
+    whole = random_tensor("w", spec, 9, torch.float32)
+    assert torch.equal(whole.flatten()[37:91], standard_normal(_tensor_seed(9, "w"), 37, 54) * 0.02 + 0.0)
+    # stored in bfloat16, computed in float32: the bfloat16 values, exactly
+    assert torch.equal(random_tensor("w", spec, 9, torch.float32, store_dtype=torch.bfloat16),
+                       random_tensor("w", spec, 9, torch.bfloat16).float())
