@@ -75,3 +75,36 @@ def assert_close(actual: torch.Tensor, expected: torch.Tensor, dtype: str, what:
         worst = float((actual - expected).abs().max())
         raise AssertionError(f"{what}: {int(bad.sum())} values differ, first wrong row {rows[0]} of {bad.shape[0]} "
                              f"(wrong rows {rows[:12]}), max abs error {worst:.3e}")
+
+
+@functools.lru_cache(maxsize=None)
+def peaky_folder(preset: str, dtype: str, gain: float = 1.5) -> Path:
+    """The preset's random model with every q_norm and k_norm weight multiplied by ``gain``: scores spread
+    ``gain`` squared times as far, fewer keys carry each softmax, and a key that is missed, misplaced or read
+    from the wrong page changes the logits by more (with plain random weights attention over hundreds of keys is
+    nearly flat).  The gain also amplifies rounding, smoothly: measured at 1,100 tokens, the worst error over the
+    tolerance is 0.03 / 0.16 (float32 / bfloat16) at gain 1, 0.24 / 0.77 at 1.5, 1.06 / 3.2 at 2; 1.5 is the largest
+    that leaves the tolerances of the other model tests in place."""
+    from qwen_triton_b200.weights import write_safetensors
+    source = model_folder(preset, dtype)
+    checkpoint = Checkpoint(source)
+    tensors = {}
+    for name in checkpoint.names():
+        tensor = checkpoint.read(name)
+        if name.endswith(("q_norm.weight", "k_norm.weight")):
+            tensor = (tensor.float() * gain).to(tensor.dtype)
+        tensors[name] = tensor
+    holder = tempfile.TemporaryDirectory(prefix=f"qt_{preset}_{dtype}_peaky_")
+    _KEEP.append(holder)
+    folder = Path(holder.name)
+    write_safetensors(folder / "model.safetensors", tensors)
+    (folder / "config.json").write_text((source / "config.json").read_text())
+    return folder
+
+
+@functools.lru_cache(maxsize=None)
+def folder_logits(folder: Path, preset: str, tokens: tuple[int, ...]) -> torch.Tensor:
+    """The plain implementation's logits for the model in ``folder``."""
+    checkpoint = Checkpoint(folder)
+    weights = {name: checkpoint.read(name).float() for name in checkpoint.names()}
+    return plain.forward(load_preset(preset).to_hf_dict(), weights, list(tokens))
