@@ -7,7 +7,7 @@ as in the reference's ``_reset_parameters`` (qwen_triton/models/core.py:265-272)
 wrong weight changes the logits.
 
 The draw is the same bits wherever it is made: element ``i`` of a tensor is the sum of twelve 16-bit
-fields of three splitmix64 outputs (counters 3i, 3i+1, 3i+2 of the tensor's stream), centred and divided
+fields of three splitmix64 outputs (numbers 3i+1, 3i+2, 3i+3 of the tensor's stream), centred and divided
 by 65,536, which is a standard normal to within its twelfth-order Irwin-Hall approximation (tails end at
 six sigma).  Only integer operations and two exactly rounded float operations are involved, so a model
 drawn on the device (``Engine.from_config``) and a model folder written on the host
@@ -23,7 +23,7 @@ from typing import Mapping
 
 import torch
 
-from .safetensors_io import write_safetensors
+from .safetensors_io import write_safetensors_from
 from .tensors import TensorSpec
 
 _MASK64 = (1 << 64) - 1
@@ -98,19 +98,19 @@ def random_source(expected: Mapping[str, TensorSpec], seed: int, dtype: torch.dt
     return source
 
 
-def write_random_model(folder: str | Path, config, seed: int, dtype: torch.dtype = torch.bfloat16) -> Path:
-    """Write ``config.json`` and ``model.safetensors`` for ``config`` with seeded random weights."""
+def write_random_model(folder: str | Path, config, seed: int, dtype: torch.dtype = torch.bfloat16,
+                       device: str | torch.device = "cpu") -> Path:
+    """Write ``config.json`` and ``model.safetensors`` for ``config`` with seeded random weights.  ``device`` is
+    where the values are drawn (the same bits anywhere; a device draws a large model much faster); they are written
+    tensor by tensor."""
     from ..engine.model import expected_tensors  # parts declare the tensors; no device is touched
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    expected = expected_tensors(config.model_spec())
-    tensors = {}
-    for name, spec in expected.items():
-        if spec.optional:
-            continue
-        tensors[name] = random_tensor(name, spec, seed, dtype if spec.role != "table" else torch.int32)
-    write_safetensors(folder / "model.safetensors", tensors)
+    expected = {name: spec for name, spec in expected_tensors(config.model_spec()).items() if not spec.optional}
+    entries = {name: (dtype if spec.role != "table" else torch.int32, tuple(spec.shape)) for name, spec in expected.items()}
+    write_safetensors_from(folder / "model.safetensors", entries,
+                           lambda name: random_tensor(name, expected[name], seed, entries[name][0], device))
     raw = config.to_hf_dict()
     raw["torch_dtype"] = {torch.bfloat16: "bfloat16", torch.float32: "float32"}.get(dtype, str(dtype))
     with (folder / "config.json").open("w", encoding="utf-8") as handle:

@@ -89,17 +89,25 @@ class Checkpoint:
 
 
 def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor]) -> None:
-    """Write ``tensors`` (CPU, any listed dtype) as one safetensors file, names sorted."""
+    """Write ``tensors`` (any listed dtype) as one safetensors file, names sorted."""
+    write_safetensors_from(path, {name: (t.dtype, tuple(t.shape)) for name, t in tensors.items()}, tensors.__getitem__)
+
+
+def write_safetensors_from(path: str | Path, entries: dict[str, tuple[torch.dtype, tuple[int, ...]]], produce) -> None:
+    """The same file from ``produce(name) -> tensor``, called once per tensor in the order they are written, so
+    that a model larger than the host would like to hold at once can be written tensor by tensor."""
     header: dict[str, dict] = {}
     offset = 0
-    order = sorted(tensors)
+    order = sorted(entries)
     for name in order:
-        tensor = tensors[name]
-        if tensor.dtype not in _DTYPE_NAMES:
-            raise ValueError(f"cannot store dtype {tensor.dtype}")
-        size = tensor.numel() * tensor.element_size()
-        header[name] = {"dtype": _DTYPE_NAMES[tensor.dtype], "shape": list(tensor.shape),
-                        "data_offsets": [offset, offset + size]}
+        dtype, shape = entries[name]
+        if dtype not in _DTYPE_NAMES:
+            raise ValueError(f"cannot store dtype {dtype}")
+        count = 1
+        for dim in shape:
+            count *= dim
+        size = count * torch.empty((), dtype=dtype).element_size()
+        header[name] = {"dtype": _DTYPE_NAMES[dtype], "shape": list(shape), "data_offsets": [offset, offset + size]}
         offset += size
     blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
     blob += b" " * (-len(blob) % 8)
@@ -107,5 +115,9 @@ def write_safetensors(path: str | Path, tensors: dict[str, torch.Tensor]) -> Non
         handle.write(struct.pack("<Q", len(blob)))
         handle.write(blob)
         for name in order:
-            tensor = tensors[name].detach().contiguous().cpu()
-            handle.write(tensor.reshape(-1).view(torch.uint8).numpy().tobytes() if tensor.numel() else b"")
+            dtype, shape = entries[name]
+            tensor = produce(name).detach().contiguous().cpu()
+            if tensor.dtype != dtype or tuple(tensor.shape) != tuple(shape):
+                raise ValueError(f"{name}: produced {tensor.dtype} {tuple(tensor.shape)}, declared {dtype} {tuple(shape)}")
+            if tensor.numel():
+                handle.write(memoryview(tensor.reshape(-1).view(torch.uint8).numpy()))

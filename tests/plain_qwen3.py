@@ -2,7 +2,8 @@
 
 Written from the formulas of luozoupi/Qwen-Triton (each function cites the
 file and lines it restates).  Whole sequences only, no cache, one function per
-part, float32 (or float64 on request) throughout, plain tensor operations.  It
+part, float32 (or float64 on request) throughout, plain tensor operations, on whatever device
+its weights lie (a large model's oracle runs on the GPU, with library products in full precision).  It
 shares no code with the ``qwen_triton_b200`` package: it reads the raw
 config.json mapping itself and takes weights as a ``name -> tensor`` mapping.
 
@@ -53,6 +54,12 @@ def read_config(raw: Mapping) -> dict:
 
 
 # ----------------------------------------------------------------------------- parts
+def _wide(x: torch.Tensor) -> torch.Tensor:
+    """float32 and float64 stay; a 16-bit model dtype is widened to float32, as the reference's kernels do inside
+    norms, rotation, softmax and the SiLU gate before they round their result once to the model dtype."""
+    return x if x.dtype in (torch.float32, torch.float64) else x.float()
+
+
 def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """Row gather (qwen_triton/kernels/embedding.py:34-35)."""
     return table[ids]
@@ -60,26 +67,29 @@ def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """y = x * rsqrt(mean(x^2) + eps) * w over the last dim (qwen_triton/kernels/rmsnorm.py:35-42)."""
-    variance = x.pow(2).mean(dim=-1, keepdim=True)
-    return x * torch.rsqrt(variance + eps) * weight
+    wide = _wide(x)
+    variance = wide.pow(2).mean(dim=-1, keepdim=True)
+    return (wide * torch.rsqrt(variance + eps) * _wide(weight)).to(x.dtype)
 
 
 def rope_tables(positions: torch.Tensor, rotary_dim: int, theta: float, dtype: torch.dtype):
     """inv_freq[j] = theta^(-2j/rd); angle = pos * inv_freq; cos/sin of the angle
     (qwen_triton/modules/rotary.py:14-26).  Returns the half tables [S, rd/2]."""
-    exponent = torch.arange(0, rotary_dim, 2, dtype=torch.float32) / rotary_dim
-    inv_freq = (1.0 / (theta ** exponent)).to(dtype)
-    angles = positions.to(dtype)[:, None] * inv_freq[None, :]
-    return angles.cos(), angles.sin()
+    exponent = torch.arange(0, rotary_dim, 2, dtype=torch.float32, device=positions.device) / rotary_dim
+    work = dtype if dtype in (torch.float32, torch.float64) else torch.float32      # rotary.py:22: angles in float32
+    inv_freq = (1.0 / (theta ** exponent)).to(work)
+    angles = positions.to(work)[:, None] * inv_freq[None, :]
+    return angles.cos().to(dtype), angles.sin().to(dtype)                           # rotary.py:25-26: tables in the model dtype
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     """Rotate-half on x [S, heads, d]: o1 = x1 cos - x2 sin, o2 = x2 cos + x1 sin; dims beyond
     the rotary width pass through (qwen_triton/kernels/rope.py:59-69)."""
     half = cos.shape[-1]
-    x1, x2, rest = x[..., :half], x[..., half:2 * half], x[..., 2 * half:]
-    c, s = cos[:, None, :], sin[:, None, :]
-    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1)
+    wide = _wide(x)
+    x1, x2, rest = wide[..., :half], wide[..., half:2 * half], wide[..., 2 * half:]
+    c, s = _wide(cos)[:, None, :], _wide(sin)[:, None, :]
+    return torch.cat((x1 * c - x2 * s, x2 * c + x1 * s, rest), dim=-1).to(x.dtype)
 
 
 def attention_scores(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
@@ -94,16 +104,18 @@ def attention_scores(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     """
     seq, nq, d = q.shape
     groups = nq // k.shape[1]
+    out_dtype = q.dtype
+    q, k, v = _wide(q), _wide(k), _wide(v)                       # attention.py:110-123: scores, softmax and PV in float32
     k = k.repeat_interleave(groups, dim=1)
     v = v.repeat_interleave(groups, dim=1)
     scores = torch.einsum("qhd,khd->hqk", q, k) * scale
-    pos = torch.arange(seq)
+    pos = torch.arange(seq, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window is not None:
         visible &= pos[None, :] > (pos[:, None] - window)
     scores = scores.masked_fill(~visible[None], torch.finfo(scores.dtype).min)
     probs = torch.softmax(scores, dim=-1)
-    return torch.einsum("hqk,khd->qhd", probs, v)
+    return torch.einsum("hqk,khd->qhd", probs, v).to(out_dtype)
 
 
 def attention_layer(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str, cfg: dict,
@@ -117,7 +129,7 @@ def attention_layer(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str,
     v = (x @ w[f"{prefix}.v_proj.weight"].T).view(seq, cfg["kv_heads"], d)
     q = rms_norm(q, w[f"{prefix}.q_norm.weight"], cfg["eps"])
     k = rms_norm(k, w[f"{prefix}.k_norm.weight"], cfg["eps"])
-    cos, sin = rope_tables(torch.arange(seq), cfg["rotary_dim"], cfg["theta"], x.dtype)
+    cos, sin = rope_tables(torch.arange(seq, device=x.device), cfg["rotary_dim"], cfg["theta"], x.dtype)
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     out = attention_scores(q, k, v, d ** -0.5, window)
     return out.reshape(seq, cfg["heads"] * d) @ w[f"{prefix}.o_proj.weight"].T
@@ -127,7 +139,8 @@ def gated_mlp(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str) -> to
     """down(silu(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:19-22; kernels/swiglu.py:35-36)."""
     gate = x @ w[f"{prefix}.gate_proj.weight"].T
     up = x @ w[f"{prefix}.up_proj.weight"].T
-    return (gate * torch.sigmoid(gate) * up) @ w[f"{prefix}.down_proj.weight"].T
+    act = (_wide(gate) * torch.sigmoid(_wide(gate)) * _wide(up)).to(x.dtype)        # swiglu.py:84-92: float32 inside, one rounding
+    return act @ w[f"{prefix}.down_proj.weight"].T
 
 
 def decoder_layer(x: torch.Tensor, w: Mapping[str, torch.Tensor], index: int, cfg: dict) -> torch.Tensor:
