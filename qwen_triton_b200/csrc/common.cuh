@@ -56,6 +56,19 @@ static thread_local char g_error[512] = "";
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Streaming multiprocessors of the current device (asked once per device).
+inline int sm_count() {
+    static int counts[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+    if (counts[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 1;
+        counts[device] = n;
+    }
+    return counts[device];
+}
+
 inline bool pdl_enabled() {
     static int enabled = -1;
     if (enabled < 0) {

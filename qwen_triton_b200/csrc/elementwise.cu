@@ -633,7 +633,7 @@ extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long l
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = inter % 8 == 0 && group % 8 == 0 && split_stride % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0);
     long long blocks = (total + threads - 1) / threads;
-    if (blocks > 148LL * 16) blocks = 148LL * 16;
+    if (blocks > (long long)sm_count() * 16) blocks = (long long)sm_count() * 16;
     // few tokens (decode): one chunk per thread, most blocks; many tokens (prefill): two chunks per thread
     const int per_thread = n_tokens >= 256 ? 2 : 1;
     unsigned per_row = (unsigned)((inter / 8 + threads * per_thread - 1) / (threads * per_thread));

@@ -1,0 +1,424 @@
+// bfloat16 matrix product for few tokens (a decode step) with what follows it done in the same launch.
+//
+// Y[M, N] = X[M, K] * W[N, K]^T as in gemm_tc.cu: the weight is the MMA's A operand (128 rows per tile), the tokens
+// its B operand, TMA stages 64-element K slices, tcgen05.mma accumulates in tensor memory.  With few tokens the
+// product is bound by reading the weight, so K is cut into `splits` ranges to have blocks on every SM; here the
+// blocks of one weight tile form a thread-block cluster and add their partial sums through distributed shared
+// memory (each block parks its accumulator tile in its own shared memory, and after a cluster barrier every block
+// sums, in the fixed order of the ranks, a share of the tile's tokens from all of them).  No partial sums pass
+// through global memory, and the kernel that used to add them up is not needed: its work is this kernel's epilogue.
+//
+//   STORE     out[m, n] = s_m * y                       float or bfloat16 (the output head)
+//   RESIDUAL  r = residual[m, n] + y; residual[m, n] = r;  and, for the norm that follows, xw[m, n] = bf16(r * g[n])
+//             and sq_out[tile, m] = sum over the tile's 128 columns of r^2
+//   SWIGLU    act[m, f] = silu(s_m * gate) * (s_m * up), the weight's rows alternating 16 of gate and 16 of up
+//   QKV       per head (head_dim divides 128): s_m * y, RMSNorm over the head with q or k weight, rotate-half by the
+//             cos/sin table at the token's position, then q to q_out and k, v into the paged cache
+//
+// s_m is the factor of an RMSNorm whose weight g was applied by the producer of X (X = bf16(r * g)):
+// s_m = rsqrt(sum over tiles of sq_in[tile, m] / hidden + eps); the product is linear in X, so scaling the result
+// equals normalising the input.  sq_in == nullptr means s_m = 1.  Partial sums of squares are kept per tile and added
+// in a fixed order: results do not depend on scheduling.
+//
+// Warp roles and bounded waits as in gemm_tc.cu.  Every thread of every block reaches both cluster barriers whatever
+// happens before them, so no block waits for one that has left.
+//
+// Counterparts in luozoupi/Qwen-Triton: kernels/matmul.py:52-97, kernels/rmsnorm.py:100-133, kernels/residual_add.py:50-60,
+// kernels/swiglu.py:84-92, kernels/rope.py:99-120, kernels/cache.py:71-98 (one launch each, or two).
+#include "tc_common.cuh"
+
+using namespace qt;
+using namespace qt_tc;
+
+namespace {
+
+constexpr int BW = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t W_BYTES = BW * BK * 2;
+constexpr int MAX_SPLITS = 8;              // portable cluster size
+
+enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+
+struct FusedParams {
+    int M, N, kb_total, kb_per_split, stages, splits;
+    int* status;
+    // the deferred factor of the norm in front of this product
+    const float* sq_in; int sq_tiles; float inv_hidden; float eps;
+    // STORE / SWIGLU
+    void* out; int out_is_float;
+    // RESIDUAL
+    float* residual; const float* norm_w; __nv_bfloat16* xw; float* sq_out;
+    // QKV
+    __nv_bfloat16* q_out; __nv_bfloat16* k_cache; __nv_bfloat16* v_cache;
+    const int* token_seq; const int* token_pos; const int* block_table; int max_blocks;
+    const float* q_w; const float* k_w; float qk_eps;
+    const float* cos_sin; int rotary_dim; int max_pos;
+    int nq, nkv, d, page_tokens, ring_tokens, write_kv;
+};
+
+__device__ __forceinline__ float4 ld_cluster4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 ld_cluster2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// The factor of the deferred norm for token m: every lane of the warp gets it.
+__device__ __forceinline__ float row_scale(const FusedParams& p, int m, int lane) {
+    if (p.sq_in == nullptr) return 1.f;
+    float s = 0.f;
+    for (int i = lane; i < p.sq_tiles; i += 32) s += p.sq_in[(size_t)i * p.M + m];
+    return rsqrtf(warp_sum(s) * p.inv_hidden + p.eps);
+}
+
+template <int BX, int EPI>
+__global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                             const __grid_constant__ CUtensorMap map_x,
+                                                             const __grid_constant__ FusedParams p) {
+    constexpr uint32_t X_BYTES = BX * BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr uint32_t TMEM_COLS = BX < 32 ? 32 : BX;
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BX >> 3) << 17) | ((uint32_t)(BW >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const int stages = p.stages;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);
+    const uint32_t full0 = base + stages * STAGE_BYTES, empty0 = full0 + 8 * stages, tmem_full = empty0 + 8 * stages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 1);
+    // Once this block's MMAs are done its ring is free: the accumulator tile is parked there as float [token][row].
+    float* park = reinterpret_cast<float*>(smem);
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int splits = p.splits;
+    const int rank = (int)(blockIdx.x % (unsigned)splits);          // = the block's rank in its cluster (clusters lie along x)
+    const int w_tile = (int)(blockIdx.x / (unsigned)splits), x_tile = blockIdx.y;
+    const int w0 = w_tile * BW, x0 = x_tile * BX;
+    const int m_tile = min(BX, p.M - x0);
+    const int kb_begin = rank * p.kb_per_split;
+    const int nkb = min(p.kb_total, kb_begin + p.kb_per_split) - kb_begin;
+    int* status = p.status;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_w);
+        prefetch_tensor_map(&map_x);
+        for (int s = 0; s < stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // weights depend on no earlier kernel: they fill the ring before the wait for the producer of X
+            const int ahead = min(nkb, stages);
+            for (int i = 0; i < ahead; ++i) {
+                mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+                tma_load_2d(base + i * STAGE_BYTES, &map_w, full0 + 8 * i, (kb_begin + i) * BK, w0);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; ++i)
+                tma_load_2d(base + i * STAGE_BYTES + W_BYTES, &map_x, full0 + 8 * i, (kb_begin + i) * BK, x0);
+            int s = ahead == stages ? 0 : ahead;
+            uint32_t phase = ahead == stages ? 1u : 0u;
+            for (int i = ahead; i < nkb; ++i) {
+                if (!mbar_wait(empty0 + 8 * s, phase ^ 1u, status, 1)) break;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                const uint32_t dst = base + s * STAGE_BYTES;
+                tma_load_2d(dst, &map_w, full0 + 8 * s, (kb_begin + i) * BK, w0);
+                tma_load_2d(dst + W_BYTES, &map_x, full0 + 8 * s, (kb_begin + i) * BK, x0);
+                if (++s == stages) { s = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint64_t a_desc0 = operand_desc(base), b_desc0 = operand_desc(base + W_BYTES);
+            int s = 0;
+            uint32_t phase = 0;
+            for (int i = 0; i < nkb; ++i) {
+                if (!mbar_wait(full0 + 8 * s, phase, status, 2)) break;
+                tc_fence_after();
+                const uint64_t a_desc = a_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+                const uint64_t b_desc = b_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);
+                if (++s == stages) { s = 0; phase ^= 1u; }
+            }
+            umma_commit(tmem_full);
+        }
+    } else {
+        const int quarter = warp & 3;
+        pdl_wait();
+        const bool ready = mbar_wait(tmem_full, 0, status, 3);      // every K slice has been read: the ring is free
+        tc_fence_after();
+        const int row = quarter * 32 + lane;
+        if (ready) {
+#pragma unroll 1
+            for (int c = 0; c < m_tile; c += 16) {
+                uint32_t v[16];
+                tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) park[(c + j) * BW + row] = __uint_as_float(v[j]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                             // every block of the cluster has parked its tile
+
+    if (warp >= 2 && *(volatile int*)status == 0) {
+        const uint32_t park0 = smem_u32(park);
+        uint32_t peer[MAX_SPLITS];
+#pragma unroll
+        for (int r = 0; r < MAX_SPLITS; ++r) peer[r] = map_to_cta(park0, (uint32_t)min(r, splits - 1));
+        const int n_rows = p.N;
+        for (int t = rank * 4 + (warp - 2); t < m_tile; t += 4 * splits) {
+            const int m = x0 + t;
+            const float scale = row_scale(p, m, lane);
+            if (EPI == EPI_SWIGLU) {
+                // features 2 lane, 2 lane + 1 of the tile's 64: gate rows g * 32 + i, up rows 16 further
+                const int f = 2 * lane, gate_row = (f >> 4) * 32 + (f & 15);
+                const uint32_t off = (uint32_t)(t * BW + gate_row) * 4u;
+                float2 g = make_float2(0.f, 0.f), u = make_float2(0.f, 0.f);
+                float2 gs[MAX_SPLITS], us[MAX_SPLITS];
+#pragma unroll
+                for (int r = 0; r < MAX_SPLITS; ++r)
+                    if (r < splits) { gs[r] = ld_cluster2(peer[r] + off); us[r] = ld_cluster2(peer[r] + off + 64u); }
+#pragma unroll
+                for (int r = 0; r < MAX_SPLITS; ++r)
+                    if (r < splits) { g.x += gs[r].x; g.y += gs[r].y; u.x += us[r].x; u.y += us[r].y; }
+                g.x *= scale; g.y *= scale; u.x *= scale; u.y *= scale;
+                const int features = n_rows >> 1, feature = w_tile * (BW / 2) + f;
+                if (feature < features) {
+                    const float a0 = __fdividef(g.x, 1.f + __expf(-g.x)) * u.x, a1 = __fdividef(g.y, 1.f + __expf(-g.y)) * u.y;
+                    *reinterpret_cast<uint32_t*>((__nv_bfloat16*)p.out + (size_t)m * features + feature) = pack2(a0, a1);
+                }
+                continue;
+            }
+            // the other epilogues: four consecutive columns per lane
+            const uint32_t off = (uint32_t)(t * BW + 4 * lane) * 4u;
+            float4 parts[MAX_SPLITS];
+#pragma unroll
+            for (int r = 0; r < MAX_SPLITS; ++r)
+                if (r < splits) parts[r] = ld_cluster4(peer[r] + off);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < MAX_SPLITS; ++r)
+                if (r < splits) { v.x += parts[r].x; v.y += parts[r].y; v.z += parts[r].z; v.w += parts[r].w; }
+            const int n = w0 + 4 * lane;
+            if (EPI == EPI_STORE) {
+                v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+                const float e[4] = {v.x, v.y, v.z, v.w};
+                if (p.out_is_float) {
+                    float* dst = (float*)p.out + (size_t)m * n_rows + n;
+                    if (n + 3 < n_rows && (n_rows & 3) == 0) *reinterpret_cast<float4*>(dst) = v;
+                    else for (int i = 0; i < 4; ++i) if (n + i < n_rows) dst[i] = e[i];
+                } else {
+                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * n_rows + n;
+                    if (n + 3 < n_rows && (n_rows & 3) == 0) *reinterpret_cast<uint2*>(dst) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+                    else for (int i = 0; i < 4; ++i) if (n + i < n_rows) dst[i] = __float2bfloat16_rn(e[i]);
+                }
+            } else if (EPI == EPI_RESIDUAL) {                       // N is a multiple of 4 (checked by the host)
+                float sq = 0.f;
+                if (n < n_rows) {
+                    float* res = p.residual + (size_t)m * n_rows + n;
+                    const float4 r = *reinterpret_cast<const float4*>(res);
+                    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+                    *reinterpret_cast<float4*>(res) = v;
+                    sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                    if (p.norm_w) {
+                        const float4 g = *reinterpret_cast<const float4*>(p.norm_w + n);
+                        *reinterpret_cast<uint2*>(p.xw + (size_t)m * n_rows + n) = make_uint2(pack2(v.x * g.x, v.y * g.y), pack2(v.z * g.z, v.w * g.w));
+                    }
+                }
+                if (p.norm_w) {
+                    sq = warp_sum(sq);
+                    if (lane == 0) p.sq_out[(size_t)w_tile * p.M + m] = sq;
+                }
+            } else {                                                // EPI_QKV
+                const int d = p.d, lanes_per_head = d >> 2;
+                v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+                const int heads_total = n_rows / d;
+                const int head = n / d, c = n - head * d;
+                const bool valid = head < heads_total;
+                const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+                const float* w = is_q ? p.q_w : (is_k ? p.k_w : nullptr);
+                float sq = valid ? v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w : 0.f;
+                for (int o = 1; o < lanes_per_head; o <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (valid && w) {
+                    const float inv = rsqrtf(sq / (float)d + p.qk_eps);
+                    const float4 g = *reinterpret_cast<const float4*>(w + c);
+                    v.x *= inv * g.x; v.y *= inv * g.y; v.z *= inv * g.z; v.w *= inv * g.w;
+                }
+                const int half = p.rotary_dim >> 1;
+                const int pos = p.token_pos[m];
+                const bool rotates = valid && (is_q || is_k) && c < p.rotary_dim;
+                const bool low = c < half;
+                const int partner = rotates ? (low ? lane + (half >> 2) : lane - (half >> 2)) : lane;
+                const float4 other = make_float4(__shfl_sync(0xffffffffu, v.x, partner), __shfl_sync(0xffffffffu, v.y, partner),
+                                                 __shfl_sync(0xffffffffu, v.z, partner), __shfl_sync(0xffffffffu, v.w, partner));
+                if (rotates) {
+                    const float* cs = p.cos_sin + (size_t)(pos < p.max_pos ? pos : p.max_pos - 1) * p.rotary_dim + (low ? c : c - half);
+                    const float4 co = *reinterpret_cast<const float4*>(cs), si = *reinterpret_cast<const float4*>(cs + half);
+                    if (low) { v.x = v.x * co.x - other.x * si.x; v.y = v.y * co.y - other.y * si.y; v.z = v.z * co.z - other.z * si.z; v.w = v.w * co.w - other.w * si.w; }
+                    else { v.x = v.x * co.x + other.x * si.x; v.y = v.y * co.y + other.y * si.y; v.z = v.z * co.z + other.z * si.z; v.w = v.w * co.w + other.w * si.w; }
+                }
+                if (valid) {
+                    const uint2 packed = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+                    if (is_q) {
+                        *reinterpret_cast<uint2*>(p.q_out + ((size_t)m * p.nq + head) * d + c) = packed;
+                    } else if (p.write_kv) {
+                        const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
+                        const int* table = p.block_table + (size_t)p.token_seq[m] * p.max_blocks;
+                        __nv_bfloat16* cache = is_k ? p.k_cache : p.v_cache;
+                        *reinterpret_cast<uint2*>(cache + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, kvh, d) + c) = packed;
+                    }
+                }
+            }
+        }
+    }
+    cluster_sync_all();                                             // no block leaves while another still reads its tile
+    if (*(volatile int*)status != 0) {
+        const unsigned long long t0 = global_timer();
+        while (global_timer() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <int BX, int EPI>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, FusedParams p, int stages, cudaStream_t stream) {
+    constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
+    const int most = (224 * 1024) / (int)STAGE_BYTES;
+    if (stages <= 0) {
+        // up to 32 tokens: three stages (54 KB), four blocks per SM; more: two blocks with deeper rings (as in gemm_tc.cu)
+        stages = ((BX <= 32 ? 56 : 110) * 1024 - 2048) / (int)STAGE_BYTES;
+        if (stages > 8) stages = 8;
+    }
+    if (stages > most) stages = most;
+    // the ring also parks the accumulator tile, BX x 128 floats
+    while ((size_t)stages * STAGE_BYTES < (size_t)BX * BW * 4) ++stages;
+    if (stages < 2) stages = 2;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(gemm_fused_kernel<BX, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_fused: cannot raise shared memory: %s", cudaGetErrorString(err));
+        configured = true;
+    }
+    dim3 grid(((p.N + BW - 1) / BW) * p.splits, (p.M + BX - 1) / BX, 1);
+    launch_kernel_cluster(gemm_fused_kernel<BX, EPI>, grid, dim3(THREADS), smem, stream, (unsigned)p.splits, map_w, map_x, p);
+    QT_CHECK_LAUNCH("gemm_fused");
+    return QT_OK;
+}
+
+template <int EPI>
+int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, const FusedParams& p, int stages, cudaStream_t stream) {
+    switch (bx) {
+        case 16: return launch<16, EPI>(map_w, map_x, p, stages, stream);
+        case 32: return launch<32, EPI>(map_w, map_x, p, stages, stream);
+        case 64: return launch<64, EPI>(map_w, map_x, p, stages, stream);
+        case 128: return launch<128, EPI>(map_w, map_x, p, stages, stream);
+    }
+    QT_FAIL(QT_ERR_ARG, "gemm_fused: token tile %d is not one of 16, 32, 64, 128", bx);
+}
+
+}  // namespace
+
+// x [M, K] bfloat16, w [N, K] bfloat16.  `epilogue` picks what is done with the product (see the top of the file) and
+// which of the pointers are read; `splits` (1..8) is the size of the cluster that shares a weight tile and must leave
+// no rank without K blocks: (splits - 1) * ceil(ceil(K / 64) / splits) < ceil(K / 64).  `status` as in qt_gemm_tc.
+extern "C" int qt_gemm_fused(const void* x, const void* w, int M, int N, int K, int token_tile, int splits, int stages, int epilogue,
+                             const float* sq_in, int sq_tiles, int norm_width, float eps,
+                             void* out, int out_dtype,
+                             float* residual, const float* norm_w, void* xw, float* sq_out,
+                             void* q_out, void* k_cache, void* v_cache, const int* token_seq, const int* token_pos,
+                             const int* block_table, int max_blocks, const float* q_w, const float* k_w, float qk_eps,
+                             const float* cos_sin, int rotary_dim, int max_pos, int nq, int nkv, int d, int page_tokens,
+                             int ring_tokens, int write_kv, int* status, void* stream) {
+    QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_fused: bad sizes M=%d N=%d K=%d", M, N, K);
+    QT_REQUIRE(K % 8 == 0, "gemm_fused: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
+    QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_fused: operands must be 16-byte aligned");
+    QT_REQUIRE(status != nullptr, "gemm_fused: a status word is required");
+    const int kb_total = (K + BK - 1) / BK;
+    QT_REQUIRE(splits >= 1 && splits <= MAX_SPLITS && splits <= kb_total, "gemm_fused: splits=%d (1..%d) for %d K blocks", splits, MAX_SPLITS, kb_total);
+    const int per = (kb_total + splits - 1) / splits;
+    QT_REQUIRE((splits - 1) * per < kb_total, "gemm_fused: splits=%d would leave a rank without K blocks (%d blocks)", splits, kb_total);
+    QT_REQUIRE((M + token_tile - 1) / token_tile <= 65535, "gemm_fused: M=%d is too many tokens for tiles of %d", M, token_tile);
+    QT_REQUIRE(sq_in == nullptr || (sq_tiles > 0 && norm_width > 0 && eps > 0.f), "gemm_fused: the deferred norm needs its tile count, width and eps");
+    FusedParams p = {};
+    p.M = M; p.N = N; p.kb_total = kb_total; p.kb_per_split = per; p.splits = splits; p.status = status;
+    p.sq_in = sq_in; p.sq_tiles = sq_tiles; p.inv_hidden = norm_width > 0 ? 1.f / (float)norm_width : 0.f; p.eps = eps;
+    p.out = out; p.out_is_float = out_dtype == QT_F32;
+    p.residual = residual; p.norm_w = norm_w; p.xw = (__nv_bfloat16*)xw; p.sq_out = sq_out;
+    p.q_out = (__nv_bfloat16*)q_out; p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
+    p.token_seq = token_seq; p.token_pos = token_pos; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.q_w = q_w; p.k_w = k_w; p.qk_eps = qk_eps; p.cos_sin = cos_sin; p.rotary_dim = rotary_dim; p.max_pos = max_pos;
+    p.nq = nq; p.nkv = nkv; p.d = d; p.page_tokens = page_tokens; p.ring_tokens = ring_tokens; p.write_kv = write_kv;
+    switch (epilogue) {
+        case EPI_STORE:
+            QT_REQUIRE(out != nullptr && (out_dtype == QT_F32 || out_dtype == QT_BF16), "gemm_fused: the store epilogue needs a float or bfloat16 output");
+            QT_REQUIRE((uintptr_t)out % 16 == 0, "gemm_fused: the output must be 16-byte aligned");
+            break;
+        case EPI_RESIDUAL:
+            QT_REQUIRE(residual != nullptr && N % 4 == 0 && (uintptr_t)residual % 16 == 0, "gemm_fused: the residual epilogue needs an aligned stream whose width is a multiple of 4 (N=%d)", N);
+            QT_REQUIRE(norm_w == nullptr || (xw != nullptr && sq_out != nullptr && (uintptr_t)norm_w % 16 == 0 && (uintptr_t)xw % 8 == 0),
+                       "gemm_fused: preparing the next norm needs its weight, an output for the weighted stream and one for the sums of squares");
+            break;
+        case EPI_SWIGLU:
+            QT_REQUIRE(out != nullptr && out_dtype == QT_BF16 && N % 32 == 0 && (uintptr_t)out % 4 == 0, "gemm_fused: the gated epilogue writes bfloat16 and needs gate and up rows in groups of 16 (N=%d)", N);
+            break;
+        case EPI_QKV:
+            QT_REQUIRE(d >= 16 && BW % d == 0 && d % 4 == 0 && N % d == 0, "gemm_fused: head_dim=%d must divide %d for the fused rotation (N=%d)", d, BW, N);
+            QT_REQUIRE(nq > 0 && nkv > 0 && (N == nq * d || N == (nq + 2 * nkv) * d), "gemm_fused: N=%d is neither nq*d nor (nq+2nkv)*d", N);
+            QT_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 8 == 0, "gemm_fused: rotary_dim=%d must be a multiple of 8 within head_dim=%d", rotary_dim, d);
+            QT_REQUIRE(rotary_dim == 0 || (cos_sin && max_pos > 0 && (uintptr_t)cos_sin % 16 == 0), "gemm_fused: rotation needs an aligned cos/sin table");
+            QT_REQUIRE(q_out && token_pos && (uintptr_t)q_out % 8 == 0, "gemm_fused: q output or positions missing");
+            QT_REQUIRE((!q_w || (uintptr_t)q_w % 16 == 0) && (!k_w || (uintptr_t)k_w % 16 == 0), "gemm_fused: norm weights must be 16-byte aligned");
+            QT_REQUIRE(!write_kv || (N == (nq + 2 * nkv) * d && k_cache && v_cache && block_table && token_seq && page_tokens > 0 && ring_tokens >= 0 &&
+                                     (uintptr_t)k_cache % 8 == 0 && (uintptr_t)v_cache % 8 == 0),
+                       "gemm_fused: writing keys and values needs them in the projection, the caches and the page table");
+            break;
+        default:
+            QT_FAIL(QT_ERR_ARG, "gemm_fused: unknown epilogue %d", epilogue);
+    }
+    CUtensorMap map_w, map_x;
+    int rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
+    if (rc) return rc;
+    rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)token_tile);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (epilogue) {
+        case EPI_STORE: return dispatch_tile<EPI_STORE>(token_tile, map_w, map_x, p, stages, s);
+        case EPI_RESIDUAL: return dispatch_tile<EPI_RESIDUAL>(token_tile, map_w, map_x, p, stages, s);
+        case EPI_SWIGLU: return dispatch_tile<EPI_SWIGLU>(token_tile, map_w, map_x, p, stages, s);
+        default: return dispatch_tile<EPI_QKV>(token_tile, map_w, map_x, p, stages, s);
+    }
+}
+
+QT_DEFINE_LAST_ERROR(gemm_fused)

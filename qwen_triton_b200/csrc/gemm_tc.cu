@@ -379,7 +379,7 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
         cudaError_t err = cudaFuncSetAttribute(gemm_tc_pair_kernel<TO, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc_pair: cannot raise shared memory: %s", cudaGetErrorString(err));
         cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(2 * 148);
+        config.gridDim = dim3(2 * (unsigned)sm_count());
         config.blockDim = dim3(THREADS);
         config.dynamicSmemBytes = smem;
         cudaLaunchAttribute attribute[1];

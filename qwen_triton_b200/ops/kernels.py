@@ -55,6 +55,14 @@ _SIGNATURES = {
         "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
         "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
     },
+    "gemm_fused": {
+        "qt_gemm_fused": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_ptr, _c_int, _c_int, _c_float,
+                          _c_ptr, _c_int,
+                          _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                          _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float,
+                          _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_sample": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -422,7 +430,17 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
 
 _STATUS: dict[int, torch.Tensor] = {}
 _TC_TILES = (16, 32, 64, 128, 256)
-_SM_COUNT = 148
+_SM_COUNTS: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | str | None = None) -> int:
+    """Streaming multiprocessors of ``device`` (asked once per device)."""
+    device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _SM_COUNTS:
+        _SM_COUNTS[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _SM_COUNTS[index]
+
 TC_MAX_BLOCK_TOKENS = 128      # tokens per block that ``gemm`` gives the one-block kernel (256 measured slower at every split count)
 
 
@@ -516,7 +534,7 @@ def gemm_uses_pairs(a: torch.Tensor, w: torch.Tensor) -> bool:
         return False
     # more than 256 tokens; or more than one block's 128 with a weight whose tiles fill the machine unsplit (the fused
     # gate/up projection, the head), which single blocks would read once per token tile
-    return a.shape[0] > _TC_TILES[-1] or (a.shape[0] > TC_MAX_BLOCK_TOKENS and w.shape[0] >= 128 * _SM_COUNT)
+    return a.shape[0] > _TC_TILES[-1] or (a.shape[0] > TC_MAX_BLOCK_TOKENS and w.shape[0] >= 128 * sm_count(a.device))
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
@@ -531,3 +549,128 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: GemmOut) -> None:
         gemm_simt(a, w, out)
     else:
         raise KernelError("gemm: split-K output is only produced by the tensor-core kernel")
+
+
+# ----------------------------------------------------------------------------- products of a decode step, fused
+FUSED_MAX_ROWS = 128        # most tokens the fused product takes (one token tile per block)
+FUSED_MAX_SPLITS = 8        # blocks of a cluster that share a weight tile
+_EPI_STORE, _EPI_RESIDUAL, _EPI_SWIGLU, _EPI_QKV = 0, 1, 2, 3
+
+
+@dataclass
+class ScaledRows:
+    """Rows handed from an RMSNorm to the product behind it with the norm half done: ``tensor`` [M, K] holds
+    bf16(r * g) for the stream rows r and the norm's weight g, and the rows' factor rsqrt(mean(r^2) + eps) is
+    still to be applied, by the product's epilogue (the product is linear in its input).  ``sq`` [tiles, M]
+    holds the sums of squares of r over ``tiles`` column ranges; mean(r^2) = sum over tiles / ``width``."""
+
+    tensor: torch.Tensor
+    sq: torch.Tensor
+    width: int
+    eps: float
+
+    @property
+    def shape(self):
+        return self.tensor.shape
+
+
+def fused_supported(w: torch.Tensor) -> bool:
+    """The fused products take bfloat16 weights [N, K] with K a multiple of 8, 16-byte aligned."""
+    return w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()
+
+
+def fused_qkv_supported(head_dim: int, rotary_dim: int) -> bool:
+    """The fused q/k-norm + rotation + cache write needs whole heads inside a 128-row weight tile and rotation
+    pairs that four-element pieces can exchange."""
+    return head_dim >= 16 and 128 % head_dim == 0 and rotary_dim % 8 == 0 and rotary_dim <= head_dim
+
+
+def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual=None, norm_w=None, xw=None, sq_out=None,
+           q_out=None, k_cache=None, v_cache=None, token_seq=None, token_pos=None, block_table=None, q_w=None, k_w=None,
+           qk_eps=0.0, cos_sin=None, nq=0, nkv=0, d=0, page_tokens=0, ring_tokens=0, write_kv=False, stages: int = 0) -> None:
+    scaled = x if isinstance(x, ScaledRows) else None
+    a = scaled.tensor if scaled is not None else x
+    _need(a, "x", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    rows, k = a.shape
+    if k != w.shape[1]:
+        raise KernelError(f"gemm_fused: x {tuple(a.shape)} and w {tuple(w.shape)} do not fit")
+    if not 0 < rows <= FUSED_MAX_ROWS:
+        raise KernelError(f"gemm_fused: {rows} tokens (1..{FUSED_MAX_ROWS})")
+    if scaled is not None:
+        _need(scaled.sq, "sq", torch.float32)
+        if scaled.sq.dim() != 2 or scaled.sq.shape[1] != rows:
+            raise KernelError(f"gemm_fused: sums of squares {tuple(scaled.sq.shape)} for {rows} rows")
+    rotary_dim, max_pos = (0, 0) if cos_sin is None else (cos_sin.shape[1], cos_sin.shape[0])
+    _call("gemm_fused", "qt_gemm_fused", _ptr(a), _ptr(w), rows, w.shape[0], k, tc_token_tile(rows), int(splits), int(stages), epilogue,
+          _ptr(scaled.sq) if scaled is not None else None, scaled.sq.shape[0] if scaled is not None else 0,
+          scaled.width if scaled is not None else 0, float(scaled.eps) if scaled is not None else 0.0,
+          _ptr(out), _CODES.get(out.dtype, -1) if out is not None else 0,
+          _ptr(residual), _ptr(norm_w), _ptr(xw), _ptr(sq_out),
+          _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(token_seq), _ptr(token_pos), _ptr(block_table),
+          block_table.shape[1] if block_table is not None else 0, _ptr(q_w), _ptr(k_w), float(qk_eps),
+          _ptr(cos_sin), rotary_dim, max_pos, nq, nkv, d, page_tokens, ring_tokens, 1 if write_kv else 0,
+          _ptr(_status_word(a.device)), _stream())
+
+
+def gemm_fused_store(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0) -> None:
+    """out [M, N] (float or bfloat16) = x w^T, times the rows' deferred norm factor if ``x`` is ``ScaledRows``."""
+    _need(out, "out", shape=(x.shape[0], w.shape[0]))
+    _fused(x, w, splits, _EPI_STORE, out=out, stages=stages)
+
+
+def gemm_fused_residual(x, w: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor | None = None,
+                        eps: float = 0.0, xw: torch.Tensor | None = None, sq: torch.Tensor | None = None, splits: int = 1,
+                        stages: int = 0) -> "ScaledRows | None":
+    """residual [M, N] (float, in place) += x w^T.  With ``norm_weight`` [N] the RMSNorm that follows is prepared in
+    the same launch: ``xw`` [M, N] = bf16(residual * norm_weight) and ``sq`` [ceil(N / 128), M] = the rows' sums of
+    squares per 128 columns; returns them as ``ScaledRows`` for the product behind the norm."""
+    rows, n = x.shape[0], w.shape[0]
+    _need(residual, "residual", torch.float32, (rows, n))
+    if norm_weight is None:
+        _fused(x, w, splits, _EPI_RESIDUAL, residual=residual, stages=stages)
+        return None
+    _need(norm_weight, "norm_weight", torch.float32, (n,))
+    _need(xw, "xw", torch.bfloat16, (rows, n))
+    _need(sq, "sq", torch.float32, (-(-n // 128), rows))
+    _fused(x, w, splits, _EPI_RESIDUAL, residual=residual, norm_w=norm_weight, xw=xw, sq_out=sq, stages=stages)
+    return ScaledRows(xw, sq, n, float(eps))
+
+
+def gemm_fused_swiglu(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0) -> None:
+    """out [M, N / 2] (bfloat16) = silu(gate) * up for a weight whose rows alternate SWIGLU_GROUP of gate and of up."""
+    if w.shape[0] % (2 * SWIGLU_GROUP):
+        raise KernelError(f"gemm_fused_swiglu: {w.shape[0]} rows are not gate and up rows in groups of {SWIGLU_GROUP}")
+    _need(out, "out", torch.bfloat16, (x.shape[0], w.shape[0] // 2))
+    _fused(x, w, splits, _EPI_SWIGLU, out=out, stages=stages)
+
+
+def gemm_fused_qkv(x, w: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,
+                   token_seq: torch.Tensor, token_pos: torch.Tensor, block_table: torch.Tensor | None,
+                   q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
+                   num_heads: int, num_kv_heads: int, head_dim: int, page_tokens: int, ring_tokens: int,
+                   write_kv: bool = True, splits: int = 1, stages: int = 0) -> None:
+    """The fused projection [q; k; v] (or q alone) with per-head q/k RMSNorm, rotation and the cache write done in
+    its epilogue: what ``gemm`` followed by ``qk_norm_rope_write`` does, in one launch."""
+    rows = x.shape[0]
+    rotary_dim = 0 if cos_sin is None else cos_sin.shape[1]
+    if not fused_qkv_supported(head_dim, rotary_dim):
+        raise KernelError(f"gemm_fused_qkv: head_dim={head_dim} with rotary_dim={rotary_dim} is not taken")
+    _need(q_out, "q_out", torch.bfloat16, (rows, num_heads, head_dim))
+    _need(token_seq, "token_seq", torch.int32, (rows,))
+    _need(token_pos, "token_pos", torch.int32, (rows,))
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _need(weight, name, torch.float32, (head_dim,))
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+    if write_kv:
+        _need(block_table, "block_table", torch.int32)
+        for name, cache in (("k_cache", k_cache), ("v_cache", v_cache)):
+            _need(cache, name, torch.bfloat16)
+            if tuple(cache.shape[1:]) != (num_kv_heads, page_tokens, head_dim):
+                raise KernelError(f"{name}: shape {tuple(cache.shape)} is not [pages, {num_kv_heads}, {page_tokens}, {head_dim}]")
+    _fused(x, w, splits, _EPI_QKV, q_out=q_out, k_cache=k_cache if write_kv else None, v_cache=v_cache if write_kv else None,
+           token_seq=token_seq, token_pos=token_pos, block_table=block_table if write_kv else None, q_w=q_weight, k_w=k_weight,
+           qk_eps=eps, cos_sin=cos_sin, nq=num_heads, nkv=num_kv_heads, d=head_dim, page_tokens=page_tokens,
+           ring_tokens=ring_tokens, write_kv=write_kv, stages=stages)
