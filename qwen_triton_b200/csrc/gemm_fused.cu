@@ -21,7 +21,9 @@
 // in a fixed order: results do not depend on scheduling.
 //
 // Warp roles and bounded waits as in gemm_tc.cu.  Every thread of every block reaches both cluster barriers whatever
-// happens before them, so no block waits for one that has left.
+// happens before them, so no block waits for one that has left.  What a launch adds to the plain product is its
+// tail, after the last MMA: park, barrier, the peers' sums, the epilogue; to keep it short the epilogue's operands
+// are fetched under the main loop and the closing barrier is arrived at before the epilogue's own work.
 //
 // Counterparts in luozoupi/Qwen-Triton: kernels/matmul.py:52-97, kernels/rmsnorm.py:100-133, kernels/residual_add.py:50-60,
 // kernels/swiglu.py:84-92, kernels/rope.py:99-120, kernels/cache.py:71-98 (one launch each, or two).
@@ -68,6 +70,8 @@ __device__ __forceinline__ float2 ld_cluster2(uint32_t addr) {
     asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ void cluster_arrive_all() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_all() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -81,8 +85,53 @@ __device__ __forceinline__ float row_scale(const FusedParams& p, int m, int lane
     return rsqrtf(warp_sum(s) * p.inv_hidden + p.eps);
 }
 
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+// What the epilogue of one token needs from global memory besides the product itself.  It depends only on kernels
+// before this one, so a warp asks for its first token's share before it waits for the accumulator: the loads then run
+// under the main loop instead of after it.
+struct Operands {
+    float scale;            // the deferred norm factor of the token
+    float4 a, b, c;         // RESIDUAL: stream piece, norm weight piece.  QKV: cos piece, sin piece, q/k norm weight piece
+    int pos;                // QKV: the token's position
+    long long cache_at;     // QKV: element offset of this lane's piece in the key or value cache
+};
+
+template <int EPI>
+__device__ __forceinline__ Operands load_operands(const FusedParams& p, int m, int w0, int lane) {
+    Operands o;
+    o.scale = row_scale(p, m, lane);
+    o.a = o.b = o.c = make_float4(0.f, 0.f, 0.f, 0.f);
+    o.pos = 0;
+    o.cache_at = 0;
+    const int n = w0 + 4 * lane;
+    if (EPI == EPI_RESIDUAL) {
+        if (n < p.N) {
+            o.a = ld4(p.residual + (size_t)m * p.N + n);
+            if (p.norm_w) o.b = ld4(p.norm_w + n);
+        }
+    } else if (EPI == EPI_QKV) {
+        const int d = p.d, head = n / d, c = n - head * d, half = p.rotary_dim >> 1;
+        const bool valid = head < p.N / d, is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+        const float* w = is_q ? p.q_w : (is_k ? p.k_w : nullptr);
+        o.pos = p.token_pos[m];
+        if (valid && w) o.c = ld4(w + c);
+        if (valid && (is_q || is_k) && c < p.rotary_dim) {
+            const float* cs = p.cos_sin + (size_t)(o.pos < p.max_pos ? o.pos : p.max_pos - 1) * p.rotary_dim + (c < half ? c : c - half);
+            o.a = ld4(cs);
+            o.b = ld4(cs + half);
+        }
+        if (valid && !is_q && p.write_kv) {
+            const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
+            const int* table = p.block_table + (size_t)p.token_seq[m] * p.max_blocks;
+            o.cache_at = (long long)cache_offset(table, o.pos, p.ring_tokens, p.page_tokens, p.nkv, kvh, d) + c;
+        }
+    }
+    return o;
+}
+
 template <int BX, int EPI>
-__global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(THREADS, (BX <= 32 ? 4 : 2)) gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w,
                                                              const __grid_constant__ CUtensorMap map_x,
                                                              const __grid_constant__ FusedParams p) {
     constexpr uint32_t X_BYTES = BX * BK * 2;
@@ -127,6 +176,7 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    Operands first;                                                 // of the first token this warp finishes (warps 2..5)
 
     if (warp == 0) {
         if (lane == 0) {
@@ -171,6 +221,7 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
     } else {
         const int quarter = warp & 3;
         pdl_wait();
+        if (rank * 4 + (warp - 2) < m_tile) first = load_operands<EPI>(p, x0 + rank * 4 + (warp - 2), w0, lane);
         const bool ready = mbar_wait(tmem_full, 0, status, 3);      // every K slice has been read: the ring is free
         tc_fence_after();
         const int row = quarter * 32 + lane;
@@ -188,15 +239,21 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
     __syncthreads();
     cluster_sync_all();                                             // every block of the cluster has parked its tile
 
+    // Every block sums a share of the tile's tokens from all parked tiles, in the order of the ranks.  A warp arrives at
+    // the closing barrier as soon as it has read its last token's partial sums (its epilogue then runs under the
+    // barrier), and nobody leaves before every warp of the cluster has done so: no tile is freed while it is read.
+    bool arrived = false;
     if (warp >= 2 && *(volatile int*)status == 0) {
         const uint32_t park0 = smem_u32(park);
         uint32_t peer[MAX_SPLITS];
 #pragma unroll
         for (int r = 0; r < MAX_SPLITS; ++r) peer[r] = map_to_cta(park0, (uint32_t)min(r, splits - 1));
         const int n_rows = p.N;
-        for (int t = rank * 4 + (warp - 2); t < m_tile; t += 4 * splits) {
+        const int t0 = rank * 4 + (warp - 2), stride = 4 * splits;
+        for (int t = t0; t < m_tile; t += stride) {
             const int m = x0 + t;
-            const float scale = row_scale(p, m, lane);
+            const Operands ops = t == t0 ? first : load_operands<EPI>(p, m, w0, lane);
+            const bool last = t + stride >= m_tile;
             if (EPI == EPI_SWIGLU) {
                 // features 2 lane, 2 lane + 1 of the tile's 64: gate rows g * 32 + i, up rows 16 further
                 const int f = 2 * lane, gate_row = (f >> 4) * 32 + (f & 15);
@@ -209,7 +266,8 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
 #pragma unroll
                 for (int r = 0; r < MAX_SPLITS; ++r)
                     if (r < splits) { g.x += gs[r].x; g.y += gs[r].y; u.x += us[r].x; u.y += us[r].y; }
-                g.x *= scale; g.y *= scale; u.x *= scale; u.y *= scale;
+                if (last) { cluster_arrive_all(); arrived = true; }
+                g.x *= ops.scale; g.y *= ops.scale; u.x *= ops.scale; u.y *= ops.scale;
                 const int features = n_rows >> 1, feature = w_tile * (BW / 2) + f;
                 if (feature < features) {
                     const float a0 = __fdividef(g.x, 1.f + __expf(-g.x)) * u.x, a1 = __fdividef(g.y, 1.f + __expf(-g.y)) * u.y;
@@ -227,9 +285,10 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
 #pragma unroll
             for (int r = 0; r < MAX_SPLITS; ++r)
                 if (r < splits) { v.x += parts[r].x; v.y += parts[r].y; v.z += parts[r].z; v.w += parts[r].w; }
+            if (last) { cluster_arrive_all(); arrived = true; }
             const int n = w0 + 4 * lane;
             if (EPI == EPI_STORE) {
-                v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+                v.x *= ops.scale; v.y *= ops.scale; v.z *= ops.scale; v.w *= ops.scale;
                 const float e[4] = {v.x, v.y, v.z, v.w};
                 if (p.out_is_float) {
                     float* dst = (float*)p.out + (size_t)m * n_rows + n;
@@ -243,15 +302,12 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
             } else if (EPI == EPI_RESIDUAL) {                       // N is a multiple of 4 (checked by the host)
                 float sq = 0.f;
                 if (n < n_rows) {
-                    float* res = p.residual + (size_t)m * n_rows + n;
-                    const float4 r = *reinterpret_cast<const float4*>(res);
-                    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
-                    *reinterpret_cast<float4*>(res) = v;
+                    v.x += ops.a.x; v.y += ops.a.y; v.z += ops.a.z; v.w += ops.a.w;
+                    *reinterpret_cast<float4*>(p.residual + (size_t)m * n_rows + n) = v;
                     sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                    if (p.norm_w) {
-                        const float4 g = *reinterpret_cast<const float4*>(p.norm_w + n);
-                        *reinterpret_cast<uint2*>(p.xw + (size_t)m * n_rows + n) = make_uint2(pack2(v.x * g.x, v.y * g.y), pack2(v.z * g.z, v.w * g.w));
-                    }
+                    if (p.norm_w)
+                        *reinterpret_cast<uint2*>(p.xw + (size_t)m * n_rows + n) =
+                            make_uint2(pack2(v.x * ops.b.x, v.y * ops.b.y), pack2(v.z * ops.b.z, v.w * ops.b.w));
                 }
                 if (p.norm_w) {
                     sq = warp_sum(sq);
@@ -259,47 +315,38 @@ __global__ void __launch_bounds__(THREADS) gemm_fused_kernel(const __grid_consta
                 }
             } else {                                                // EPI_QKV
                 const int d = p.d, lanes_per_head = d >> 2;
-                v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-                const int heads_total = n_rows / d;
+                v.x *= ops.scale; v.y *= ops.scale; v.z *= ops.scale; v.w *= ops.scale;
                 const int head = n / d, c = n - head * d;
-                const bool valid = head < heads_total;
+                const bool valid = head < n_rows / d;
                 const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
-                const float* w = is_q ? p.q_w : (is_k ? p.k_w : nullptr);
+                const bool normed = is_q ? p.q_w != nullptr : (is_k && p.k_w != nullptr);
                 float sq = valid ? v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w : 0.f;
                 for (int o = 1; o < lanes_per_head; o <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                if (valid && w) {
+                if (valid && normed) {
                     const float inv = rsqrtf(sq / (float)d + p.qk_eps);
-                    const float4 g = *reinterpret_cast<const float4*>(w + c);
-                    v.x *= inv * g.x; v.y *= inv * g.y; v.z *= inv * g.z; v.w *= inv * g.w;
+                    v.x *= inv * ops.c.x; v.y *= inv * ops.c.y; v.z *= inv * ops.c.z; v.w *= inv * ops.c.w;
                 }
                 const int half = p.rotary_dim >> 1;
-                const int pos = p.token_pos[m];
                 const bool rotates = valid && (is_q || is_k) && c < p.rotary_dim;
                 const bool low = c < half;
                 const int partner = rotates ? (low ? lane + (half >> 2) : lane - (half >> 2)) : lane;
                 const float4 other = make_float4(__shfl_sync(0xffffffffu, v.x, partner), __shfl_sync(0xffffffffu, v.y, partner),
                                                  __shfl_sync(0xffffffffu, v.z, partner), __shfl_sync(0xffffffffu, v.w, partner));
                 if (rotates) {
-                    const float* cs = p.cos_sin + (size_t)(pos < p.max_pos ? pos : p.max_pos - 1) * p.rotary_dim + (low ? c : c - half);
-                    const float4 co = *reinterpret_cast<const float4*>(cs), si = *reinterpret_cast<const float4*>(cs + half);
+                    const float4 co = ops.a, si = ops.b;
                     if (low) { v.x = v.x * co.x - other.x * si.x; v.y = v.y * co.y - other.y * si.y; v.z = v.z * co.z - other.z * si.z; v.w = v.w * co.w - other.w * si.w; }
                     else { v.x = v.x * co.x + other.x * si.x; v.y = v.y * co.y + other.y * si.y; v.z = v.z * co.z + other.z * si.z; v.w = v.w * co.w + other.w * si.w; }
                 }
                 if (valid) {
                     const uint2 packed = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
-                    if (is_q) {
-                        *reinterpret_cast<uint2*>(p.q_out + ((size_t)m * p.nq + head) * d + c) = packed;
-                    } else if (p.write_kv) {
-                        const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
-                        const int* table = p.block_table + (size_t)p.token_seq[m] * p.max_blocks;
-                        __nv_bfloat16* cache = is_k ? p.k_cache : p.v_cache;
-                        *reinterpret_cast<uint2*>(cache + cache_offset(table, pos, p.ring_tokens, p.page_tokens, p.nkv, kvh, d) + c) = packed;
-                    }
+                    if (is_q) *reinterpret_cast<uint2*>(p.q_out + ((size_t)m * p.nq + head) * d + c) = packed;
+                    else if (p.write_kv) *reinterpret_cast<uint2*>((is_k ? p.k_cache : p.v_cache) + ops.cache_at) = packed;
                 }
             }
         }
     }
-    cluster_sync_all();                                             // no block leaves while another still reads its tile
+    if (!arrived) cluster_arrive_all();
+    cluster_wait_all();
     if (*(volatile int*)status != 0) {
         const unsigned long long t0 = global_timer();
         while (global_timer() - t0 < 2000000ull) __nanosleep(1000);

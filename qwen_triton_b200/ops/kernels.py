@@ -557,6 +557,15 @@ FUSED_MAX_SPLITS = 8        # blocks of a cluster that share a weight tile
 _EPI_STORE, _EPI_RESIDUAL, _EPI_SWIGLU, _EPI_QKV = 0, 1, 2, 3
 
 
+def fused_enabled(role: str) -> bool:
+    """``QT_B200_FUSED`` in the environment: "0" turns the fused products off, a comma-separated list keeps only the
+    named ones ("qkv", "gate", "attn_out", "mlp_out"); unset or "1": all of them."""
+    setting = os.environ.get("QT_B200_FUSED", "1")
+    if setting in ("1", ""):
+        return True
+    return setting != "0" and role in setting.split(",")
+
+
 @dataclass
 class ScaledRows:
     """Rows handed from an RMSNorm to the product behind it with the norm half done: ``tensor`` [M, K] holds

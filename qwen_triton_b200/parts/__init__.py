@@ -1,5 +1,5 @@
 from .base import (
-    KVRequest, ResidualStream, Runtime, StateRequest, Workspace, part_class,
+    DeferredProduct, KVRequest, ResidualStream, Runtime, StateRequest, Workspace, part_class,
     register_block, register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
     register_position,
 )
@@ -7,7 +7,7 @@ from . import attention, block, embedding, feed_forward, norm, position  # noqa:
 from .linear import Linear
 
 __all__ = [
-    "KVRequest", "Linear", "ResidualStream", "Runtime", "StateRequest", "Workspace", "part_class",
+    "DeferredProduct", "KVRequest", "Linear", "ResidualStream", "Runtime", "StateRequest", "Workspace", "part_class",
     "register_block", "register_embedding", "register_feed_forward", "register_head", "register_mixer",
     "register_norm", "register_position",
 ]

@@ -14,11 +14,10 @@ import torch
 from ..ops import kernels
 from ..ops.kernels import GemmOut
 from ..weights.tensors import TensorSpec
-from .base import KVRequest, Runtime, part_class, register_mixer, to_device
+from .base import DeferredProduct, KVRequest, Runtime, part_class, register_mixer, to_device
 from .linear import Linear
 
-_SM_COUNT = 148
-_DECODE_TARGET_BLOCKS = 3 * _SM_COUNT     # blocks of the generic one-token kernel that are resident at once (three per SM)
+_DECODE_BLOCKS_PER_SM = 3           # blocks of the generic one-token kernel that are resident at once
 _MAX_SPLIT_PAIRS = 640              # (sequence, split) pairs the scratch holds
 _MIN_KEYS_PER_SPLIT = 128
 
@@ -49,13 +48,15 @@ class Attention:
         self.cos_sin: torch.Tensor | None = None
         self.q_weight = self.k_weight = None
         proj_rows = (self.nq + (2 * self.nkv if self.own_kv else 0)) * self.d
-        self.qkv = Linear("attn.qkv", proj_rows, self.hidden, runtime)
-        self.o = Linear("attn.o", self.hidden, self.nq * self.d, runtime)
+        self.qkv = Linear("attn.qkv", proj_rows, self.hidden, runtime, role="qkv")
+        self.o = Linear("attn.o", self.hidden, self.nq * self.d, runtime, role="attn_out")
         ws = runtime.workspace
         ws.declare("attn.q", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
         ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
         ws.declare("attn.part_acc", _MAX_SPLIT_PAIRS * self.nq * self.d, torch.float32)
         ws.declare("attn.part_ml", _MAX_SPLIT_PAIRS * self.nq * 2, torch.float32)
+        # few tokens: the projection takes rows whose norm factor is still to be applied (``ScaledRows``)
+        self.takes_scaled_rows = self.qkv.fused_capable
 
     # ------------------------------------------------------------------ weights
     @classmethod
@@ -111,8 +112,9 @@ class Attention:
         if self.runtime.dtype == torch.bfloat16 and self.d % 16 == 0 and self.d <= 128 and cache.page_tokens == 64:
             pairs = ctx.n_seqs * self.nkv * math.ceil(group / 16)
             tiles = math.ceil(span / 32)
-            splits = max(1, min(_SM_COUNT // pairs, most))
-            warps = 3 if pairs * splits >= 3 * _SM_COUNT else 4
+            sms = self.runtime.sm_count
+            splits = max(1, min(sms // pairs, most))
+            warps = 3 if pairs * splits >= 3 * sms else 4
             while splits > 1 and splits * warps * 2 > tiles:
                 splits -= 1
             while warps > 1 and splits * warps * 2 > tiles:
@@ -122,24 +124,31 @@ class Attention:
         blocks = ctx.n_seqs * self.nkv * math.ceil(group / heads_per_block)
         most = max(1, min(span // _MIN_KEYS_PER_SPLIT, most))
         fills = []
+        resident = _DECODE_BLOCKS_PER_SM * self.runtime.sm_count
         for splits in range(1, most + 1):
             total = blocks * splits
-            fills.append(total / (math.ceil(total / _DECODE_TARGET_BLOCKS) * _DECODE_TARGET_BLOCKS))
+            fills.append(total / (math.ceil(total / resident) * resident))
         enough = max(fills) - 0.13
         return next(splits for splits, fill in enumerate(fills, start=1) if fill >= enough), 1
 
-    def forward(self, x: torch.Tensor, ctx, cache) -> GemmOut:
+    def forward(self, x, ctx, cache):
         tokens = x.shape[0]
         ws = self.runtime.workspace
-        qkv = self.qkv(x)
         q = ws.view("attn.q", tokens, self.nq, self.d)
         out = ws.view("attn.ctx", tokens, self.nq, self.d)
         table = ctx.block_table(cache.group)
         write = cache.writable and self.own_kv
-        kernels.qk_norm_rope_write(
-            qkv, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
-            table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
-            cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv)
+        rotary_dim = 0 if self.cos_sin is None else self.cos_sin.shape[1]
+        if self.qkv.fusable(tokens) and kernels.fused_qkv_supported(self.d, rotary_dim):
+            # few tokens: per-head norm, rotation and the cache write in the projection's epilogue
+            self.qkv.into_qkv(x, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
+                              table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv,
+                              self.d, cache.page_tokens, cache.ring_tokens, write_kv=write)
+        else:
+            kernels.qk_norm_rope_write(
+                self.qkv(x), q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
+                table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
+                cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv)
         if ctx.is_decode:
             n_splits, warps = self._splits(ctx, cache)
             kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,
@@ -149,4 +158,5 @@ class Attention:
         else:
             kernels.attention_prefill(q, cache.k, cache.v, out, table, ctx.seq_start, ctx.seq_past, ctx.max_q_len,
                                       self.nkv, cache.page_tokens, cache.ring_tokens, self.window, self.scale)
-        return self.o(out.view(tokens, self.nq * self.d))
+        out = out.view(tokens, self.nq * self.d)
+        return DeferredProduct(self.o, out) if self.o.fusable(tokens) else self.o(out)

@@ -7,8 +7,10 @@ Interfaces (what a new part must offer):
 
 * every part:  ``expected_tensors(params, prefix) -> {name: TensorSpec}`` (classmethod; no device),
   ``__init__(params, prefix, runtime)``, ``load(source)`` with ``source(name) -> CPU tensor``.
-* norm:        ``apply(stream, out=None, rows=None) -> Tensor``: folds the pending delta into the
-  residual stream and returns the normed rows in the activation dtype.
+* norm:        ``apply(stream, rows=None) -> Tensor``: folds the pending delta into the
+  residual stream and returns the normed rows in the activation dtype.  A norm that sets
+  ``offers_scaled_rows`` also takes ``lazy=True`` and may then hand on ``ScaledRows`` (the rows times its
+  weight, the rows' factor left to the consumer's product) to a consumer that sets ``takes_scaled_rows``.
 * position:    ``__init__(params, runtime)``, ``table(max_positions) -> float32 [P, rotary_dim]`` (cos | sin) or ``None``
   for no encoding, and ``key() -> tuple`` that names the table's content (equal keys share one table).
 * mixer:       ``cache_request() -> KVRequest | StateRequest | None`` and
@@ -29,7 +31,7 @@ from typing import Any, Callable, Mapping
 import torch
 
 from ..config.spec import PartSpec
-from ..ops.kernels import GemmOut
+from ..ops.kernels import GemmOut, ScaledRows
 
 _REGISTRIES: dict[str, dict[str, type]] = {"norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
                                            "embedding": {}, "head": {}}
@@ -144,23 +146,64 @@ class Runtime:
     workspace: Workspace
     page_tokens: int = 64
     options: dict[str, Any] = field(default_factory=dict)
+    sm_count: int = 0                       # streaming multiprocessors of the device (0: ask it)
+
+    def __post_init__(self) -> None:
+        if self.sm_count <= 0:
+            from ..ops import kernels
+            self.sm_count = kernels.sm_count(self.device)
+
+
+class DeferredProduct:
+    """A product x W^T that has not been launched yet.  Whoever takes it launches it together with what it does
+    next (a norm adds it to the stream and prepares itself in the product's epilogue); whoever only wants its
+    value calls ``run()``."""
+
+    def __init__(self, linear, x) -> None:
+        self.linear, self.x = linear, x
+
+    def run(self) -> GemmOut:
+        return self.linear(self.x)
+
+    def value(self) -> torch.Tensor:
+        """The finished matrix in float (for tests and host-side use)."""
+        return self.run().value()
 
 
 class ResidualStream:
     """The float residual stream [T, H] with at most one pending addition.
 
     A part's output is not added at once: it is kept as ``pending`` and folded in by the next norm
-    kernel, which reads the stream anyway.
+    kernel, which reads the stream anyway.  The addition may also be a product that is still to be
+    launched (``DeferredProduct``): ``take_deferred`` hands it to a norm that fuses with it, reading
+    ``pending`` launches it and gives its result.
     """
 
     def __init__(self, residual: torch.Tensor) -> None:
         self.residual = residual
-        self.pending: GemmOut | None = None
+        self._pending: GemmOut | DeferredProduct | None = None
 
-    def add(self, delta: GemmOut) -> None:
-        if self.pending is not None:
+    @property
+    def pending(self) -> GemmOut | None:
+        if isinstance(self._pending, DeferredProduct):
+            self._pending = self._pending.run()
+        return self._pending
+
+    @pending.setter
+    def pending(self, value: GemmOut | None) -> None:
+        self._pending = value
+
+    def add(self, delta: "GemmOut | DeferredProduct") -> None:
+        if self._pending is not None:
             raise RuntimeError("the residual stream already has a pending addition; apply a norm first")
-        self.pending = delta
+        self._pending = delta
+
+    def take_deferred(self) -> DeferredProduct | None:
+        """The pending addition if it is a product not launched yet (it is then no longer pending), else None."""
+        if isinstance(self._pending, DeferredProduct):
+            deferred, self._pending = self._pending, None
+            return deferred
+        return None
 
 
 TensorSource = Callable[[str], torch.Tensor]

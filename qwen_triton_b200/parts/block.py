@@ -50,8 +50,15 @@ class PreNormBlock:
         for part in self.parts():
             part.load(source)
 
+    @staticmethod
+    def _normed(norm, stream: ResidualStream, consumer):
+        """The consumer's input: ``ScaledRows`` where the norm offers them and the consumer takes them."""
+        if getattr(norm, "offers_scaled_rows", False) and getattr(consumer, "takes_scaled_rows", False):
+            return norm.apply(stream, lazy=True)
+        return norm.apply(stream)
+
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
-        x = self.mixer_norm.apply(stream)
+        x = self._normed(self.mixer_norm, stream, self.mixer)
         stream.add(self.mixer.forward(x, ctx, cache))
-        x = self.feed_forward_norm.apply(stream)
+        x = self._normed(self.feed_forward_norm, stream, self.feed_forward)
         stream.add(self.feed_forward.forward(x, ctx))

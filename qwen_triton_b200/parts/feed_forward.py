@@ -12,7 +12,7 @@ import torch
 from ..ops import kernels
 from ..ops.kernels import GemmOut
 from ..weights.tensors import TensorSpec
-from .base import Runtime, register_feed_forward
+from .base import DeferredProduct, Runtime, register_feed_forward
 from .linear import Linear
 
 
@@ -31,9 +31,12 @@ class GatedMLP:
         self.names = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
         fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0
         self.group = kernels.SWIGLU_GROUP if fused else 0
-        self.gate_up = Linear("mlp.gate_up", 2 * self.inter, self.hidden, runtime)
-        self.down = Linear("mlp.down", self.hidden, self.inter, runtime)
+        self.gate_up = Linear("mlp.gate_up", 2 * self.inter, self.hidden, runtime, role="gate")
+        self.down = Linear("mlp.down", self.hidden, self.inter, runtime, role="mlp_out")
         runtime.workspace.declare("mlp.act", runtime.max_step_tokens * self.inter, runtime.dtype)
+        # few tokens: the gate in the epilogue of the gate/up product, which then also applies the factor of the norm
+        # in front of it (``ScaledRows``)
+        self.takes_scaled_rows = bool(self.group) and self.gate_up.fused_capable
 
     @classmethod
     def expected_tensors(cls, params, prefix: str) -> dict[str, TensorSpec]:
@@ -49,9 +52,12 @@ class GatedMLP:
         self.gate_up.set_weight(kernels.interleave_gate_up(gate.to(self.runtime.dtype), up.to(self.runtime.dtype), self.group))
         self.down.set_weight(source(f"{p}.{n['down']}.weight"))
 
-    def forward(self, x: torch.Tensor, ctx) -> GemmOut:
+    def forward(self, x, ctx):
         tokens = x.shape[0]
         act = self.runtime.workspace.view("mlp.act", tokens, self.inter)
+        if self.takes_scaled_rows and self.gate_up.fusable(tokens):
+            self.gate_up.into_swiglu(x, act)
+            return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
         if self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
             kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True)
         else:

@@ -19,6 +19,7 @@ class _Workspace:
 class _Runtime:
     def __init__(self, dtype, max_step_tokens):
         self.dtype, self.max_step_tokens, self.workspace, self.device = dtype, max_step_tokens, _Workspace(), "cpu"
+        self.sm_count = 148
 
 
 SHAPES = [(6144, 4096), (4096, 12288), (24576, 4096), (151936, 4096), (1024, 2048), (130, 72), (5003, 1000), (200, 8), (51200, 5120)]
@@ -26,11 +27,13 @@ SHAPES = [(6144, 4096), (4096, 12288), (24576, 4096), (151936, 4096), (1024, 204
 
 @pytest.mark.parametrize("out_features, in_features", SHAPES)
 def test_every_split_count_leaves_no_split_without_k_blocks(out_features, in_features):
-    for rows, target in linear._SPLIT_PLANS:
-        splits = linear.pick_splits(out_features, in_features, target, rows)
+    for rows, per_sm in linear._SPLIT_PLANS:
+        splits = linear.pick_splits(out_features, in_features, per_sm * 148, rows)
         assert 1 <= splits <= 16 and kernels.tc_normalise_splits(in_features, splits) == splits
+        fused = linear.pick_splits(out_features, in_features, per_sm * 148, rows, kernels.FUSED_MAX_SPLITS, 1.0)
+        assert 1 <= fused <= kernels.FUSED_MAX_SPLITS and kernels.tc_normalise_splits(in_features, fused) == fused
     for rows in (257, 300, 512, 1000, 2048, 4096):
-        splits = linear.pick_pair_splits(out_features, in_features, rows)
+        splits = linear.pick_pair_splits(out_features, in_features, rows, 74)
         assert 1 <= splits <= 4 and kernels.tc_normalise_splits(in_features, splits) == splits
         blocks = -(-in_features // 64)
         assert (splits - 1) * -(-blocks // splits) < blocks
@@ -38,8 +41,8 @@ def test_every_split_count_leaves_no_split_without_k_blocks(out_features, in_fea
 
 def test_a_product_with_many_tiles_is_not_split():
     assert linear.pick_splits(151936, 4096, 296, 64) == 1
-    assert linear.pick_pair_splits(24576, 4096, 2048) == 1
-    assert linear.pick_pair_splits(4096, 4096, 512) > 1          # 32 tiles on 74 pairs
+    assert linear.pick_pair_splits(24576, 4096, 2048, 74) == 1
+    assert linear.pick_pair_splits(4096, 4096, 512, 74) > 1          # 32 tiles on 74 pairs
 
 
 @pytest.mark.parametrize("max_rows", [40, 256, 300, 4096])
