@@ -54,15 +54,10 @@ extern "C" int qt_argmax(const float* logits, int* out, int rows, int vocab, voi
 
 // One block per row: token = first index whose cumulative weight exceeds uniform * total, with
 // weight_i = exp((logit_i - max) / T).  Thread t owns the contiguous ids [t * span, (t + 1) * span).
-__global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
-                                                            const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
-    pdl_launch_dependents();
-    pdl_wait();
+__device__ __forceinline__ int sample_row(const float* __restrict__ row, float inv_t, float uniform, int vocab) {
     __shared__ float scratch[32];
     __shared__ float sums[SMP_THREADS];
     __shared__ int chosen;
-    const float* row = logits + (size_t)blockIdx.x * vocab;
-    const float inv_t = 1.f / temperature[blockIdx.x];
     const int span = (vocab + blockDim.x - 1) / blockDim.x;
     const int begin = min(vocab, (int)threadIdx.x * span), end = min(vocab, begin + span);
 
@@ -83,7 +78,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __rest
         // serial scan over the 1024 partial sums: a fixed order, so the choice is reproducible
         float total = 0.f;
         for (int t = 0; t < SMP_THREADS; ++t) total += sums[t];
-        const float target = uniform[blockIdx.x] * total;
+        const float target = uniform * total;
         float running = 0.f;
         int owner = -1;
         for (int t = 0; t < SMP_THREADS; ++t) {
@@ -101,7 +96,15 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __rest
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) out[blockIdx.x] = chosen;
+    return chosen;
+}
+
+__global__ void __launch_bounds__(SMP_THREADS) sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                                                            const float* __restrict__ uniform, int* __restrict__ out, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int token = sample_row(logits + (size_t)blockIdx.x * vocab, 1.f / temperature[blockIdx.x], uniform[blockIdx.x], vocab);
+    if (threadIdx.x == 0) out[blockIdx.x] = token;
 }
 
 extern "C" int qt_sample(const float* logits, const float* temperature, const float* uniform, int* out, int rows,
@@ -109,6 +112,39 @@ extern "C" int qt_sample(const float* logits, const float* temperature, const fl
     QT_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
     if (rows == 0) return QT_OK;
     launch_kernel(sample_kernel, dim3(rows), dim3(SMP_THREADS), 0, (cudaStream_t)stream, logits, temperature, uniform, out, vocab);
+    QT_CHECK_LAUNCH("sample");
+    return QT_OK;
+}
+
+// The same choice with the uniform number made here: the counter-based stream of (seed, request, step), three rounds of
+// the splitmix64 finaliser, its top 24 bits as a float in [0, 1).  keys[2 r] is row r's request number, keys[2 r + 1]
+// its step number; nothing but these few integers has to come from the host for a step's sampling.
+__device__ __forceinline__ unsigned long long mix64(unsigned long long v) {
+    v += 0x9E3779B97F4A7C15ull;
+    v = (v ^ (v >> 30)) * 0xBF58476D1CE4E5B9ull;
+    v = (v ^ (v >> 27)) * 0x94D049BB133111EBull;
+    return v ^ (v >> 31);
+}
+
+__global__ void __launch_bounds__(SMP_THREADS) sample_keyed_kernel(const float* __restrict__ logits, float inv_t, unsigned long long seed,
+                                                                  const int* __restrict__ keys, int* __restrict__ out, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
+    unsigned long long state = mix64(seed);
+    state = mix64(state ^ (unsigned long long)(long long)keys[2 * blockIdx.x]);
+    state = mix64(state ^ (unsigned long long)(long long)keys[2 * blockIdx.x + 1]);
+    const float uniform = (float)(state >> 40) * (1.f / 16777216.f);
+    const int token = sample_row(logits + (size_t)blockIdx.x * vocab, inv_t, uniform, vocab);
+    if (threadIdx.x == 0) out[blockIdx.x] = token;
+}
+
+extern "C" int qt_sample_keyed(const float* logits, float temperature, long long seed, const int* keys, int* out, int rows, int vocab,
+                               void* stream) {
+    QT_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
+    QT_REQUIRE(temperature > 0.f, "sample: temperature must be positive (greedy choice is qt_argmax)");
+    if (rows == 0) return QT_OK;
+    launch_kernel(sample_keyed_kernel, dim3(rows), dim3(SMP_THREADS), 0, (cudaStream_t)stream, logits, 1.f / temperature,
+                  (unsigned long long)seed, keys, out, vocab);
     QT_CHECK_LAUNCH("sample");
     return QT_OK;
 }

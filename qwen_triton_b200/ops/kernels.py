@@ -66,6 +66,7 @@ _SIGNATURES = {
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_sample": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_sample_keyed": [_c_ptr, _c_float, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_feed_tokens": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
     },
 }
@@ -426,6 +427,18 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     _need(out, "out", torch.int32, (rows,))
     _call("sampling", "qt_sample", _ptr(logits), _ptr(temperature), _ptr(uniform), _ptr(out), rows, logits.shape[1],
           _stream())
+
+
+def sample_keyed(logits: torch.Tensor, temperature: float, seed: int, keys: torch.Tensor, out: torch.Tensor) -> None:
+    """Temperature sampling with the uniform number of each row made on the device from (seed, request, step);
+    ``keys`` int32 [rows, 2] holds each row's request and step number."""
+    rows = logits.shape[0]
+    _need(logits, "logits", torch.float32)
+    _need(keys, "keys", torch.int32, (rows, 2))
+    _need(out, "out", torch.int32, (rows,))
+    seed &= (1 << 64) - 1
+    _call("sampling", "qt_sample_keyed", _ptr(logits), float(temperature), seed - (1 << 64) if seed >> 63 else seed, _ptr(keys),
+          _ptr(out), rows, logits.shape[1], _stream())
 
 
 _STATUS: dict[int, torch.Tensor] = {}

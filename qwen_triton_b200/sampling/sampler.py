@@ -34,7 +34,8 @@ def _mix64(value: int) -> int:
 
 
 def uniform_for(seed: int, request: int, step: int) -> float:
-    """Uniform number in [0, 1) for the ``step``-th new token of request ``request``."""
+    """Uniform number in [0, 1) for the ``step``-th new token of request ``request``.  The sampling kernel computes
+    the same number on the device; this host statement of it is what tests compare with."""
     state = _mix64(seed & _MASK64)
     state = _mix64(state ^ (request & _MASK64))
     state = _mix64(state ^ (step & _MASK64))
@@ -61,7 +62,26 @@ class Sampler:
     def __init__(self, device: torch.device) -> None:
         self.device = torch.device(device)
         self._hosts: list[torch.Tensor] = []     # pinned buffers the ids are copied into, used in turn
+        self._keys: list[tuple] = []             # pinned (request, step) buffers, their events and the device copy
         self._turn = 0
+
+    def _keys_on_device(self, requests: list[int], steps: list[int]) -> torch.Tensor:
+        """(request, step) per row as int32 [rows, 2] on the device, through a pinned buffer and an asynchronous
+        copy: the host does not wait for the device and the device not for the host."""
+        rows = len(requests)
+        if not self._keys or self._keys[0][0].shape[0] < rows:
+            size = max(rows, 64)
+            self._keys = [(torch.empty((size, 2), dtype=torch.int32, pin_memory=True), torch.cuda.Event(),
+                           torch.empty((size, 2), dtype=torch.int32, device=self.device)) for _ in range(self._RING)]
+        host, event, device = self._keys[self._turn % self._RING]
+        if self._turn >= self._RING:
+            event.synchronize()                  # the copy that last used this buffer has happened
+        pairs = host.numpy()
+        pairs[:rows, 0] = requests
+        pairs[:rows, 1] = steps
+        device[:rows].copy_(host[:rows], non_blocking=True)
+        event.record()
+        return device[:rows]
 
     def launch(self, logits: torch.Tensor, params: SamplingParams, requests: list[int], steps: list[int]) -> PendingTokens:
         """Start the choice and the copy of the ids to pinned host memory; the caller may do other work before
@@ -73,10 +93,7 @@ class Sampler:
         if params.temperature == 0.0:
             kernels.argmax(logits, out)
         else:
-            uniform = torch.tensor([uniform_for(params.seed, r, s) for r, s in zip(requests, steps)],
-                                   dtype=torch.float32).to(self.device)
-            temperature = torch.full((rows,), params.temperature, dtype=torch.float32, device=self.device)
-            kernels.sample(logits, temperature, uniform, out)
+            kernels.sample_keyed(logits, params.temperature, params.seed, self._keys_on_device(requests, steps), out)
         if not self._hosts or self._hosts[0].numel() < rows:
             self._hosts = [torch.empty(max(rows, 64), dtype=torch.int32, pin_memory=True) for _ in range(self._RING)]
         host = self._hosts[self._turn % self._RING]

@@ -341,6 +341,26 @@ def test_sample_follows_the_inverse_cdf():
     assert (freq - torch.softmax(small[0].cpu() / 1.3, 0)).abs().max() < 0.03
 
 
+def test_sample_draws_its_uniform_number_from_seed_request_and_step():
+    """The kernel that makes the uniform number itself picks what the plain statement of that number picks, and a
+    probe row whose logits make each token's share of the unit interval wide shows the number itself."""
+    import plain_qwen3 as plain
+    rows, vocab, seed = 40, 1009, (1 << 63) + 12345
+    logits = rand(rows, vocab, seed=105, scale=2.0)
+    keys = torch.stack([torch.arange(rows) * 7 - 3, torch.arange(rows) % 5], dim=1).int()      # a negative request number too
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    kernels.sample_keyed(logits, 0.7, seed, keys.to(DEV), out)
+    host = logits.cpu()
+    for r in range(rows):
+        uniform = plain.uniform_for(seed, int(keys[r, 0]), int(keys[r, 1]))
+        assert plain.choice_is_consistent(host[r], 0.7, uniform, int(out[r])), r
+    # 4,096 tokens of equal weight: the chosen token is floor(uniform * 4096)
+    flat = torch.zeros(rows, 4096, device=DEV)
+    kernels.sample_keyed(flat, 1.0, seed, keys.to(DEV), out)
+    expected = [int(plain.uniform_for(seed, int(keys[r, 0]), int(keys[r, 1])) * 4096) for r in range(rows)]
+    assert all(abs(int(out[r]) - expected[r]) <= 1 for r in range(rows)), (out.tolist(), expected)
+
+
 def test_kernels_refuse_what_they_cannot_run():
     with pytest.raises(kernels.KernelError, match="CUDA tensor"):
         kernels.argmax(torch.zeros(1, 4), torch.zeros(1, dtype=torch.int32))
