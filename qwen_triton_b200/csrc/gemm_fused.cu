@@ -8,17 +8,7 @@
 // sums, in the fixed order of the ranks, a share of the tile's tokens from all of them).  No partial sums pass
 // through global memory, and the kernel that used to add them up is not needed: its work is this kernel's epilogue.
 //
-//   STORE     out[m, n] = s_m * y                       float or bfloat16 (the output head)
-//   RESIDUAL  r = residual[m, n] + y; residual[m, n] = r;  and, for the norm that follows, xw[m, n] = bf16(r * g[n])
-//             and sq_out[tile, m] = sum over the tile's 128 columns of r^2
-//   SWIGLU    act[m, f] = silu(s_m * gate) * (s_m * up), the weight's rows alternating 16 of gate and 16 of up
-//   QKV       per head (head_dim divides 128): s_m * y, RMSNorm over the head with q or k weight, rotate-half by the
-//             cos/sin table at the token's position, then q to q_out and k, v into the paged cache
-//
-// s_m is the factor of an RMSNorm whose weight g was applied by the producer of X (X = bf16(r * g)):
-// s_m = rsqrt(sum over tiles of sq_in[tile, m] / hidden + eps); the product is linear in X, so scaling the result
-// equals normalising the input.  sq_in == nullptr means s_m = 1.  Partial sums of squares are kept per tile and added
-// in a fixed order: results do not depend on scheduling.
+// The epilogues (STORE, RESIDUAL, SWIGLU, QKV) and the deferred norm factor s_m are stated in fused_epilogue.cuh.
 //
 // Warp roles and bounded waits as in gemm_tc.cu.  Every thread of every block reaches both cluster barriers whatever
 // happens before them, so no block waits for one that has left.  What a launch adds to the plain product is its
@@ -27,10 +17,12 @@
 //
 // Counterparts in luozoupi/Qwen-Triton: kernels/matmul.py:52-97, kernels/rmsnorm.py:100-133, kernels/residual_add.py:50-60,
 // kernels/swiglu.py:84-92, kernels/rope.py:99-120, kernels/cache.py:71-98 (one launch each, or two).
+#include "fused_epilogue.cuh"
 #include "tc_common.cuh"
 
 using namespace qt;
 using namespace qt_tc;
+using namespace qt_epi;
 
 namespace {
 
@@ -41,23 +33,10 @@ constexpr int THREADS = 192;
 constexpr uint32_t W_BYTES = BW * BK * 2;
 constexpr int MAX_SPLITS = 8;              // portable cluster size
 
-enum Epilogue { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
-
 struct FusedParams {
-    int M, N, kb_total, kb_per_split, stages, splits;
+    int kb_total, kb_per_split, stages, splits;
     int* status;
-    // the deferred factor of the norm in front of this product
-    const float* sq_in; int sq_tiles; float inv_hidden; float eps;
-    // STORE / SWIGLU
-    void* out; int out_is_float;
-    // RESIDUAL
-    float* residual; const float* norm_w; __nv_bfloat16* xw; float* sq_out;
-    // QKV
-    __nv_bfloat16* q_out; __nv_bfloat16* k_cache; __nv_bfloat16* v_cache;
-    const int* token_seq; const int* token_pos; const int* block_table; int max_blocks;
-    const float* q_w; const float* k_w; float qk_eps;
-    const float* cos_sin; int rotary_dim; int max_pos;
-    int nq, nkv, d, page_tokens, ring_tokens, write_kv;
+    EpilogueParams e;
 };
 
 __device__ __forceinline__ float4 ld_cluster4(uint32_t addr) {
@@ -72,64 +51,6 @@ __device__ __forceinline__ float2 ld_cluster2(uint32_t addr) {
 }
 __device__ __forceinline__ void cluster_arrive_all() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait_all() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ uint32_t pack2(float a, float b) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
-// The factor of the deferred norm for token m: every lane of the warp gets it.
-__device__ __forceinline__ float row_scale(const FusedParams& p, int m, int lane) {
-    if (p.sq_in == nullptr) return 1.f;
-    float s = 0.f;
-    for (int i = lane; i < p.sq_tiles; i += 32) s += p.sq_in[(size_t)i * p.M + m];
-    return rsqrtf(warp_sum(s) * p.inv_hidden + p.eps);
-}
-
-__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
-
-// What the epilogue of one token needs from global memory besides the product itself.  It depends only on kernels
-// before this one, so a warp asks for its first token's share before it waits for the accumulator: the loads then run
-// under the main loop instead of after it.
-struct Operands {
-    float scale;            // the deferred norm factor of the token
-    float4 a, b, c;         // RESIDUAL: stream piece, norm weight piece.  QKV: cos piece, sin piece, q/k norm weight piece
-    int pos;                // QKV: the token's position
-    long long cache_at;     // QKV: element offset of this lane's piece in the key or value cache
-};
-
-template <int EPI>
-__device__ __forceinline__ Operands load_operands(const FusedParams& p, int m, int w0, int lane) {
-    Operands o;
-    o.scale = row_scale(p, m, lane);
-    o.a = o.b = o.c = make_float4(0.f, 0.f, 0.f, 0.f);
-    o.pos = 0;
-    o.cache_at = 0;
-    const int n = w0 + 4 * lane;
-    if (EPI == EPI_RESIDUAL) {
-        if (n < p.N) {
-            o.a = ld4(p.residual + (size_t)m * p.N + n);
-            if (p.norm_w) o.b = ld4(p.norm_w + n);
-        }
-    } else if (EPI == EPI_QKV) {
-        const int d = p.d, head = n / d, c = n - head * d, half = p.rotary_dim >> 1;
-        const bool valid = head < p.N / d, is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
-        const float* w = is_q ? p.q_w : (is_k ? p.k_w : nullptr);
-        o.pos = p.token_pos[m];
-        if (valid && w) o.c = ld4(w + c);
-        if (valid && (is_q || is_k) && c < p.rotary_dim) {
-            const float* cs = p.cos_sin + (size_t)(o.pos < p.max_pos ? o.pos : p.max_pos - 1) * p.rotary_dim + (c < half ? c : c - half);
-            o.a = ld4(cs);
-            o.b = ld4(cs + half);
-        }
-        if (valid && !is_q && p.write_kv) {
-            const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
-            const int* table = p.block_table + (size_t)p.token_seq[m] * p.max_blocks;
-            o.cache_at = (long long)cache_offset(table, o.pos, p.ring_tokens, p.page_tokens, p.nkv, kvh, d) + c;
-        }
-    }
-    return o;
-}
-
 template <int BX, int EPI>
 __global__ void __launch_bounds__(THREADS, (BX <= 32 ? 4 : 2)) gemm_fused_kernel(const __grid_constant__ CUtensorMap map_w,
                                                              const __grid_constant__ CUtensorMap map_x,
@@ -156,7 +77,8 @@ __global__ void __launch_bounds__(THREADS, (BX <= 32 ? 4 : 2)) gemm_fused_kernel
     const int rank = (int)(blockIdx.x % (unsigned)splits);          // = the block's rank in its cluster (clusters lie along x)
     const int w_tile = (int)(blockIdx.x / (unsigned)splits), x_tile = blockIdx.y;
     const int w0 = w_tile * BW, x0 = x_tile * BX;
-    const int m_tile = min(BX, p.M - x0);
+    const EpilogueParams& ep = p.e;
+    const int m_tile = min(BX, ep.M - x0);
     const int kb_begin = rank * p.kb_per_split;
     const int nkb = min(p.kb_total, kb_begin + p.kb_per_split) - kb_begin;
     int* status = p.status;
@@ -221,7 +143,7 @@ __global__ void __launch_bounds__(THREADS, (BX <= 32 ? 4 : 2)) gemm_fused_kernel
     } else {
         const int quarter = warp & 3;
         pdl_wait();
-        if (rank * 4 + (warp - 2) < m_tile) first = load_operands<EPI>(p, x0 + rank * 4 + (warp - 2), w0, lane);
+        if (rank * 4 + (warp - 2) < m_tile) first = load_operands<EPI>(ep, x0 + rank * 4 + (warp - 2), w0, lane);
         const bool ready = mbar_wait(tmem_full, 0, status, 3);      // every K slice has been read: the ring is free
         tc_fence_after();
         const int row = quarter * 32 + lane;
@@ -248,16 +170,13 @@ __global__ void __launch_bounds__(THREADS, (BX <= 32 ? 4 : 2)) gemm_fused_kernel
         uint32_t peer[MAX_SPLITS];
 #pragma unroll
         for (int r = 0; r < MAX_SPLITS; ++r) peer[r] = map_to_cta(park0, (uint32_t)min(r, splits - 1));
-        const int n_rows = p.N;
         const int t0 = rank * 4 + (warp - 2), stride = 4 * splits;
         for (int t = t0; t < m_tile; t += stride) {
             const int m = x0 + t;
-            const Operands ops = t == t0 ? first : load_operands<EPI>(p, m, w0, lane);
+            const Operands ops = t == t0 ? first : load_operands<EPI>(ep, m, w0, lane);
             const bool last = t + stride >= m_tile;
             if (EPI == EPI_SWIGLU) {
-                // features 2 lane, 2 lane + 1 of the tile's 64: gate rows g * 32 + i, up rows 16 further
-                const int f = 2 * lane, gate_row = (f >> 4) * 32 + (f & 15);
-                const uint32_t off = (uint32_t)(t * BW + gate_row) * 4u;
+                const uint32_t off = (uint32_t)(t * BW + swiglu_gate_row(lane)) * 4u;
                 float2 g = make_float2(0.f, 0.f), u = make_float2(0.f, 0.f);
                 float2 gs[MAX_SPLITS], us[MAX_SPLITS];
 #pragma unroll
@@ -267,81 +186,19 @@ __global__ void __launch_bounds__(THREADS, (BX <= 32 ? 4 : 2)) gemm_fused_kernel
                 for (int r = 0; r < MAX_SPLITS; ++r)
                     if (r < splits) { g.x += gs[r].x; g.y += gs[r].y; u.x += us[r].x; u.y += us[r].y; }
                 if (last) { cluster_arrive_all(); arrived = true; }
-                g.x *= ops.scale; g.y *= ops.scale; u.x *= ops.scale; u.y *= ops.scale;
-                const int features = n_rows >> 1, feature = w_tile * (BW / 2) + f;
-                if (feature < features) {
-                    const float a0 = __fdividef(g.x, 1.f + __expf(-g.x)) * u.x, a1 = __fdividef(g.y, 1.f + __expf(-g.y)) * u.y;
-                    *reinterpret_cast<uint32_t*>((__nv_bfloat16*)p.out + (size_t)m * features + feature) = pack2(a0, a1);
-                }
-                continue;
-            }
-            // the other epilogues: four consecutive columns per lane
-            const uint32_t off = (uint32_t)(t * BW + 4 * lane) * 4u;
-            float4 parts[MAX_SPLITS];
+                finish_swiglu(ep, ops, g, u, m, w_tile, lane);
+            } else {
+                const uint32_t off = (uint32_t)(t * BW + 4 * lane) * 4u;
+                float4 parts[MAX_SPLITS];
 #pragma unroll
-            for (int r = 0; r < MAX_SPLITS; ++r)
-                if (r < splits) parts[r] = ld_cluster4(peer[r] + off);
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; r < MAX_SPLITS; ++r)
+                    if (r < splits) parts[r] = ld_cluster4(peer[r] + off);
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int r = 0; r < MAX_SPLITS; ++r)
-                if (r < splits) { v.x += parts[r].x; v.y += parts[r].y; v.z += parts[r].z; v.w += parts[r].w; }
-            if (last) { cluster_arrive_all(); arrived = true; }
-            const int n = w0 + 4 * lane;
-            if (EPI == EPI_STORE) {
-                v.x *= ops.scale; v.y *= ops.scale; v.z *= ops.scale; v.w *= ops.scale;
-                const float e[4] = {v.x, v.y, v.z, v.w};
-                if (p.out_is_float) {
-                    float* dst = (float*)p.out + (size_t)m * n_rows + n;
-                    if (n + 3 < n_rows && (n_rows & 3) == 0) *reinterpret_cast<float4*>(dst) = v;
-                    else for (int i = 0; i < 4; ++i) if (n + i < n_rows) dst[i] = e[i];
-                } else {
-                    __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * n_rows + n;
-                    if (n + 3 < n_rows && (n_rows & 3) == 0) *reinterpret_cast<uint2*>(dst) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
-                    else for (int i = 0; i < 4; ++i) if (n + i < n_rows) dst[i] = __float2bfloat16_rn(e[i]);
-                }
-            } else if (EPI == EPI_RESIDUAL) {                       // N is a multiple of 4 (checked by the host)
-                float sq = 0.f;
-                if (n < n_rows) {
-                    v.x += ops.a.x; v.y += ops.a.y; v.z += ops.a.z; v.w += ops.a.w;
-                    *reinterpret_cast<float4*>(p.residual + (size_t)m * n_rows + n) = v;
-                    sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                    if (p.norm_w)
-                        *reinterpret_cast<uint2*>(p.xw + (size_t)m * n_rows + n) =
-                            make_uint2(pack2(v.x * ops.b.x, v.y * ops.b.y), pack2(v.z * ops.b.z, v.w * ops.b.w));
-                }
-                if (p.norm_w) {
-                    sq = warp_sum(sq);
-                    if (lane == 0) p.sq_out[(size_t)w_tile * p.M + m] = sq;
-                }
-            } else {                                                // EPI_QKV
-                const int d = p.d, lanes_per_head = d >> 2;
-                v.x *= ops.scale; v.y *= ops.scale; v.z *= ops.scale; v.w *= ops.scale;
-                const int head = n / d, c = n - head * d;
-                const bool valid = head < n_rows / d;
-                const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
-                const bool normed = is_q ? p.q_w != nullptr : (is_k && p.k_w != nullptr);
-                float sq = valid ? v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w : 0.f;
-                for (int o = 1; o < lanes_per_head; o <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                if (valid && normed) {
-                    const float inv = rsqrtf(sq / (float)d + p.qk_eps);
-                    v.x *= inv * ops.c.x; v.y *= inv * ops.c.y; v.z *= inv * ops.c.z; v.w *= inv * ops.c.w;
-                }
-                const int half = p.rotary_dim >> 1;
-                const bool rotates = valid && (is_q || is_k) && c < p.rotary_dim;
-                const bool low = c < half;
-                const int partner = rotates ? (low ? lane + (half >> 2) : lane - (half >> 2)) : lane;
-                const float4 other = make_float4(__shfl_sync(0xffffffffu, v.x, partner), __shfl_sync(0xffffffffu, v.y, partner),
-                                                 __shfl_sync(0xffffffffu, v.z, partner), __shfl_sync(0xffffffffu, v.w, partner));
-                if (rotates) {
-                    const float4 co = ops.a, si = ops.b;
-                    if (low) { v.x = v.x * co.x - other.x * si.x; v.y = v.y * co.y - other.y * si.y; v.z = v.z * co.z - other.z * si.z; v.w = v.w * co.w - other.w * si.w; }
-                    else { v.x = v.x * co.x + other.x * si.x; v.y = v.y * co.y + other.y * si.y; v.z = v.z * co.z + other.z * si.z; v.w = v.w * co.w + other.w * si.w; }
-                }
-                if (valid) {
-                    const uint2 packed = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
-                    if (is_q) *reinterpret_cast<uint2*>(p.q_out + ((size_t)m * p.nq + head) * d + c) = packed;
-                    else if (p.write_kv) *reinterpret_cast<uint2*>((is_k ? p.k_cache : p.v_cache) + ops.cache_at) = packed;
-                }
+                for (int r = 0; r < MAX_SPLITS; ++r)
+                    if (r < splits) { v.x += parts[r].x; v.y += parts[r].y; v.z += parts[r].z; v.w += parts[r].w; }
+                if (last) { cluster_arrive_all(); arrived = true; }
+                finish<EPI>(ep, ops, v, m, w_tile, lane);
             }
         }
     }
@@ -378,7 +235,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, FusedParams p, in
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_fused: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
-    dim3 grid(((p.N + BW - 1) / BW) * p.splits, (p.M + BX - 1) / BX, 1);
+    dim3 grid(((p.e.N + BW - 1) / BW) * p.splits, (p.e.M + BX - 1) / BX, 1);
     launch_kernel_cluster(gemm_fused_kernel<BX, EPI>, grid, dim3(THREADS), smem, stream, (unsigned)p.splits, map_w, map_x, p);
     QT_CHECK_LAUNCH("gemm_fused");
     return QT_OK;
@@ -417,45 +274,21 @@ extern "C" int qt_gemm_fused(const void* x, const void* w, int M, int N, int K, 
     const int per = (kb_total + splits - 1) / splits;
     QT_REQUIRE((splits - 1) * per < kb_total, "gemm_fused: splits=%d would leave a rank without K blocks (%d blocks)", splits, kb_total);
     QT_REQUIRE((M + token_tile - 1) / token_tile <= 65535, "gemm_fused: M=%d is too many tokens for tiles of %d", M, token_tile);
-    QT_REQUIRE(sq_in == nullptr || (sq_tiles > 0 && norm_width > 0 && eps > 0.f), "gemm_fused: the deferred norm needs its tile count, width and eps");
     FusedParams p = {};
-    p.M = M; p.N = N; p.kb_total = kb_total; p.kb_per_split = per; p.splits = splits; p.status = status;
-    p.sq_in = sq_in; p.sq_tiles = sq_tiles; p.inv_hidden = norm_width > 0 ? 1.f / (float)norm_width : 0.f; p.eps = eps;
-    p.out = out; p.out_is_float = out_dtype == QT_F32;
-    p.residual = residual; p.norm_w = norm_w; p.xw = (__nv_bfloat16*)xw; p.sq_out = sq_out;
-    p.q_out = (__nv_bfloat16*)q_out; p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
-    p.token_seq = token_seq; p.token_pos = token_pos; p.block_table = block_table; p.max_blocks = max_blocks;
-    p.q_w = q_w; p.k_w = k_w; p.qk_eps = qk_eps; p.cos_sin = cos_sin; p.rotary_dim = rotary_dim; p.max_pos = max_pos;
-    p.nq = nq; p.nkv = nkv; p.d = d; p.page_tokens = page_tokens; p.ring_tokens = ring_tokens; p.write_kv = write_kv;
-    switch (epilogue) {
-        case EPI_STORE:
-            QT_REQUIRE(out != nullptr && (out_dtype == QT_F32 || out_dtype == QT_BF16), "gemm_fused: the store epilogue needs a float or bfloat16 output");
-            QT_REQUIRE((uintptr_t)out % 16 == 0, "gemm_fused: the output must be 16-byte aligned");
-            break;
-        case EPI_RESIDUAL:
-            QT_REQUIRE(residual != nullptr && N % 4 == 0 && (uintptr_t)residual % 16 == 0, "gemm_fused: the residual epilogue needs an aligned stream whose width is a multiple of 4 (N=%d)", N);
-            QT_REQUIRE(norm_w == nullptr || (xw != nullptr && sq_out != nullptr && (uintptr_t)norm_w % 16 == 0 && (uintptr_t)xw % 8 == 0),
-                       "gemm_fused: preparing the next norm needs its weight, an output for the weighted stream and one for the sums of squares");
-            break;
-        case EPI_SWIGLU:
-            QT_REQUIRE(out != nullptr && out_dtype == QT_BF16 && N % 32 == 0 && (uintptr_t)out % 4 == 0, "gemm_fused: the gated epilogue writes bfloat16 and needs gate and up rows in groups of 16 (N=%d)", N);
-            break;
-        case EPI_QKV:
-            QT_REQUIRE(d >= 16 && BW % d == 0 && d % 4 == 0 && N % d == 0, "gemm_fused: head_dim=%d must divide %d for the fused rotation (N=%d)", d, BW, N);
-            QT_REQUIRE(nq > 0 && nkv > 0 && (N == nq * d || N == (nq + 2 * nkv) * d), "gemm_fused: N=%d is neither nq*d nor (nq+2nkv)*d", N);
-            QT_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 8 == 0, "gemm_fused: rotary_dim=%d must be a multiple of 8 within head_dim=%d", rotary_dim, d);
-            QT_REQUIRE(rotary_dim == 0 || (cos_sin && max_pos > 0 && (uintptr_t)cos_sin % 16 == 0), "gemm_fused: rotation needs an aligned cos/sin table");
-            QT_REQUIRE(q_out && token_pos && (uintptr_t)q_out % 8 == 0, "gemm_fused: q output or positions missing");
-            QT_REQUIRE((!q_w || (uintptr_t)q_w % 16 == 0) && (!k_w || (uintptr_t)k_w % 16 == 0), "gemm_fused: norm weights must be 16-byte aligned");
-            QT_REQUIRE(!write_kv || (N == (nq + 2 * nkv) * d && k_cache && v_cache && block_table && token_seq && page_tokens > 0 && ring_tokens >= 0 &&
-                                     (uintptr_t)k_cache % 8 == 0 && (uintptr_t)v_cache % 8 == 0),
-                       "gemm_fused: writing keys and values needs them in the projection, the caches and the page table");
-            break;
-        default:
-            QT_FAIL(QT_ERR_ARG, "gemm_fused: unknown epilogue %d", epilogue);
-    }
+    p.kb_total = kb_total; p.kb_per_split = per; p.splits = splits; p.status = status;
+    EpilogueParams& e = p.e;
+    e.M = M; e.N = N;
+    e.sq_in = sq_in; e.sq_tiles = sq_tiles; e.inv_hidden = norm_width > 0 ? 1.f / (float)norm_width : 0.f; e.eps = eps;
+    e.out = out; e.out_is_float = out_dtype == QT_F32;
+    e.residual = residual; e.norm_w = norm_w; e.xw = (__nv_bfloat16*)xw; e.sq_out = sq_out;
+    e.q_out = (__nv_bfloat16*)q_out; e.k_cache = (__nv_bfloat16*)k_cache; e.v_cache = (__nv_bfloat16*)v_cache;
+    e.token_seq = token_seq; e.token_pos = token_pos; e.block_table = block_table; e.max_blocks = max_blocks;
+    e.q_w = q_w; e.k_w = k_w; e.qk_eps = qk_eps; e.cos_sin = cos_sin; e.rotary_dim = rotary_dim; e.max_pos = max_pos;
+    e.nq = nq; e.nkv = nkv; e.d = d; e.page_tokens = page_tokens; e.ring_tokens = ring_tokens; e.write_kv = write_kv;
+    int rc = check_epilogue("gemm_fused", epilogue, e, out_dtype);
+    if (rc) return rc;
     CUtensorMap map_w, map_x;
-    int rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
+    rc = tensor_map(&map_w, w, (uint64_t)N, (uint64_t)K, BW);
     if (rc) return rc;
     rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)token_tile);
     if (rc) return rc;
