@@ -141,6 +141,25 @@ template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// Gate activations of a gated feed-forward, out = act(gate) * up (a parameter of the part, a code here).
+#define QT_ACT_SILU 0
+#define QT_ACT_GELU_TANH 1
+#define QT_ACT_GELU 2
+#define QT_ACT_RELU 3
+#define QT_ACT_COUNT 4
+
+// act(g) in float.  FAST takes the hardware approximations of exp and division for SiLU (2 ulp of float, for results
+// that are rounded to bfloat16 anyway); the other activations are the library's forms.
+template <bool FAST>
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    switch (act) {
+        case QT_ACT_GELU_TANH: return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        case QT_ACT_GELU: return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));
+        case QT_ACT_RELU: return fmaxf(g, 0.f);
+        default: return FAST ? __fdividef(g, 1.f + __expf(-g)) : g / (1.f + expf(-g));
+    }
+}
+
 // Sum of `n_splits` partial results stored `split_stride` elements apart (split-K GEMM output).
 template <typename T>
 __device__ __forceinline__ float load_sum(const T* base, size_t index, int n_splits, size_t split_stride) {

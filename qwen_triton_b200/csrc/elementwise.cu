@@ -538,15 +538,15 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     return QT_OK;
 }
 
-// ----------------------------------------------------------------------------- SiLU-gated product
-// out[t, i] = silu(g) * u; float inside.  Plain layout (group 0): g = gate_up[t, i], u = gate_up[t, inter + i].
+// ----------------------------------------------------------------------------- gated product
+// out[t, i] = act(g) * u (act: SiLU or another of QT_ACT_*); float inside.  Plain layout (group 0): g = gate_up[t, i], u = gate_up[t, inter + i].
 // Interleaved layout (group G, the fused weight's rows alternate G of gate and G of up, which is what lets a GEMM
 // epilogue see both in one warp): g = gate_up[t, (i / G) * 2G + i % G], u = the element G further on.
 __device__ __forceinline__ size_t gate_column(int i, int group) { return group ? (size_t)(i / group) * 2 * group + i % group : (size_t)i; }
 
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                              long long total, int inter, int group) {
+                              long long total, int inter, int group, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int up_offset = group ? group : inter;
@@ -557,7 +557,7 @@ __global__ void swiglu_kernel(const TI* __restrict__ gate_up, int n_splits, size
         const size_t base = (size_t)t * 2 * inter + gate_column(i, group);
         const float g = load_sum(gate_up, base, n_splits, split_stride);
         const float u = load_sum(gate_up, base + up_offset, n_splits, split_stride);
-        out[idx] = from_float<TO>(g / (1.f + expf(-g)) * u);
+        out[idx] = from_float<TO>(gate_activation<false>(g, act) * u);
     }
 }
 
@@ -581,16 +581,16 @@ __device__ __forceinline__ void add4(float4& x, const float4& y) { x.x += y.x; x
 // silu(g) * u.  For a float result the exponential and the division are the library's; for a bfloat16 result
 // (8 bits of mantissa) the hardware approximations (2 ulp of float) are used: with the exact forms the kernel was
 // bound by instruction issue, not by memory.
-template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
-template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
-template <typename TO> __device__ __forceinline__ float4 silu_mul4(const float4& g, const float4& u) {
-    return make_float4(silu_mul<TO>(g.x, u.x), silu_mul<TO>(g.y, u.y), silu_mul<TO>(g.z, u.z), silu_mul<TO>(g.w, u.w));
+template <typename TO> __device__ __forceinline__ float silu_mul(float g, float u, int act) { return gate_activation<false>(g, act) * u; }
+template <> __device__ __forceinline__ float silu_mul<__nv_bfloat16>(float g, float u, int act) { return gate_activation<true>(g, act) * u; }
+template <typename TO> __device__ __forceinline__ float4 silu_mul4(const float4& g, const float4& u, int act) {
+    return make_float4(silu_mul<TO>(g.x, u.x, act), silu_mul<TO>(g.y, u.y, act), silu_mul<TO>(g.z, u.z, act), silu_mul<TO>(g.w, u.w, act));
 }
 
 // PT chunks per thread, all loads issued before the first store.
 template <typename TI, typename TO, int PT>
 __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, size_t split_stride, TO* __restrict__ out,
-                                  int inter, int group) {
+                                  int inter, int group, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int chunks = inter >> 3;
@@ -618,13 +618,14 @@ __global__ void swiglu_vec_kernel(const TI* __restrict__ gate_up, int n_splits, 
 #pragma unroll
         for (int i = 0; i < PT; ++i) {
             const int c = c0 + i * blockDim.x;
-            if (c < chunks) store8(orow + 8 * c, Float8{silu_mul4<TO>(g[i].a, u[i].a), silu_mul4<TO>(g[i].b, u[i].b)});
+            if (c < chunks) store8(orow + 8 * c, Float8{silu_mul4<TO>(g[i].a, u[i].a, act), silu_mul4<TO>(g[i].b, u[i].b, act)});
         }
     }
 }
 
 extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long long split_stride, void* out, int out_dtype,
-                         int n_tokens, int inter, int group, void* stream) {
+                         int n_tokens, int inter, int group, int act, void* stream) {
+    QT_REQUIRE(act >= 0 && act < QT_ACT_COUNT, "swiglu: unknown activation code %d", act);
     QT_REQUIRE(n_tokens >= 0 && inter > 0 && n_splits >= 1, "swiglu: bad sizes T=%d I=%d", n_tokens, inter);
     QT_REQUIRE(group >= 0 && (group == 0 || inter % group == 0), "swiglu: rows interleaved in groups of %d do not divide I=%d", group, inter);
     if (n_tokens == 0) return QT_OK;
@@ -641,11 +642,11 @@ extern "C" int qt_swiglu(const void* gate_up, int in_dtype, int n_splits, long l
 #define QT_LAUNCH_SWIGLU(TI, TO)                                                                                              \
     do {                                                                                                                      \
         if (vec && per_thread == 2) launch_kernel(swiglu_vec_kernel<TI, TO, 2>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s, \
-                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group);                   \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group, act);              \
         else if (vec) launch_kernel(swiglu_vec_kernel<TI, TO, 1>, dim3((unsigned)n_tokens, per_row), dim3(threads), 0, s,     \
-                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group);                   \
+                               (const TI*)gate_up, n_splits, (size_t)split_stride, (TO*)out, inter, group, act);              \
         else launch_kernel(swiglu_kernel<TI, TO>, dim3((unsigned)blocks), dim3(threads), 0, s, (const TI*)gate_up, n_splits,  \
-                           (size_t)split_stride, (TO*)out, total, inter, group);                                              \
+                           (size_t)split_stride, (TO*)out, total, inter, group, act);                                         \
     } while (0)
     if (in_dtype == QT_F32 && out_dtype == QT_F32) QT_LAUNCH_SWIGLU(float, float);
     else if (in_dtype == QT_F32 && out_dtype == QT_BF16) QT_LAUNCH_SWIGLU(float, __nv_bfloat16);

@@ -4,7 +4,7 @@
 //   STORE     out[m, n] = s_m * y                       float or bfloat16 (the output head)
 //   RESIDUAL  r = residual[m, n] + y; residual[m, n] = r;  and, for the norm that follows, xw[m, n] = bf16(r * g[n])
 //             and sq_out[tile, m] = sum over the tile's 128 columns of r^2
-//   SWIGLU    act[m, f] = silu(s_m * gate) * (s_m * up), the weight's rows alternating 16 of gate and 16 of up
+//   SWIGLU    act[m, f] = a(s_m * gate) * (s_m * up), a = SiLU or another QT_ACT_*, the weight's rows alternating 16 of gate and 16 of up
 //   QKV       per head (head_dim divides 128): s_m * y, RMSNorm over the head with q or k weight, rotate-half by the
 //             cos/sin table at the token's position, then q to q_out and k, v into the paged cache
 //
@@ -32,7 +32,7 @@ struct EpilogueParams {
     // the deferred factor of the norm in front of this product
     const float* sq_in; int sq_tiles; float inv_hidden; float eps;
     // STORE / SWIGLU
-    void* out; int out_is_float;
+    void* out; int out_is_float; int act;      // act: the gate's activation, QT_ACT_*
     // RESIDUAL
     float* residual; const float* norm_w; __nv_bfloat16* xw; float* sq_out;
     // QKV
@@ -105,7 +105,7 @@ __device__ __forceinline__ void finish_swiglu(const EpilogueParams& p, const Ope
     g.x *= ops.scale; g.y *= ops.scale; u.x *= ops.scale; u.y *= ops.scale;
     const int features = p.N >> 1, feature = w_tile * (TILE / 2) + 2 * lane;
     if (feature < features) {
-        const float a0 = __fdividef(g.x, 1.f + __expf(-g.x)) * u.x, a1 = __fdividef(g.y, 1.f + __expf(-g.y)) * u.y;
+        const float a0 = gate_activation<true>(g.x, p.act) * u.x, a1 = gate_activation<true>(g.y, p.act) * u.y;
         *reinterpret_cast<uint32_t*>((__nv_bfloat16*)p.out + (size_t)m * features + feature) = pack2(a0, a1);
     }
 }
@@ -187,6 +187,7 @@ inline int check_epilogue(const char* who, int epilogue, const EpilogueParams& p
             break;
         case EPI_SWIGLU:
             QT_REQUIRE(p.out != nullptr && out_dtype == QT_BF16 && p.N % 32 == 0 && (uintptr_t)p.out % 4 == 0, "%s: the gated epilogue writes bfloat16 and needs gate and up rows in groups of 16 (N=%d)", who, p.N);
+            QT_REQUIRE(p.act >= 0 && p.act < QT_ACT_COUNT, "%s: unknown activation code %d", who, p.act);
             break;
         case EPI_QKV:
             QT_REQUIRE(p.d >= 16 && TILE % p.d == 0 && p.d % 4 == 0 && p.N % p.d == 0, "%s: head_dim=%d must divide %d for the fused rotation (N=%d)", who, p.d, TILE, p.N);

@@ -259,7 +259,7 @@ int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, co
 // no rank without K blocks: (splits - 1) * ceil(ceil(K / 64) / splits) < ceil(K / 64).  `status` as in qt_gemm_tc.
 extern "C" int qt_gemm_fused(const void* x, const void* w, int M, int N, int K, int token_tile, int splits, int stages, int epilogue,
                              const float* sq_in, int sq_tiles, int norm_width, float eps,
-                             void* out, int out_dtype,
+                             void* out, int out_dtype, int act,
                              float* residual, const float* norm_w, void* xw, float* sq_out,
                              void* q_out, void* k_cache, void* v_cache, const int* token_seq, const int* token_pos,
                              const int* block_table, int max_blocks, const float* q_w, const float* k_w, float qk_eps,
@@ -279,7 +279,7 @@ extern "C" int qt_gemm_fused(const void* x, const void* w, int M, int N, int K, 
     EpilogueParams& e = p.e;
     e.M = M; e.N = N;
     e.sq_in = sq_in; e.sq_tiles = sq_tiles; e.inv_hidden = norm_width > 0 ? 1.f / (float)norm_width : 0.f; e.eps = eps;
-    e.out = out; e.out_is_float = out_dtype == QT_F32;
+    e.out = out; e.out_is_float = out_dtype == QT_F32; e.act = act;
     e.residual = residual; e.norm_w = norm_w; e.xw = (__nv_bfloat16*)xw; e.sq_out = sq_out;
     e.q_out = (__nv_bfloat16*)q_out; e.k_cache = (__nv_bfloat16*)k_cache; e.v_cache = (__nv_bfloat16*)v_cache;
     e.token_seq = token_seq; e.token_pos = token_pos; e.block_table = block_table; e.max_blocks = max_blocks;

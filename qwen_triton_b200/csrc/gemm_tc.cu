@@ -198,7 +198,7 @@ template <typename TO, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
                                                                   int M, int N, int kb_total, int kb_per_split, int splits,
-                                                                  size_t split_stride, int* status) {
+                                                                  size_t split_stride, int act, int* status) {
     // instruction descriptor: float accumulator, bfloat16 A and B, both K-major, N = 256, M = 256 over the pair
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PAIR_X >> 3) << 17) | ((uint32_t)((2 * BW) >> 4) << 24);
     constexpr int S = PAIR_STAGES;
@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
                         const float g = upper ? got : mine0;          // lower lanes: token j (their gate, the partner's up)
                         const float u = upper ? mine1 : got;          // upper lanes: token j + 1 (the partner's gate, their up)
                         const int m = x0 + c + j + (upper ? 1 : 0);
-                        if (stores && m < M) plane[(size_t)m * features + feature] = from_float<TO>(__fdividef(g, 1.f + __expf(-g)) * u);
+                        if (stores && m < M) plane[(size_t)m * features + feature] = from_float<TO>(gate_activation<true>(g, act) * u);
                     }
                 } else if (stores) {
 #pragma unroll
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tc_pair_kernel(const __grid_c
 
 template <typename TO, bool SWIGLU>
 int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-                size_t split_stride, int* status, cudaStream_t stream) {
+                size_t split_stride, int act, int* status, cudaStream_t stream) {
     const size_t smem = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + (2 * PAIR_STAGES + 4) * 8 + 16;
     static int resident_pairs = 0;                           // pairs the device runs at once (one per TPC that can host a cluster)
     if (resident_pairs == 0) {
@@ -399,7 +399,7 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
     const unsigned pairs = (unsigned)(items < resident_pairs ? items : resident_pairs);
     const int kb_per_split = (kb_total + splits - 1) / splits;
     launch_kernel_cluster(gemm_tc_pair_kernel<TO, SWIGLU>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2, map_w, map_x, out, M, N, kb_total,
-                          kb_per_split, splits, split_stride, status);
+                          kb_per_split, splits, split_stride, act, status);
     QT_CHECK_LAUNCH("gemm_tc_pair");
     return QT_OK;
 }
@@ -483,10 +483,11 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
 
 // The same product by pairs of blocks (see gemm_tc_pair_kernel): bfloat16 or float output, meant for many tokens (a
 // pair covers 256 weight rows x 256 tokens); out[splits, M, N] in float when `splits` > 1, under the rule above.  With `swiglu` the weight's rows alternate 16 of a gate and
-// 16 of an up projection and `out` is [M, N / 2] = silu(gate) * up.  Codes in `status`: as above, 4 = the MMA issuer
+// 16 of an up projection and `out` is [M, N / 2] = act(gate) * up (`act`: one of QT_ACT_*).  Codes in `status`: as above, 4 = the MMA issuer
 // waiting for the epilogues to free an accumulator.
 extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int swiglu,
-                               int splits, long long split_stride, int* status, void* stream) {
+                               int act, int splits, long long split_stride, int* status, void* stream) {
+    QT_REQUIRE(act >= 0 && act < QT_ACT_COUNT, "gemm_tc_pair: unknown activation code %d", act);
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc_pair: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc_pair: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc_pair: operands must be 16-byte aligned");
@@ -503,9 +504,9 @@ extern "C" int qt_gemm_tc_pair(const void* x, const void* w, void* out, int out_
     rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)PAIR_HALF);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, status, s);
-    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, status, s);
-    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, status, s);
+    if (out_dtype == QT_BF16 && swiglu) return launch_pair<__nv_bfloat16, true>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, act, status, s);
+    if (out_dtype == QT_BF16) return launch_pair<__nv_bfloat16, false>(map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, 0, status, s);
+    if (out_dtype == QT_F32 && !swiglu) return launch_pair<float, false>(map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, 0, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc_pair: output type %d%s is not offered", out_dtype, swiglu ? " with the SiLU-gated epilogue" : "");
 }
 

@@ -28,7 +28,7 @@ _SIGNATURES = {
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
-        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "attention": {
         "qt_attention_prefill": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
@@ -53,12 +53,12 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
-        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
     },
     "gemm_fused": {
         "qt_gemm_fused": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_ptr, _c_int, _c_int, _c_float,
-                          _c_ptr, _c_int,
+                          _c_ptr, _c_int, _c_int,
                           _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                           _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float,
                           _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -253,7 +253,17 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
           1 if write_kv else 0, 1 if kv_in_proj else 0, _stream())
 
 
-SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid out for the GEMM's SiLU-gated epilogue
+SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid out for the GEMM's gated epilogue
+# gate activations of a gated feed-forward, act(gate) * up: names a configuration may use -> the kernels' codes
+ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu": 2, "relu": 3}
+
+
+def activation_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"unknown gate activation {name!r}; the kernels compute {sorted(ACTIVATIONS)}") from None
+
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torch.Tensor:
@@ -266,15 +276,15 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int) -> torc
     return torch.stack((gate.view(inter // group, group, hidden), up.view(inter // group, group, hidden)), dim=1).reshape(2 * inter, hidden)
 
 
-def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0) -> None:
-    """out[t, i] = silu(gate[t, i]) * up[t, i] where gate_up[t] holds gate then up (``group`` 0) or alternates
-    ``group`` elements of gate and ``group`` of up."""
+def swiglu(gate_up: GemmOut, out: torch.Tensor, group: int = 0, activation: str = "silu") -> None:
+    """out[t, i] = act(gate[t, i]) * up[t, i] where gate_up[t] holds gate then up (``group`` 0) or alternates
+    ``group`` elements of gate and ``group`` of up; ``activation`` is one of ``ACTIVATIONS``."""
     tokens, inter = out.shape
     _need(out, "out")
     if (gate_up.rows, gate_up.cols) != (tokens, 2 * inter):
         raise KernelError(f"swiglu: input {tuple(gate_up.tensor.shape)} does not match output {tuple(out.shape)}")
     _call("elementwise", "qt_swiglu", _ptr(gate_up.tensor), _code(gate_up.tensor, "gate_up"), gate_up.n_splits,
-          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, int(group), _stream())
+          gate_up.split_stride, _ptr(out), _code(out, "out"), tokens, inter, int(group), activation_code(activation), _stream())
 
 
 # ----------------------------------------------------------------------------- attention
@@ -519,14 +529,14 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
           out.n_splits, out.split_stride, int(stages), _ptr(_status_word(a.device)), _stream())
 
 
-def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False) -> None:
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False, activation: str = "silu") -> None:
     """The same product by pairs of blocks on the two SMs of a TPC (tcgen05 cta_group::2): 256 weight rows x
     256 tokens per tile, each block staging half of both operands; one persistent pair per TPC with two
     accumulators in tensor memory.  Meant for many tokens; ``out`` may be [splits, M, N] float partial sums, which
     pays for a few hundred tokens whose tiles alone do not fill the TPCs.
 
     With ``swiglu`` the rows of ``w`` alternate SWIGLU_GROUP of a gate and of an up projection
-    (``interleave_gate_up``) and ``out`` [1, M, N / 2] receives silu(gate) * up from the epilogue."""
+    (``interleave_gate_up``) and ``out`` [1, M, N / 2] receives act(gate) * up from the epilogue."""
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     rows, k = a.shape
@@ -538,7 +548,8 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = 
     if not out.tensor.is_cuda or out.tensor.dtype not in _CODES:
         raise KernelError("gemm_tc_pair: the output must be a bfloat16 or float32 CUDA tensor")
     _call("gemm_tc", "qt_gemm_tc_pair", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k,
-          1 if swiglu else 0, out.n_splits, out.split_stride, _ptr(_status_word(a.device)), _stream())
+          1 if swiglu else 0, activation_code(activation) if swiglu else 0, out.n_splits, out.split_stride,
+          _ptr(_status_word(a.device)), _stream())
 
 
 def gemm_uses_pairs(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -609,7 +620,8 @@ def fused_qkv_supported(head_dim: int, rotary_dim: int) -> bool:
 
 def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual=None, norm_w=None, xw=None, sq_out=None,
            q_out=None, k_cache=None, v_cache=None, token_seq=None, token_pos=None, block_table=None, q_w=None, k_w=None,
-           qk_eps=0.0, cos_sin=None, nq=0, nkv=0, d=0, page_tokens=0, ring_tokens=0, write_kv=False, stages: int = 0) -> None:
+           qk_eps=0.0, cos_sin=None, nq=0, nkv=0, d=0, page_tokens=0, ring_tokens=0, write_kv=False, stages: int = 0,
+           act: int = 0) -> None:
     scaled = x if isinstance(x, ScaledRows) else None
     a = scaled.tensor if scaled is not None else x
     _need(a, "x", torch.bfloat16)
@@ -627,7 +639,7 @@ def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual
     _call("gemm_fused", "qt_gemm_fused", _ptr(a), _ptr(w), rows, w.shape[0], k, tc_token_tile(rows), int(splits), int(stages), epilogue,
           _ptr(scaled.sq) if scaled is not None else None, scaled.sq.shape[0] if scaled is not None else 0,
           scaled.width if scaled is not None else 0, float(scaled.eps) if scaled is not None else 0.0,
-          _ptr(out), _CODES.get(out.dtype, -1) if out is not None else 0,
+          _ptr(out), _CODES.get(out.dtype, -1) if out is not None else 0, int(act),
           _ptr(residual), _ptr(norm_w), _ptr(xw), _ptr(sq_out),
           _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(token_seq), _ptr(token_pos), _ptr(block_table),
           block_table.shape[1] if block_table is not None else 0, _ptr(q_w), _ptr(k_w), float(qk_eps),
@@ -659,12 +671,12 @@ def gemm_fused_residual(x, w: torch.Tensor, residual: torch.Tensor, norm_weight:
     return ScaledRows(xw, sq, n, float(eps))
 
 
-def gemm_fused_swiglu(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0) -> None:
-    """out [M, N / 2] (bfloat16) = silu(gate) * up for a weight whose rows alternate SWIGLU_GROUP of gate and of up."""
+def gemm_fused_swiglu(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0, activation: str = "silu") -> None:
+    """out [M, N / 2] (bfloat16) = act(gate) * up for a weight whose rows alternate SWIGLU_GROUP of gate and of up."""
     if w.shape[0] % (2 * SWIGLU_GROUP):
         raise KernelError(f"gemm_fused_swiglu: {w.shape[0]} rows are not gate and up rows in groups of {SWIGLU_GROUP}")
     _need(out, "out", torch.bfloat16, (x.shape[0], w.shape[0] // 2))
-    _fused(x, w, splits, _EPI_SWIGLU, out=out, stages=stages)
+    _fused(x, w, splits, _EPI_SWIGLU, out=out, stages=stages, act=activation_code(activation))
 
 
 def gemm_fused_qkv(x, w: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None, v_cache: torch.Tensor | None,

@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: down(act(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:10-22).
+"""Dense gated feed-forward: down(act(gate(x)) * up(x)) (qwen_triton/modules/mlp.py:10-22, where act is SiLU;
+here it is a parameter: any of ``kernels.ACTIVATIONS``).
 
 gate and up run as one product over the fused weight [gate; up].  In bfloat16 its rows alternate 16 of gate and
 16 of up, so that the GEMM for many tokens can apply the SiLU gate in its epilogue (one warp then holds both halves
@@ -25,9 +26,9 @@ class GatedMLP:
         self.runtime = runtime
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
-        activation = params.get("activation", "silu")
-        if activation != "silu":
-            raise ValueError(f"{prefix}: the gated feed-forward kernel computes SiLU, not {activation!r}")
+        self.activation = params.get("activation", "silu")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"{prefix}: gate activation {self.activation!r} is not one of {sorted(kernels.ACTIVATIONS)}")
         self.names = {k: params.get(k, f"{k}_proj") for k in ("gate", "up", "down")}
         fused = runtime.dtype == torch.bfloat16 and self.inter % kernels.SWIGLU_GROUP == 0 and self.hidden % 8 == 0
         self.group = kernels.SWIGLU_GROUP if fused else 0
@@ -56,10 +57,10 @@ class GatedMLP:
         tokens = x.shape[0]
         act = self.runtime.workspace.view("mlp.act", tokens, self.inter)
         if self.takes_scaled_rows and self.gate_up.fusable(tokens):
-            self.gate_up.into_swiglu(x, act)
+            self.gate_up.into_swiglu(x, act, self.activation)
             return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
         if self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
-            kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True)
+            kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
         else:
-            kernels.swiglu(self.gate_up(x), act, self.group)
+            kernels.swiglu(self.gate_up(x), act, self.group, self.activation)
         return self.down(act)

@@ -152,8 +152,9 @@ class Linear:
         """residual += x W^T, and the norm behind it prepared (see ``kernels.gemm_fused_residual``)."""
         return kernels.gemm_fused_residual(x, self.weight, residual, norm_weight, eps, xw, sq, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages())
 
-    def into_swiglu(self, x, out: torch.Tensor) -> None:
-        kernels.gemm_fused_swiglu(x, self.weight, out, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages())
+    def into_swiglu(self, x, out: torch.Tensor, activation: str = "silu") -> None:
+        kernels.gemm_fused_swiglu(x, self.weight, out, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(),
+                                  activation=activation)
 
     def into_qkv(self, x, *args, **kwargs) -> None:
         kernels.gemm_fused_qkv(x, self.weight, *args, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(), **kwargs)

@@ -7,7 +7,7 @@ import torch
 import plain_qwen3 as plain
 from qwen_triton_b200.ops import kernels
 from qwen_triton_b200.ops.kernels import ScaledRows
-from test_gpu_kernels import DEV, PAGE, close, paged, rand
+from test_gpu_kernels import DEV, PAGE, close, gate_act, paged, rand
 
 pytestmark = pytest.mark.gpu
 BF16 = torch.bfloat16
@@ -82,6 +82,9 @@ def test_silu_gate(rows, inter, k, splits):
     kernels.check_status(DEV)
     g, u = product(handed.tensor, gate) * factor, product(handed.tensor, up) * factor
     close(out, g * torch.sigmoid(g) * u, BF16, "silu(gate) * up")
+    for name in ("gelu", "relu"):
+        kernels.gemm_fused_swiglu(handed, w, out, splits, activation=name)
+        close(out, gate_act(name, g) * u, BF16, f"{name}(gate) * up")
 
 
 @pytest.mark.parametrize("nq, nkv, d, rotary, ring, splits, lengths, own_kv", [

@@ -26,6 +26,12 @@ def rand(*shape, seed=0, scale=1.0, dtype=torch.float32):
     return (torch.randn(*shape, generator=gen(seed)) * scale).to(dtype).to(DEV)
 
 
+def gate_act(name, g):
+    """The gate activations the kernels offer, stated plainly."""
+    return {"silu": lambda x: x * torch.sigmoid(x), "gelu": lambda x: torch.nn.functional.gelu(x),
+            "gelu_tanh": lambda x: torch.nn.functional.gelu(x, approximate="tanh"), "relu": torch.relu}[name](g)
+
+
 def close(actual, expected, dtype, what=""):
     torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), **TOL[dtype], msg=lambda m: f"{what}: {m}")
 
@@ -164,6 +170,11 @@ def test_swiglu(dtype, tokens, inter, group):      # vector form, scalar form, s
         out = torch.empty(tokens, inter, dtype=dtype, device=DEV)
         kernels.swiglu(GemmOut(gate_up), out, group)
         close(out, torch.nn.functional.silu(gate.float().sum(0)) * up.float().sum(0), dtype, f"splits={splits}")
+        for name in ("gelu", "gelu_tanh", "relu"):                  # the activation is a parameter of the part
+            kernels.swiglu(GemmOut(gate_up), out, group, name)
+            close(out, gate_act(name, gate.float().sum(0)) * up.float().sum(0), dtype, f"{name}, splits={splits}")
+    with pytest.raises(kernels.KernelError, match="activation"):
+        kernels.swiglu(GemmOut(gate_up), out, group, "softplus")
 
 
 # ----------------------------------------------------------------------------- matrix product
@@ -435,6 +446,8 @@ def test_gemm_block_pairs_with_the_silu_gate_in_the_epilogue(m, inter, k):
     kernels.check_status(DEV)
     expected = torch.nn.functional.silu(a.double() @ gate.double().T) * (a.double() @ up.double().T)
     close(out[0], expected, torch.bfloat16, f"{m} tokens, {inter} features, K={k}")
+    kernels.gemm_tc_pair(a, w, GemmOut(out), swiglu=True, activation="gelu_tanh")
+    close(out[0], gate_act("gelu_tanh", a.double() @ gate.double().T) * (a.double() @ up.double().T), torch.bfloat16, "gelu_tanh")
     with pytest.raises(kernels.KernelError):
         kernels.gemm_tc_pair(a, w[:-8], GemmOut(out[:, :, :-4].contiguous()), swiglu=True)
 

@@ -126,8 +126,24 @@ def test_feed_forward_part(dtype, inter, tokens):
     x = (torch.randn(tokens, 72, generator=torch.Generator().manual_seed(6))).to(DTYPES[dtype])
     out = ff.forward(x.to(DEV), None).value()
     assert_close(out, plain.gated_mlp(x.float(), {k: v.float() for k, v in w.items()}, "m"), dtype, "feed-forward part")
-    with pytest.raises(ValueError, match="SiLU"):
-        part_class("feed_forward", PartSpec("gated_mlp"))({**params, "activation": "gelu"}, "m", rt)
+    with pytest.raises(ValueError, match="activation"):
+        part_class("feed_forward", PartSpec("gated_mlp"))({**params, "activation": "softplus"}, "m", rt)
+
+
+@pytest.mark.parametrize("tokens", [9, 300])
+def test_feed_forward_part_with_another_activation(tokens):
+    """The gate's activation is a parameter of the part: GELU here, through the few-token and the many-token kernels."""
+    rt = runtime("bf16", max_tokens=512)
+    params = {"hidden_size": 72, "intermediate_size": 208, "activation": "gelu_pytorch_tanh"}
+    ff = part_class("feed_forward", PartSpec("gated_mlp"))(params, "m", rt)
+    w = weights_for(ff.expected_tensors(params, "m"), "bf16", seed=5)
+    ff.load(w.__getitem__)
+    rt.workspace.allocate()
+    x = torch.randn(tokens, 72, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    wf = {k: v.float() for k, v in w.items()}
+    gate, up = x.float() @ wf["m.gate_proj.weight"].T, x.float() @ wf["m.up_proj.weight"].T
+    want = (torch.nn.functional.gelu(gate, approximate="tanh") * up).to(torch.bfloat16).float() @ wf["m.down_proj.weight"].T
+    assert_close(ff.forward(x.to(DEV), None).value(), want, "bf16", "feed-forward part with GELU")
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
