@@ -47,7 +47,9 @@ class SequenceCache:
     """Slots, paged key/value pools per group, and per-slot state.
 
     ``requests[i]`` is what schedule position ``i`` asks for (``KVRequest``, ``StateRequest`` or
-    None) and ``cache_of[i]`` the position whose entry it reads instead (or None).
+    None; or a list of them where the layer has several parts that keep something per sequence) and
+    ``cache_of[i]`` the position whose entries it reads instead (or None).  ``view(i)`` gives one
+    ``CacheView`` for a single request and a tuple of them, in the order asked, for a list.
     """
 
     def __init__(self, requests, cache_of, *, max_tokens: int, max_seq_len: int, dtype: torch.dtype,
@@ -61,27 +63,34 @@ class SequenceCache:
         total_pages = max(1, round_up(max_tokens, page_tokens) // page_tokens)
         self.num_slots = num_slots if num_slots is not None else total_pages
         self.groups: list[_Group] = []
-        self._entry_of: dict[int, tuple[int, int]] = {}     # schedule position -> (group, entry)
-        self._state_of: dict[int, torch.Tensor] = {}
-        self._state_requests: dict[int, StateRequest] = {}
+        self._entry_of: dict[tuple[int, int], tuple[int, int]] = {}     # (schedule position, request number) -> (group, entry)
+        self._state_of: dict[tuple[int, int], torch.Tensor] = {}
+        self._state_requests: dict[tuple[int, int], StateRequest] = {}
         self._cache_of = list(cache_of)
-        for position, request in enumerate(requests):
-            if self._cache_of[position] is not None or request is None:
+        self._counts: list[int | None] = []        # requests per position (None: a single request, viewed as one CacheView)
+        for position, asked in enumerate(requests):
+            several = isinstance(asked, (list, tuple))
+            self._counts.append(len(asked) if several else None)
+            if self._cache_of[position] is not None:
                 continue
-            if isinstance(request, StateRequest):
-                self._state_requests[position] = request
-                continue
-            for index, group in enumerate(self.groups):
-                if group.request == request:
-                    break
-            else:
-                ring = 0
-                if request.window:
-                    ring = round_up(request.window + chunk_tokens - 1, page_tokens)
-                self.groups.append(_Group(request, [], ring))
-                index = len(self.groups) - 1
-            self._entry_of[position] = (index, len(self.groups[index].owners))
-            self.groups[index].owners.append(position)
+            for number, request in enumerate(asked if several else [asked]):
+                if request is None:
+                    continue
+                key = (position, number)
+                if isinstance(request, StateRequest):
+                    self._state_requests[key] = request
+                    continue
+                for index, group in enumerate(self.groups):
+                    if group.request == request:
+                        break
+                else:
+                    ring = 0
+                    if request.window:
+                        ring = round_up(request.window + chunk_tokens - 1, page_tokens)
+                    self.groups.append(_Group(request, [], ring))
+                    index = len(self.groups) - 1
+                self._entry_of[key] = (index, len(self.groups[index].owners))
+                self.groups[index].owners.append(key)
         geometry = [GroupGeometry(total_pages, g.ring_tokens // page_tokens) for g in self.groups]
         self.book = CacheBook(self.num_slots, page_tokens, geometry, max_seq_len)
         self.has_window = any(g.ring_tokens for g in self.groups)
@@ -94,24 +103,29 @@ class SequenceCache:
                 shape = (len(group.owners), total_pages + 1, group.request.kv_heads, page_tokens, group.request.head_dim)
                 group.k = torch.zeros(shape, dtype=dtype, device=device)
                 group.v = torch.zeros(shape, dtype=dtype, device=device)
-            for position, request in self._state_requests.items():
-                self._state_of[position] = torch.zeros((self.num_slots + 1, *request.shape), dtype=request.dtype, device=device)
+            for key, request in self._state_requests.items():
+                self._state_of[key] = torch.zeros((self.num_slots + 1, *request.shape), dtype=request.dtype, device=device)
 
     # ------------------------------------------------------------------ views
-    def view(self, position: int) -> CacheView:
+    def view(self, position: int):
         source = self._cache_of[position]
         owner = position if source is None else source
-        view = CacheView(page_tokens=self.page_tokens, writable=source is None)
-        if owner in self._entry_of:
-            group_index, entry = self._entry_of[owner]
-            group = self.groups[group_index]
-            view.group = group_index
-            view.ring_tokens = group.ring_tokens
-            if group.k is not None:
-                view.k, view.v = group.k[entry], group.v[entry]
-        if owner in self._state_of:
-            view.state = self._state_of[owner]
-        return view
+        count = self._counts[owner]
+        views = []
+        for number in range(1 if count is None else count):
+            key = (owner, number)
+            view = CacheView(page_tokens=self.page_tokens, writable=source is None)
+            if key in self._entry_of:
+                group_index, entry = self._entry_of[key]
+                group = self.groups[group_index]
+                view.group = group_index
+                view.ring_tokens = group.ring_tokens
+                if group.k is not None:
+                    view.k, view.v = group.k[entry], group.v[entry]
+            if key in self._state_of:
+                view.state = self._state_of[key]
+            views.append(view)
+        return views[0] if count is None else tuple(views)
 
     # ------------------------------------------------------------------ slots
     def alloc(self) -> int:

@@ -41,7 +41,11 @@ class LayerSpec:
     ``prefix`` is the tensor-name prefix of the layer in the checkpoint
     (``model.layers.3``).  ``block`` names the arrangement of the parts
     (``pre_norm``); the arrangement's parameters give the sub-prefixes under
-    which each part finds its tensors.
+    which each part finds its tensors.  ``extra`` holds, by a name the block
+    arrangement knows, the parts a layer has beyond one mixer, one
+    feed-forward and one kind of norm: ``pre_norm`` reads ``mixer_norm`` and
+    ``feed_forward_norm`` from it (another norm kind in one of the two places);
+    an arrangement with a second mixer beside the first finds it there.
     """
 
     prefix: str
@@ -49,6 +53,7 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward: PartSpec
     norm: PartSpec
+    extra: Mapping[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -46,11 +46,13 @@ class CausalLM:
         self.head.load(source, self.embedding)
 
     def cache_requests(self) -> list:
-        """Per schedule position: what its mixer keeps per sequence (None for a reader of another entry)."""
+        """Per schedule position: what its block keeps per sequence (None for a reader of another position's
+        entries): one request, or a list where the block has several parts that keep something."""
         out = []
         for call in self.spec.schedule:
-            mixer = self.blocks[call.layer].mixer
-            out.append(mixer.cache_request() if call.cache_of is None else None)
+            block = self.blocks[call.layer]
+            asked = block.cache_requests() if hasattr(block, "cache_requests") else block.mixer.cache_request()
+            out.append(asked if call.cache_of is None else ([None] * len(asked) if isinstance(asked, (list, tuple)) else None))
         return out
 
     def weight_bytes(self) -> int:

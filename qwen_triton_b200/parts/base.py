@@ -18,7 +18,8 @@ Interfaces (what a new part must offer):
   uses (``cache.writable`` tells whether it owns it).
 * feed-forward: ``forward(x, ctx) -> GemmOut``.
 * block:       ``forward(stream, ctx, cache) -> None``: arranges norm, mixer and feed-forward
-  around the residual stream.
+  around the residual stream; ``cache_requests()`` says what it keeps per sequence: its mixer's
+  request, or a list of requests if it has several such parts (``cache`` is then a tuple of views).
 * a part whose work in a step is kernel launches only (no host reads, no shapes that depend on data) may set
   ``graph_safe = True``; a block reports it for the parts it runs.  One-token steps are captured in CUDA graphs
   only if the embedding, every block, the final norm and the head say so.

@@ -14,8 +14,9 @@ from .base import ResidualStream, Runtime, part_class, register_block
 class PreNormBlock:
     def __init__(self, layer: LayerSpec, runtime: Runtime) -> None:
         names = self._names(layer)
-        self.mixer_norm = part_class("norm", layer.norm)(layer.norm.params, names["mixer_norm"], runtime)
-        self.feed_forward_norm = part_class("norm", layer.norm)(layer.norm.params, names["feed_forward_norm"], runtime)
+        norms = self._norm_specs(layer)
+        self.mixer_norm = part_class("norm", norms[0])(norms[0].params, names["mixer_norm"], runtime)
+        self.feed_forward_norm = part_class("norm", norms[1])(norms[1].params, names["feed_forward_norm"], runtime)
         self.mixer = part_class("mixer", layer.mixer)(layer.mixer.params, names["mixer"], runtime)
         self.feed_forward = part_class("feed_forward", layer.feed_forward)(layer.feed_forward.params,
                                                                            names["feed_forward"], runtime)
@@ -25,17 +26,28 @@ class PreNormBlock:
         p = layer.block.params
         return {key: f"{layer.prefix}.{p.get(key, key)}" for key in ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")}
 
+    @staticmethod
+    def _norm_specs(layer: LayerSpec):
+        """The norm in front of the mixer and the one in front of the feed-forward: ``layer.norm`` for both unless
+        ``layer.extra`` names another kind for one of them."""
+        return layer.extra.get("mixer_norm", layer.norm), layer.extra.get("feed_forward_norm", layer.norm)
+
     @classmethod
     def expected_tensors(cls, layer: LayerSpec) -> dict[str, TensorSpec]:
         names = cls._names(layer)
         out: dict[str, TensorSpec] = {}
-        norm_cls = part_class("norm", layer.norm)
-        out.update(norm_cls.expected_tensors(layer.norm.params, names["mixer_norm"]))
-        out.update(norm_cls.expected_tensors(layer.norm.params, names["feed_forward_norm"]))
+        norms = cls._norm_specs(layer)
+        out.update(part_class("norm", norms[0]).expected_tensors(norms[0].params, names["mixer_norm"]))
+        out.update(part_class("norm", norms[1]).expected_tensors(norms[1].params, names["feed_forward_norm"]))
         out.update(part_class("mixer", layer.mixer).expected_tensors(layer.mixer.params, names["mixer"]))
         out.update(part_class("feed_forward", layer.feed_forward).expected_tensors(layer.feed_forward.params,
                                                                                    names["feed_forward"]))
         return out
+
+    def cache_requests(self):
+        """What this block keeps per sequence: its mixer's request.  (A block with several such parts returns a
+        list, and its ``forward`` then gets a tuple of cache views in the same order.)"""
+        return self.mixer.cache_request()
 
     def parts(self) -> tuple:
         """The parts this block runs in a step."""

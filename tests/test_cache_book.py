@@ -3,6 +3,7 @@ import random
 
 import pytest
 
+from qwen_triton_b200.cache.store import CacheView
 from qwen_triton_b200.cache import CacheBook, CacheError, CacheFull, GroupGeometry, SequenceCache
 from qwen_triton_b200.parts.base import KVRequest, StateRequest
 
@@ -106,10 +107,25 @@ def test_groups_by_need_and_shared_entries():
     cache = SequenceCache(requests, cache_of, max_tokens=1000, max_seq_len=512, dtype=None, device=None,
                           chunk_tokens=32, allocate=False)
     assert len(cache.groups) == 2
-    assert cache.groups[0].owners == [0, 1] and cache.groups[1].owners == [2, 5]
+    assert cache.groups[0].owners == [(0, 0), (1, 0)] and cache.groups[1].owners == [(2, 0), (5, 0)]      # (position, request number)
     assert cache.groups[0].ring_tokens == 0 and cache.groups[1].ring_tokens == 64      # 24 + 32 - 1 rounded up to pages
     assert cache.num_slots == 16 and cache.book.groups[1].ring_pages == 1
     reader = cache.view(3)
     assert reader.group == 0 and not reader.writable                                    # reads the entry of position 1
     assert cache.view(4).group is None and cache.view(2).ring_tokens == 64
     assert cache.max_blocks(0) == 8 and cache.max_blocks(1) == 1
+
+
+def test_a_layer_with_several_parts_that_keep_something():
+    """A position may ask for a list (keys and values beside a fixed-size state): its view is a tuple in that order,
+    and a later position that reads its entries sees both, read-only."""
+    full = KVRequest(2, 16)
+    requests = [full, [full, StateRequest((3,)), None], [None, None, None]]
+    cache = SequenceCache(requests, [None, None, 1], max_tokens=256, max_seq_len=128, dtype=None, device=None, allocate=False)
+    assert len(cache.groups) == 1 and cache.groups[0].owners == [(0, 0), (1, 0)]
+    assert isinstance(cache.view(0), CacheView)
+    pair = cache.view(1)
+    assert isinstance(pair, tuple) and len(pair) == 3
+    assert pair[0].group == 0 and pair[0].writable and pair[1].group is None and pair[2].group is None
+    reader = cache.view(2)
+    assert len(reader) == 3 and reader[0].group == 0 and not reader[0].writable

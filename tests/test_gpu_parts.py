@@ -374,3 +374,153 @@ def test_padded_rows_of_a_captured_step_leave_every_live_state_alone(dtype):
     for i, tokens in enumerate(requests):
         assert_close(torch.cat(rows[i]), toy_oracle(raw, wf, tokens)[prompt - 1:7], dtype, f"request {i} in slot {slots[i]}")
         engine.release(slots[i])
+
+
+# ----------------------------------------------------------------------------- a block with two parts that keep something
+class ToyTwoBranchBlock:
+    """h += attention(norm1(h)) + decay_mixer(norm1(h)); h += feed_forward(norm2(h)): an arrangement with a recurrent
+    branch beside the attention, defined here.  It asks the cache for keys/values and for a state block, and gets a
+    tuple of two views; its second mixer comes from ``LayerSpec.extra``, as does another norm kind in front of the
+    feed-forward."""
+
+    def __init__(self, layer, runtime):
+        p = layer.prefix
+        self.norm1 = part_class("norm", layer.norm)(layer.norm.params, f"{p}.norm1", runtime)
+        second = layer.extra.get("feed_forward_norm", layer.norm)
+        self.norm2 = part_class("norm", second)(second.params, f"{p}.norm2", runtime)
+        self.attention = part_class("mixer", layer.mixer)(layer.mixer.params, f"{p}.attn", runtime)
+        side = layer.extra["side_mixer"]
+        self.side = part_class("mixer", side)(side.params, f"{p}.side", runtime)
+        self.feed_forward = part_class("feed_forward", layer.feed_forward)(layer.feed_forward.params, f"{p}.ff", runtime)
+        self.runtime = runtime
+
+    @classmethod
+    def expected_tensors(cls, layer):
+        p, out = layer.prefix, {}
+        second = layer.extra.get("feed_forward_norm", layer.norm)
+        out.update(part_class("norm", layer.norm).expected_tensors(layer.norm.params, f"{p}.norm1"))
+        out.update(part_class("norm", second).expected_tensors(second.params, f"{p}.norm2"))
+        out.update(part_class("mixer", layer.mixer).expected_tensors(layer.mixer.params, f"{p}.attn"))
+        out.update(part_class("mixer", layer.extra["side_mixer"]).expected_tensors(layer.extra["side_mixer"].params, f"{p}.side"))
+        out.update(part_class("feed_forward", layer.feed_forward).expected_tensors(layer.feed_forward.params, f"{p}.ff"))
+        return out
+
+    graph_safe = True
+
+    def load(self, source):
+        for part in (self.norm1, self.norm2, self.attention, self.side, self.feed_forward):
+            part.load(source)
+
+    def cache_requests(self):
+        return [self.attention.cache_request(), self.side.cache_request()]
+
+    def forward(self, stream, ctx, caches):
+        x = self.norm1.apply(stream)
+        both = self.attention.forward(x, ctx, caches[0]).value() + self.side.forward(x, ctx, caches[1]).value()
+        stream.add(GemmOut(both[None].contiguous()))
+        x = self.norm2.apply(stream)
+        stream.add(self.feed_forward.forward(x, ctx))
+
+
+class ToyShiftedNorm:
+    """x * rsqrt(mean(x^2) + eps) * (w + 0.5): another norm kind for one of a block's two places."""
+
+    graph_safe = True
+
+    def __init__(self, params, name, runtime):
+        self.size, self.eps, self.name, self.runtime = int(params["size"]), float(params["eps"]), name, runtime
+        runtime.workspace.declare("toy_shifted", runtime.max_step_tokens * self.size, runtime.dtype)
+
+    @classmethod
+    def expected_tensors(cls, params, name):
+        return {f"{name}.weight": TensorSpec((int(params["size"]),), role="vector", init_std=0.1, init_mean=1.0)}
+
+    def load(self, source):
+        self.weight = (source(f"{self.name}.weight").float() + 0.5).to(self.runtime.device).contiguous()
+
+    def apply(self, stream, rows=None):
+        from qwen_triton_b200.ops import kernels
+        count = stream.residual.shape[0] if rows is None else rows.shape[0]
+        out = self.runtime.workspace.view("toy_shifted", count, self.size)
+        kernels.add_rmsnorm(stream.residual, stream.pending, self.weight, self.eps, out, rows)
+        if rows is None:
+            stream.pending = None
+        return out
+
+
+class TwoBranchConfig(ToyConfig):
+    def model_spec(self):
+        r = self.raw
+        hidden = r["hidden_size"]
+        norm = PartSpec("rmsnorm", {"size": hidden, "eps": r["eps"]})
+        shifted = PartSpec("toy_shifted_norm", {"size": hidden, "eps": r["eps"]})
+        ff = PartSpec("gated_mlp", {"hidden_size": hidden, "intermediate_size": r["inter"], "activation": "relu"})
+        attn = PartSpec("attention", {"hidden_size": hidden, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "window": None,
+                                      "qk_norm": False, "position": PartSpec("none"),
+                                      "q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"})
+        side = PartSpec("toy_decay_device", {"hidden_size": hidden, "decay": r["decay"]})
+        layer = LayerSpec("blocks.0", PartSpec("toy_two_branch"), attn, ff, norm, extra={"side_mixer": side, "feed_forward_norm": shifted})
+        return ModelSpec(architecture="TwoBranchForCausalLM", vocab_size=r["vocab"], hidden_size=hidden,
+                         embedding=PartSpec("token_embedding", {"name": "embed.weight"}), layers=(layer,),
+                         schedule=(LayerCall(0), LayerCall(0)),
+                         final_norm=PartSpec("rmsnorm", {"size": hidden, "eps": r["eps"], "name": "final"}),
+                         head=PartSpec("linear_head", {"name": "head.weight", "tied_to": "embed.weight"}), max_positions=256)
+
+
+def two_branch_oracle(raw, w, tokens):
+    hidden, eps, n = raw["hidden_size"], raw["eps"], len(tokens)
+    x = w["embed.weight"][torch.tensor(tokens)]
+    p = "blocks.0"
+    for _ in range(2):                                          # the layer's weights run twice, each call with caches of its own
+        h = plain.rms_norm(x, w[f"{p}.norm1.weight"], eps)
+        q = (h @ w[f"{p}.attn.q_proj.weight"].T).view(n, 2, 16)
+        k = (h @ w[f"{p}.attn.k_proj.weight"].T).view(n, 1, 16)
+        v = (h @ w[f"{p}.attn.v_proj.weight"].T).view(n, 1, 16)
+        attended = plain.attention_scores(q, k, v, 16 ** -0.5, None).reshape(n, 32) @ w[f"{p}.attn.o_proj.weight"].T
+        proj = h @ w[f"{p}.side.mix.weight"].T
+        state, side = torch.zeros(hidden), []
+        for t in range(n):
+            state = raw["decay"] * state + proj[t]
+            side.append(state)
+        x = x + attended + torch.stack(side)
+        h = plain.rms_norm(x, w[f"{p}.norm2.weight"] + 0.5, eps)
+        gate, up = h @ w[f"{p}.ff.gate_proj.weight"].T, h @ w[f"{p}.ff.up_proj.weight"].T
+        x = x + (torch.relu(gate) * up) @ w[f"{p}.ff.down_proj.weight"].T
+    return plain.rms_norm(x, w["final.weight"], eps) @ w["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
+def test_a_block_with_two_parts_that_keep_something_and_two_norm_kinds(dtype):
+    from qwen_triton_b200.parts import register_block, register_norm
+    register_mixer("toy_decay_device", ToyDecayMixerOnDevice)
+    register_block("toy_two_branch", ToyTwoBranchBlock)
+    register_norm("toy_shifted_norm", ToyShiftedNorm)
+    register_architecture("TwoBranchForCausalLM", TwoBranchConfig)
+    raw = {"architectures": ["TwoBranchForCausalLM"], "hidden_size": 40, "inter": 48, "vocab": 61, "eps": 1e-5, "decay": 0.7}
+    from qwen_triton_b200.config import config_from_dict
+    from qwen_triton_b200.engine.model import expected_tensors
+    import json
+    config = config_from_dict(raw)
+    weights = weights_for(expected_tensors(config.model_spec()), dtype, seed=12)
+    with tempfile.TemporaryDirectory() as folder:
+        write_safetensors(f"{folder}/model.safetensors", weights)
+        with open(f"{folder}/config.json", "w") as handle:
+            json.dump(raw, handle)
+        engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=512)
+    assert len(engine.cache.groups) == 1 and len(engine.cache.groups[0].owners) == 2         # two calls, an attention entry each
+    views = engine.cache.view(1)
+    assert isinstance(views, tuple) and views[0].k is not None and views[1].state is not None
+    wf = {k: v.float() for k, v in weights.items()}
+    requests = [[5, 9, 2, 60, 30, 11, 4, 8], [17, 0, 41, 7, 7, 19]]
+    slots = [engine.new_sequence() for _ in requests]
+    first = engine.step([StepEntry(slots[0], requests[0][:3], [0, 1, 2]), StepEntry(slots[1], requests[1][:2], [0, 1])])
+    rows = {0: [first[:3]], 1: [first[3:]]}
+    for t in range(5):
+        live = [i for i in (0, 1) if (3 if i == 0 else 2) + t < len(requests[i])]
+        out = engine.step([StepEntry(slots[i], [requests[i][(3 if i == 0 else 2) + t]], [0]) for i in live])
+        for row, i in enumerate(live):
+            rows[i].append(out[row:row + 1])
+    assert engine.graph_replays >= 2
+    for i in (0, 1):
+        assert_close(torch.cat(rows[i]), two_branch_oracle(raw, wf, requests[i]), dtype, f"request {i}")
+        engine.release(slots[i])
