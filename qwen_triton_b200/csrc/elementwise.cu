@@ -256,8 +256,9 @@ extern "C" int qt_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
 //   q head:  RMSNorm over d with q_weight (if given), rotate, store to q_out[t, h, :]
 //   k head:  RMSNorm with k_weight (if given), rotate, store into the key cache at the token's position
 //   v head:  store into the value cache
-// Rotation (rotate-half): the first rd dims are paired (i, i + rd/2); cos/sin come from the float
-// table cos_sin[pos, 0:rd/2] = cos, [rd/2:rd] = sin.  rd = 0 means no position encoding.
+// Rotation: the first rd dims are paired (i, i + rd/2) (rotate-half) or, with `interleaved`, (2i, 2i + 1); pair i
+// turns by the angle whose cos/sin come from the float table cos_sin[pos, i] = cos, [pos, rd/2 + i] = sin.
+// rd = 0 means no position encoding.
 // With kv_in_proj = 0 the projection holds query heads only; with write_kv = 0 the k and v heads
 // are skipped (a call that reads the cache another call wrote).
 struct QkvParams {
@@ -267,6 +268,7 @@ struct QkvParams {
     const float* q_weight; const float* k_weight; float eps;
     const float* cos_sin; int rotary_dim; int max_pos;
     int n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj;
+    int interleaved;        // rotation pairs are (2i, 2i + 1) instead of (i, i + rd/2)
 };
 
 template <typename TI, typename TO, bool VEC>
@@ -325,7 +327,10 @@ __global__ void qk_norm_rope_write_kernel(const QkvParams p) {
     auto rotated = [&](int i) {
         float y = value(i);
         if (rotate && i < p.rotary_dim) {
-            if (i < half) y = y * cs[i] - value(i + half) * cs[half + i];
+            if (p.interleaved) {
+                const int j = i >> 1;
+                y = (i & 1) ? y * cs[j] + value(i - 1) * cs[half + j] : y * cs[j] - value(i + 1) * cs[half + j];
+            } else if (i < half) y = y * cs[i] - value(i + half) * cs[half + i];
             else y = y * cs[i - half] + value(i - half) * cs[i];
         }
         return y;
@@ -480,7 +485,7 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
                                      const int* token_pos, const int* block_table, int max_blocks,
                                      const float* q_weight, const float* k_weight, float eps, const float* cos_sin,
                                      int rotary_dim, int max_pos, int n_tokens, int nq, int nkv, int d, int page_tokens,
-                                     int ring_tokens, int write_kv, int kv_in_proj, void* stream) {
+                                     int ring_tokens, int write_kv, int kv_in_proj, int interleaved, void* stream) {
     QT_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && d <= 1024, "qk_norm_rope_write: bad sizes T=%d nq=%d nkv=%d d=%d", n_tokens, nq, nkv, d);
     QT_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0, "qk_norm_rope_write: rotary_dim=%d must be even and at most head_dim=%d", rotary_dim, d);
     QT_REQUIRE(rotary_dim == 0 || (cos_sin && max_pos > 0), "qk_norm_rope_write: rotation needs a cos/sin table");
@@ -489,7 +494,7 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     QT_REQUIRE(!write_kv || kv_in_proj, "qk_norm_rope_write: nothing to write without k and v in the projection");
     if (n_tokens == 0) return QT_OK;
     QkvParams p{qkv, n_splits, (size_t)split_stride, q_out, k_cache, v_cache, token_seq, token_pos, block_table, max_blocks,
-                q_weight, k_weight, eps, cos_sin, rotary_dim, max_pos, n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj};
+                q_weight, k_weight, eps, cos_sin, rotary_dim, max_pos, n_tokens, nq, nkv, d, page_tokens, ring_tokens, write_kv, kv_in_proj, interleaved};
     const int warps = 4;
     const long long items = (long long)n_tokens * (nq + (kv_in_proj ? 2 * nkv : 0));
     const unsigned grid = (unsigned)((items + warps - 1) / warps);
@@ -502,7 +507,8 @@ extern "C" int qt_qk_norm_rope_write(const void* qkv, int in_dtype, int n_splits
     // to fill the machine with a few heads per warp
     const int half = d / 2;
     int pe = 0, pit = 0;
-    if (rotary_dim == d && half % 64 == 0 && half / 64 <= 2) { pe = 2; pit = half / 64; }
+    if (interleaved) { pe = 0; }                     // the register form pairs (i, i + d/2)
+    else if (rotary_dim == d && half % 64 == 0 && half / 64 <= 2) { pe = 2; pit = half / 64; }
     else if (rotary_dim == d && half == 32) { pe = 1; pit = 1; }
     const bool pair_aligned = split_stride % 2 == 0 && ((uintptr_t)qkv % 8 == 0) && ((uintptr_t)q_out % 8 == 0) && ((uintptr_t)cos_sin % 8 == 0) &&
                               (!q_weight || (uintptr_t)q_weight % 8 == 0) && (!k_weight || (uintptr_t)k_weight % 8 == 0) &&

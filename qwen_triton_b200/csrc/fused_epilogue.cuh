@@ -5,8 +5,9 @@
 //   RESIDUAL  r = residual[m, n] + y; residual[m, n] = r;  and, for the norm that follows, xw[m, n] = bf16(r * g[n])
 //             and sq_out[tile, m] = sum over the tile's 128 columns of r^2
 //   SWIGLU    act[m, f] = a(s_m * gate) * (s_m * up), a = SiLU or another QT_ACT_*, the weight's rows alternating 16 of gate and 16 of up
-//   QKV       per head (head_dim divides 128): s_m * y, RMSNorm over the head with q or k weight, rotate-half by the
-//             cos/sin table at the token's position, then q to q_out and k, v into the paged cache
+//   QKV       per head (head_dim divides 128): s_m * y, RMSNorm over the head with q or k weight, rotation by the
+//             cos/sin table at the token's position (pairs (i, i + rd/2) or (2i, 2i + 1)), then q to q_out and k, v
+//             into the paged cache
 //
 // s_m is the factor of an RMSNorm whose weight g was applied by the producer of X (X = bf16(r * g)):
 // s_m = rsqrt(sum over tiles of sq_in[tile, m] / hidden + eps); the product is linear in X, so scaling the result
@@ -41,6 +42,7 @@ struct EpilogueParams {
     const float* q_w; const float* k_w; float qk_eps;
     const float* cos_sin; int rotary_dim; int max_pos;
     int nq, nkv, d, page_tokens, ring_tokens, write_kv;
+    int interleaved;        // QKV: rotation pairs are (2i, 2i + 1) instead of (i, i + rd/2)
 };
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -86,9 +88,16 @@ __device__ __forceinline__ Operands load_operands(const EpilogueParams& p, int m
         o.pos = p.token_pos[m];
         if (valid && w) o.c = ld4(w + c);
         if (valid && (is_q || is_k) && c < p.rotary_dim) {
-            const float* cs = p.cos_sin + (size_t)(o.pos < p.max_pos ? o.pos : p.max_pos - 1) * p.rotary_dim + (c < half ? c : c - half);
-            o.a = ld4(cs);
-            o.b = ld4(cs + half);
+            const float* row = p.cos_sin + (size_t)(o.pos < p.max_pos ? o.pos : p.max_pos - 1) * p.rotary_dim;
+            if (p.interleaved) {                            // this lane's pairs c/2 and c/2 + 1
+                const float2 co = *reinterpret_cast<const float2*>(row + (c >> 1)), si = *reinterpret_cast<const float2*>(row + half + (c >> 1));
+                o.a = make_float4(co.x, co.y, 0.f, 0.f);
+                o.b = make_float4(si.x, si.y, 0.f, 0.f);
+            } else {
+                const float* cs = row + (c < half ? c : c - half);
+                o.a = ld4(cs);
+                o.b = ld4(cs + half);
+            }
         }
         if (valid && !is_q && p.write_kv) {
             const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
@@ -157,10 +166,14 @@ __device__ __forceinline__ void finish(const EpilogueParams& p, const Operands& 
         const int half = p.rotary_dim >> 1;
         const bool rotates = valid && (is_q || is_k) && c < p.rotary_dim;
         const bool low = c < half;
-        const int partner = rotates ? (low ? lane + (half >> 2) : lane - (half >> 2)) : lane;
+        const int partner = rotates && !p.interleaved ? (low ? lane + (half >> 2) : lane - (half >> 2)) : lane;
         const float4 other = make_float4(__shfl_sync(0xffffffffu, v.x, partner), __shfl_sync(0xffffffffu, v.y, partner),
                                          __shfl_sync(0xffffffffu, v.z, partner), __shfl_sync(0xffffffffu, v.w, partner));
-        if (rotates) {
+        if (rotates && p.interleaved) {                     // both elements of a pair sit in this lane
+            const float x0 = v.x, x1 = v.y, x2 = v.z, x3 = v.w;
+            v.x = x0 * ops.a.x - x1 * ops.b.x; v.y = x1 * ops.a.x + x0 * ops.b.x;
+            v.z = x2 * ops.a.y - x3 * ops.b.y; v.w = x3 * ops.a.y + x2 * ops.b.y;
+        } else if (rotates) {
             const float4 co = ops.a, si = ops.b;
             if (low) { v.x = v.x * co.x - other.x * si.x; v.y = v.y * co.y - other.y * si.y; v.z = v.z * co.z - other.z * si.z; v.w = v.w * co.w - other.w * si.w; }
             else { v.x = v.x * co.x + other.x * si.x; v.y = v.y * co.y + other.y * si.y; v.z = v.z * co.z + other.z * si.z; v.w = v.w * co.w + other.w * si.w; }

@@ -264,7 +264,7 @@ extern "C" int qt_gemm_fused(const void* x, const void* w, int M, int N, int K, 
                              void* q_out, void* k_cache, void* v_cache, const int* token_seq, const int* token_pos,
                              const int* block_table, int max_blocks, const float* q_w, const float* k_w, float qk_eps,
                              const float* cos_sin, int rotary_dim, int max_pos, int nq, int nkv, int d, int page_tokens,
-                             int ring_tokens, int write_kv, int* status, void* stream) {
+                             int ring_tokens, int write_kv, int interleaved, int* status, void* stream) {
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_fused: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_fused: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_fused: operands must be 16-byte aligned");
@@ -284,7 +284,7 @@ extern "C" int qt_gemm_fused(const void* x, const void* w, int M, int N, int K, 
     e.q_out = (__nv_bfloat16*)q_out; e.k_cache = (__nv_bfloat16*)k_cache; e.v_cache = (__nv_bfloat16*)v_cache;
     e.token_seq = token_seq; e.token_pos = token_pos; e.block_table = block_table; e.max_blocks = max_blocks;
     e.q_w = q_w; e.k_w = k_w; e.qk_eps = qk_eps; e.cos_sin = cos_sin; e.rotary_dim = rotary_dim; e.max_pos = max_pos;
-    e.nq = nq; e.nkv = nkv; e.d = d; e.page_tokens = page_tokens; e.ring_tokens = ring_tokens; e.write_kv = write_kv;
+    e.nq = nq; e.nkv = nkv; e.d = d; e.page_tokens = page_tokens; e.ring_tokens = ring_tokens; e.write_kv = write_kv; e.interleaved = interleaved;
     int rc = check_epilogue("gemm_fused", epilogue, e, out_dtype);
     if (rc) return rc;
     CUtensorMap map_w, map_x;

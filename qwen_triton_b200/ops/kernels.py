@@ -27,7 +27,7 @@ _SIGNATURES = {
                            _c_int, _c_ptr],
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                   _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
         "qt_swiglu": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "attention": {
@@ -61,7 +61,7 @@ _SIGNATURES = {
                           _c_ptr, _c_int, _c_int,
                           _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                           _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float,
-                          _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                          _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     },
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -219,10 +219,12 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
                        token_seq: torch.Tensor, token_pos: torch.Tensor, block_table: torch.Tensor | None,
                        q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                        cos_sin: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int,
-                       page_tokens: int, ring_tokens: int, write_kv: bool = True, kv_in_proj: bool = True) -> None:
+                       page_tokens: int, ring_tokens: int, write_kv: bool = True, kv_in_proj: bool = True,
+                       interleaved: bool = False) -> None:
     """Per-head q/k RMSNorm, rotation and the cache write, from the fused projection output.
 
-    qkv [*, T, (nq + 2 nkv) d]; q_out [T, nq, d]; caches [pages, nkv, page_tokens, d]; cos_sin float [P, rd].
+    qkv [*, T, (nq + 2 nkv) d]; q_out [T, nq, d]; caches [pages, nkv, page_tokens, d]; cos_sin float [P, rd]
+    (cos | sin of the rd/2 pair angles); pairs are (i, i + rd/2), or (2i, 2i + 1) with ``interleaved``.
     """
     tokens = qkv.rows
     width = (num_heads + (2 * num_kv_heads if kv_in_proj else 0)) * head_dim
@@ -250,7 +252,7 @@ def qk_norm_rope_write(qkv: GemmOut, q_out: torch.Tensor, k_cache: torch.Tensor 
           qkv.split_stride, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _code(q_out, "q_out"), _ptr(token_seq),
           _ptr(token_pos), _ptr(block_table), max_blocks, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos_sin),
           rotary_dim, max_pos, tokens, num_heads, num_kv_heads, head_dim, page_tokens, ring_tokens,
-          1 if write_kv else 0, 1 if kv_in_proj else 0, _stream())
+          1 if write_kv else 0, 1 if kv_in_proj else 0, 1 if interleaved else 0, _stream())
 
 
 SWIGLU_GROUP = 16      # rows of gate and of up that alternate in a weight laid out for the GEMM's gated epilogue
@@ -621,7 +623,7 @@ def fused_qkv_supported(head_dim: int, rotary_dim: int) -> bool:
 def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual=None, norm_w=None, xw=None, sq_out=None,
            q_out=None, k_cache=None, v_cache=None, token_seq=None, token_pos=None, block_table=None, q_w=None, k_w=None,
            qk_eps=0.0, cos_sin=None, nq=0, nkv=0, d=0, page_tokens=0, ring_tokens=0, write_kv=False, stages: int = 0,
-           act: int = 0) -> None:
+           act: int = 0, interleaved: bool = False) -> None:
     scaled = x if isinstance(x, ScaledRows) else None
     a = scaled.tensor if scaled is not None else x
     _need(a, "x", torch.bfloat16)
@@ -644,7 +646,7 @@ def _fused(x, w: torch.Tensor, splits: int, epilogue: int, *, out=None, residual
           _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(token_seq), _ptr(token_pos), _ptr(block_table),
           block_table.shape[1] if block_table is not None else 0, _ptr(q_w), _ptr(k_w), float(qk_eps),
           _ptr(cos_sin), rotary_dim, max_pos, nq, nkv, d, page_tokens, ring_tokens, 1 if write_kv else 0,
-          _ptr(_status_word(a.device)), _stream())
+          1 if interleaved else 0, _ptr(_status_word(a.device)), _stream())
 
 
 def gemm_fused_store(x, w: torch.Tensor, out: torch.Tensor, splits: int = 1, stages: int = 0) -> None:
@@ -683,7 +685,7 @@ def gemm_fused_qkv(x, w: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tenso
                    token_seq: torch.Tensor, token_pos: torch.Tensor, block_table: torch.Tensor | None,
                    q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
                    num_heads: int, num_kv_heads: int, head_dim: int, page_tokens: int, ring_tokens: int,
-                   write_kv: bool = True, splits: int = 1, stages: int = 0) -> None:
+                   write_kv: bool = True, splits: int = 1, stages: int = 0, interleaved: bool = False) -> None:
     """The fused projection [q; k; v] (or q alone) with per-head q/k RMSNorm, rotation and the cache write done in
     its epilogue: what ``gemm`` followed by ``qk_norm_rope_write`` does, in one launch."""
     rows = x.shape[0]
@@ -707,4 +709,4 @@ def gemm_fused_qkv(x, w: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tenso
     _fused(x, w, splits, _EPI_QKV, q_out=q_out, k_cache=k_cache if write_kv else None, v_cache=v_cache if write_kv else None,
            token_seq=token_seq, token_pos=token_pos, block_table=block_table if write_kv else None, q_w=q_weight, k_w=k_weight,
            qk_eps=eps, cos_sin=cos_sin, nq=num_heads, nkv=num_kv_heads, d=head_dim, page_tokens=page_tokens,
-           ring_tokens=ring_tokens, write_kv=write_kv, stages=stages)
+           ring_tokens=ring_tokens, write_kv=write_kv, stages=stages, interleaved=interleaved)

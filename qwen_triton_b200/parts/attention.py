@@ -45,6 +45,7 @@ class Attention:
             raise ValueError(f"{prefix}: head_dim={self.d} is beyond what the attention kernels take (256)")
         position_spec = params["position"]
         self.position = part_class("position", position_spec)(position_spec.params, runtime)
+        self.interleaved = bool(getattr(self.position, "interleaved", False))      # which elements of a head form a rotation pair
         self.cos_sin: torch.Tensor | None = None
         self.q_weight = self.k_weight = None
         proj_rows = (self.nq + (2 * self.nkv if self.own_kv else 0)) * self.d
@@ -143,12 +144,12 @@ class Attention:
             # few tokens: per-head norm, rotation and the cache write in the projection's epilogue
             self.qkv.into_qkv(x, q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
                               table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv,
-                              self.d, cache.page_tokens, cache.ring_tokens, write_kv=write)
+                              self.d, cache.page_tokens, cache.ring_tokens, write_kv=write, interleaved=self.interleaved)
         else:
             kernels.qk_norm_rope_write(
                 self.qkv(x), q, cache.k if write else None, cache.v if write else None, ctx.token_seq, ctx.token_pos,
                 table if write else None, self.q_weight, self.k_weight, self.eps, self.cos_sin, self.nq, self.nkv, self.d,
-                cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv)
+                cache.page_tokens, cache.ring_tokens, write_kv=write, kv_in_proj=self.own_kv, interleaved=self.interleaved)
         if ctx.is_decode:
             n_splits, warps = self._splits(ctx, cache)
             kernels.attention_decode(q, cache.k, cache.v, out, table, ctx.seq_len, self.nkv, cache.page_tokens,

@@ -12,7 +12,9 @@ Interfaces (what a new part must offer):
   ``offers_scaled_rows`` also takes ``lazy=True`` and may then hand on ``ScaledRows`` (the rows times its
   weight, the rows' factor left to the consumer's product) to a consumer that sets ``takes_scaled_rows``.
 * position:    ``__init__(params, runtime)``, ``table(max_positions) -> float32 [P, rotary_dim]`` (cos | sin) or ``None``
-  for no encoding, and ``key() -> tuple`` that names the table's content (equal keys share one table).
+  for no encoding, and ``key() -> tuple`` that names the table's content (equal keys share one table).  Column i
+  and rotary_dim / 2 + i of a row are the cos and sin of the angle of rotation pair i; the pair is elements
+  (i, i + rotary_dim / 2) of a head, or (2i, 2i + 1) if the part has ``interleaved = True``.
 * mixer:       ``cache_request() -> KVRequest | StateRequest | None`` and
   ``forward(x, ctx, cache) -> GemmOut`` where ``cache`` is the view of the cache entry this call
   uses (``cache.writable`` tells whether it owns it).

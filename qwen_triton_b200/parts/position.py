@@ -16,12 +16,18 @@ class RotaryTable:
     def __init__(self, params, runtime: Runtime) -> None:
         self.theta = float(params["theta"])
         self.rotary_dim = int(params["rotary_dim"])
+        # which elements turn together: (i, i + rotary_dim / 2) as in the reference (kernels/rope.py:59-69), or
+        # neighbours (2i, 2i + 1) with pairing = "interleaved"
+        pairing = params.get("pairing", "half")
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"rotary pairing {pairing!r} is neither 'half' nor 'interleaved'")
+        self.interleaved = pairing == "interleaved"
         if self.rotary_dim % 2 or self.rotary_dim <= 0 or self.rotary_dim > int(params["head_dim"]):
             raise ValueError(f"rotary_dim={self.rotary_dim} must be even and within head_dim={params['head_dim']}")
         self.runtime = runtime
 
     def key(self) -> tuple:
-        return ("rope", self.theta, self.rotary_dim)
+        return ("rope", self.theta, self.rotary_dim)          # the table does not depend on the pairing
 
     def table(self, max_positions: int) -> torch.Tensor:
         """float32 [max_positions, rotary_dim]: cos in the first half of each row, sin in the second."""

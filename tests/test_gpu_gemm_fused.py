@@ -7,7 +7,7 @@ import torch
 import plain_qwen3 as plain
 from qwen_triton_b200.ops import kernels
 from qwen_triton_b200.ops.kernels import ScaledRows
-from test_gpu_kernels import DEV, PAGE, close, gate_act, paged, rand
+from test_gpu_kernels import DEV, PAGE, close, gate_act, paged, rand, rope_interleaved
 
 pytestmark = pytest.mark.gpu
 BF16 = torch.bfloat16
@@ -90,7 +90,8 @@ def test_silu_gate(rows, inter, k, splits):
 @pytest.mark.parametrize("nq, nkv, d, rotary, ring, splits, lengths, own_kv", [
     (8, 2, 16, 16, 128, 2, [1, 1, 1], True), (5, 1, 128, 128, 0, 4, [1, 1, 1], True), (3, 3, 64, 32, 0, 1, [20, 3, 41], True),
     (6, 2, 32, 24, 0, 8, [1, 1, 1], True), (4, 2, 128, 0, 0, 2, [1, 1, 1], True), (7, 1, 64, 64, 0, 3, [1, 1, 1], False)])
-def test_qkv_with_norm_rotation_and_cache_write(nq, nkv, d, rotary, ring, splits, lengths, own_kv):
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_qkv_with_norm_rotation_and_cache_write(nq, nkv, d, rotary, ring, splits, lengths, own_kv, interleaved):
     past = [130, 0, 20]
     tokens, k, eps = sum(lengths), 512, 1e-5
     n = (nq + (2 * nkv if own_kv else 0)) * d
@@ -109,14 +110,16 @@ def test_qkv_with_norm_rotation_and_cache_write(nq, nkv, d, rotary, ring, splits
     k_cache, v_cache, table = paged(zeros, zeros, totals, BF16, ring_tokens=ring, seed=16, garbage=False)
     q_out = torch.full((tokens, nq, d), float("nan"), dtype=BF16, device=DEV)
     kernels.gemm_fused_qkv(handed, w, q_out, k_cache, v_cache, token_seq, token_pos, table, qw, kw, eps, cos_sin, nq, nkv, d,
-                           PAGE, ring, write_kv=own_kv, splits=splits)
+                           PAGE, ring, write_kv=own_kv, splits=splits, interleaved=interleaved)
     kernels.check_status(DEV)
     x = (product(handed.tensor, w) * factor).view(tokens, -1, d)
     pos = token_pos.cpu().long()
 
     def rotated(heads, weight):
         normed = plain.rms_norm(heads, weight.cpu(), eps)
-        return plain.apply_rope(normed, cos[pos], sin[pos]) if rotary else normed
+        if not rotary:
+            return normed
+        return rope_interleaved(normed, cos[pos], sin[pos]) if interleaved else plain.apply_rope(normed, cos[pos], sin[pos])
 
     close(q_out, rotated(x[:, :nq], qw), BF16, "q")
     if not own_kv:

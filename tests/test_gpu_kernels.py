@@ -32,6 +32,15 @@ def gate_act(name, g):
             "gelu_tanh": lambda x: torch.nn.functional.gelu(x, approximate="tanh"), "relu": torch.relu}[name](g)
 
 
+def rope_interleaved(x, cos, sin):
+    """Rotation with neighbours as pairs: (x[2i], x[2i+1]) turns by angle i; dims beyond 2 * cos.shape[-1] pass."""
+    rd = 2 * cos.shape[-1]
+    even, odd = x[..., 0:rd:2], x[..., 1:rd:2]
+    c, s = cos[:, None, :], sin[:, None, :]
+    turned = torch.stack((even * c - odd * s, odd * c + even * s), dim=-1).flatten(-2)
+    return torch.cat((turned, x[..., rd:]), dim=-1)
+
+
 def close(actual, expected, dtype, what=""):
     torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), **TOL[dtype], msg=lambda m: f"{what}: {m}")
 
@@ -119,8 +128,10 @@ def test_add_rmsnorm(dtype, hidden, splits, rows):
     # 256 tokens and more with every dimension rotating: the kernel that keeps rotation pairs in registers
     (5, 2, 128, 128, 0, 1, [200, 3, 150]), (3, 1, 64, 64, 0, 2, [200, 3, 150]), (2, 2, 256, 256, 512, 1, [200, 3, 150]),
     (7, 7, 128, 128, 0, 3, [190, 1, 99])])
-def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits, lengths):
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits, lengths, interleaved):
     import plain_qwen3 as plain
+    rope = rope_interleaved if interleaved else plain.apply_rope
     past = [130, 0, 20]                                  # tokens before this step, per sequence; `lengths` are this step's
     tokens = sum(lengths)
     eps = 1e-5
@@ -137,11 +148,11 @@ def test_qk_norm_rope_write(dtype, nq, nkv, d, rotary, ring, splits, lengths):
     k_cache, v_cache, table = paged(zeros, zeros, totals, dtype, ring_tokens=ring, seed=8, garbage=False)
     q_out = torch.empty(tokens, nq, d, dtype=dtype, device=DEV)
     kernels.qk_norm_rope_write(GemmOut(qkv), q_out, k_cache, v_cache, token_seq, token_pos, table, qw, kw, eps, cos_sin,
-                               nq, nkv, d, PAGE, ring)
+                               nq, nkv, d, PAGE, ring, interleaved=interleaved)
     x = qkv.float().sum(0).cpu().view(tokens, nq + 2 * nkv, d)
     pos = token_pos.cpu().long()
-    q_ref = plain.apply_rope(plain.rms_norm(x[:, :nq], qw.cpu(), eps), cos[pos], sin[pos])
-    k_ref = plain.apply_rope(plain.rms_norm(x[:, nq:nq + nkv], kw.cpu(), eps), cos[pos], sin[pos])
+    q_ref = rope(plain.rms_norm(x[:, :nq], qw.cpu(), eps), cos[pos], sin[pos])
+    k_ref = rope(plain.rms_norm(x[:, nq:nq + nkv], kw.cpu(), eps), cos[pos], sin[pos])
     v_ref = x[:, nq + nkv:]
     close(q_out, q_ref, dtype, "q")
     table_host, k_host, v_host = table.cpu(), k_cache.float().cpu(), v_cache.float().cpu()
