@@ -58,9 +58,10 @@ class GatedMLP:
         act = self.runtime.workspace.view("mlp.act", tokens, self.inter)
         if self.takes_scaled_rows and self.gate_up.fusable(tokens):
             self.gate_up.into_swiglu(x, act, self.activation)
-            return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
-        if self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
+        elif self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
             kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
         else:
             kernels.swiglu(self.gate_up(x), act, self.group, self.activation)
-        return self.down(act)
+        # few tokens: the down projection is left to the norm behind it, which launches it with the residual addition
+        # (and its own preparation) in the product's epilogue
+        return DeferredProduct(self.down, act) if self.down.fusable(tokens) else self.down(act)
