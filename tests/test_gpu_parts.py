@@ -115,6 +115,38 @@ def test_attention_part(dtype, window):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("head_dim, lengths", [(48, [40, 7]), (32, [9, 4]), (32, [200, 90])])
+def test_attention_part_with_neighbours_as_rotation_pairs(dtype, head_dim, lengths):
+    """``pairing: interleaved`` on the position part: elements (2i, 2i + 1) of a head turn together.  Head size 32 with
+    13 tokens takes the fused projection (in bfloat16), the other cases the separate kernel."""
+    from test_gpu_kernels import rope_interleaved
+    rt = runtime(dtype, max_tokens=512)
+    position = PartSpec("rope", {"theta": 7e4, "rotary_dim": head_dim, "head_dim": head_dim, "pairing": "interleaved"})
+    params = {**ATTN, "head_dim": head_dim, "position": position, "window": None}
+    mixer = part_class("mixer", PartSpec("attention"))(params, "a", rt)
+    assert mixer.interleaved
+    w = weights_for(mixer.expected_tensors(params, "a"), dtype, seed=13)
+    mixer.load(w.__getitem__)
+    rt.workspace.allocate()
+    cache = SequenceCache([mixer.cache_request()], [None], max_tokens=1024, max_seq_len=512, dtype=DTYPES[dtype], device=DEV)
+    ctx, _ = context(rt, cache, lengths)
+    x = (torch.randn(sum(lengths), 72, generator=torch.Generator().manual_seed(4)) * 0.5).to(DTYPES[dtype])
+    out = mixer.forward(x.to(DEV), ctx, cache.view(0)).value()
+    wf = {k: v.float() for k, v in w.items()}
+    nq, nkv, start = ATTN["num_heads"], ATTN["num_kv_heads"], 0
+    for n in lengths:
+        h = x[start:start + n].float()
+        q = plain.rms_norm((h @ wf["a.q_proj.weight"].T).view(n, nq, head_dim), wf["a.q_norm.weight"], 1e-5)
+        k = plain.rms_norm((h @ wf["a.k_proj.weight"].T).view(n, nkv, head_dim), wf["a.k_norm.weight"], 1e-5)
+        v = (h @ wf["a.v_proj.weight"].T).view(n, nkv, head_dim)
+        cos, sin = plain.rope_tables(torch.arange(n), head_dim, 7e4, torch.float32)
+        q, k = rope_interleaved(q, cos, sin), rope_interleaved(k, cos, sin)
+        want = plain.attention_scores(q, k, v, head_dim ** -0.5, None).reshape(n, nq * head_dim) @ wf["a.o_proj.weight"].T
+        assert_close(out[start:start + n], want, dtype, "attention part, neighbours as pairs")
+        start += n
+
+
+@pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("inter, tokens", [(200, 11), (208, 11), (208, 300)])    # 208: gate and up interleaved in bfloat16; 300 tokens: gated in the GEMM
 def test_feed_forward_part(dtype, inter, tokens):
     rt = runtime(dtype, max_tokens=512)
