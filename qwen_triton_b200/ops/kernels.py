@@ -53,7 +53,9 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
-        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr,
+                            _c_ptr, _c_int, _c_ptr, _c_ptr],
+        "qt_gemm_tc_pair_slots": [],
     },
     "gemm_fused": {
         "qt_gemm_fused": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -487,8 +489,12 @@ def check_status(device: torch.device | str = "cuda") -> None:
     code = int(word[0].item())
     if code != 0:
         word.zero_()
+        tail = _PAIR_TAIL.get(word.device.index)
+        if tail is not None:
+            tail[1].zero_()                    # flags of the pair kernel's last wave that the failed launch left up
         role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer (for a free accumulator)",
-                5: "a kernel whose shared memory was less aligned than its launch allowed for"}.get(code, f"role {code}")
+                5: "a kernel whose shared memory was less aligned than its launch allowed for",
+                6: "a pair that finishes a tile (for another pair's sums)"}.get(code, f"role {code}")
         raise KernelError(f"gemm_tc: a wait of {role} ran out; the result of that launch is invalid")
 
 
@@ -531,7 +537,32 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
           out.n_splits, out.split_stride, int(stages), _ptr(_status_word(a.device)), _stream())
 
 
-def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False, activation: str = "silu") -> None:
+_PAIR_TAIL: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = {}
+
+
+def _pair_tail(device: torch.device) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """Scratch of the pair kernel's last wave (one accumulator tile per resident pair, and the flags that guard the
+    slots), made once per device: (slots, flags, pairs)."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _PAIR_TAIL:
+        pairs = max(1, sm_count(device) // 2)  # one resident pair per TPC at most
+        floats = _fn("gemm_tc", "qt_gemm_tc_pair_slots")()
+        _PAIR_TAIL[index] = (torch.empty(pairs * floats, dtype=torch.float32, device=device),
+                             torch.zeros(pairs * 8, dtype=torch.int32, device=device), pairs)
+    return _PAIR_TAIL[index]
+
+
+def pair_tail_mode() -> int:
+    """``QT_B200_PAIR_TAIL``: 0 or unset = every tile of the pair kernel by one pair; -1 = the last wave by K ranges
+    where the kernel's model of the time saved says it pays; 1 = wherever the tiles do not divide by the pairs.
+    Off by default: launched alone at full clocks the cut saves up to a quarter of a product with a long K and a
+    half-empty last wave, but a whole prefill runs at the power limit, where idle pairs in a last wave leave their
+    power to the others, and measured the same or slower with it."""
+    return int(os.environ.get("QT_B200_PAIR_TAIL", "0"))
+
+
+def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = False, activation: str = "silu",
+                 tail: int | None = None) -> None:
     """The same product by pairs of blocks on the two SMs of a TPC (tcgen05 cta_group::2): 256 weight rows x
     256 tokens per tile, each block staging half of both operands; one persistent pair per TPC with two
     accumulators in tensor memory.  Meant for many tokens; ``out`` may be [splits, M, N] float partial sums, which
@@ -549,8 +580,11 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: GemmOut, swiglu: bool = 
         return
     if not out.tensor.is_cuda or out.tensor.dtype not in _CODES:
         raise KernelError("gemm_tc_pair: the output must be a bfloat16 or float32 CUDA tensor")
+    tail = pair_tail_mode() if tail is None else int(tail)
+    slots, flags, pairs = _pair_tail(a.device) if tail != 0 and out.n_splits == 1 else (None, None, 0)
     _call("gemm_tc", "qt_gemm_tc_pair", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k,
           1 if swiglu else 0, activation_code(activation) if swiglu else 0, out.n_splits, out.split_stride,
+          tail, _ptr(slots) if slots is not None else None, _ptr(flags) if flags is not None else None, pairs,
           _ptr(_status_word(a.device)), _stream())
 
 

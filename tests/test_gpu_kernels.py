@@ -463,6 +463,41 @@ def test_gemm_block_pairs_with_the_silu_gate_in_the_epilogue(m, inter, k):
         kernels.gemm_tc_pair(a, w[:-8], GemmOut(out[:, :, :-4].contiguous()), swiglu=True)
 
 
+@pytest.mark.parametrize("m, n, k, out_dtype, swiglu", [
+    (300, 384, 2048, torch.bfloat16, False),       # 4 tiles over all pairs: a tile finished from many pairs' slots
+    (2048, 4096, 4096, torch.bfloat16, False),     # 128 tiles: one whole wave, then 54 tiles by K ranges
+    (1000, 1100, 4096, torch.float32, False),      # ragged edges in both directions
+    (777, 5000, 1024, torch.bfloat16, False),      # 80 tiles: six of them over all pairs, a K block or two each
+    (2048, 3072, 256, torch.bfloat16, True),       # the gated epilogue after the sums
+    (4096, 24576, 448, torch.bfloat16, False)])    # many waves before the last
+def test_gemm_block_pairs_last_wave_by_k_ranges(m, n, k, out_dtype, swiglu):
+    """The pair kernel with the tiles of its last wave cut by K ranges (forced wherever the tiles do not divide by the
+    pairs): pairs that do not finish a tile leave float sums in their slot, the finishing pair adds them.  Run
+    twice: the flags that guard the slots must be down again after every launch."""
+    a, w = rand(m, k, seed=121, dtype=torch.bfloat16), rand(n, k, seed=122, scale=0.1, dtype=torch.bfloat16)
+    full = a.double() @ w.double().T
+    if swiglu:
+        gate, up = w[: n // 2], w[n // 2:]
+        expected = torch.nn.functional.silu(a.double() @ gate.double().T) * (a.double() @ up.double().T)
+        w = kernels.interleave_gate_up(gate, up, kernels.SWIGLU_GROUP).contiguous()
+    else:
+        expected = full
+    slots, flags, pairs = kernels._pair_tail(a.device)
+    tiles = -(-m // 256) * -(-n // 256)
+    assert tiles % (kernels.sm_count(a.device) // 2) != 0, "this shape has no partly filled wave on this device"
+    for attempt in range(2):
+        slots.fill_(float("nan"))
+        out = torch.full((1, m, expected.shape[1]), float("nan"), dtype=out_dtype, device=DEV)
+        kernels.gemm_tc_pair(a, w, GemmOut(out), swiglu=swiglu, tail=1)
+        kernels.check_status(DEV)
+        close(out[0], expected, out_dtype, f"{m}x{n}x{k} attempt {attempt}")
+        assert int(flags.abs().sum()) == 0
+        assert not bool(torch.isnan(slots).all()), "no pair wrote a slot: the last wave was not cut"
+    out = torch.full((1, m, expected.shape[1]), float("nan"), dtype=out_dtype, device=DEV)
+    kernels.gemm_tc_pair(a, w, GemmOut(out), swiglu=swiglu, tail=0)       # and the same product with every tile whole
+    close(out[0], expected, out_dtype, "whole tiles")
+
+
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
 def test_gemm_tensor_cores_every_token_tile(tile):
     m, n, k = 70, 384, 448
