@@ -178,8 +178,6 @@ class Qwen3Config:
             problems.append(f"head_dim={self.head_dim} must be even for rotate-half position encoding")
         if self.hidden_act != "silu":
             problems.append(f"hidden_act={self.hidden_act!r}: the feed-forward of this architecture is SiLU-gated")
-        if self.attention_bias:
-            problems.append("attention_bias=true is not built (Qwen3 dense checkpoints have no attention bias)")
         if not (0.0 < self.partial_rotary_factor <= 1.0):
             problems.append(f"partial_rotary_factor={self.partial_rotary_factor} must lie in (0, 1]")
         if self.rms_norm_eps <= 0.0 or self.rope_theta <= 0.0:
@@ -254,6 +252,7 @@ class Qwen3Config:
                 "window": self.sliding_window if kind == SLIDING_ATTENTION else None,
                 "qk_norm": True,
                 "qk_norm_eps": self.rms_norm_eps,
+                "bias": self.attention_bias,
                 "position": position,
                 "q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj",
                 "q_norm": "q_norm", "k_norm": "k_norm",

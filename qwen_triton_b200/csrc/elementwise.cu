@@ -35,6 +35,27 @@ extern "C" int qt_embedding(float* residual, const void* table, const int* ids, 
     });
 }
 
+// ----------------------------------------------------------------------------- bias of a projection
+// out[t, :] += bias, on the float sums of a product before anything rounds them (the first plane, where a product is
+// split over K).  luozoupi/Qwen-Triton adds the bias of a linear layer with a kernel of its own as well
+// (kernels/matmul.py:99-111, modules/linear.py:31).
+__global__ void add_bias_kernel(float* __restrict__ out, const float* __restrict__ bias, int cols, size_t count) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        out[i] += bias[i % (size_t)cols];
+}
+
+extern "C" int qt_add_bias(float* out, const float* bias, int rows, int cols, void* stream) {
+    QT_REQUIRE(rows >= 0 && cols > 0, "add_bias: bad sizes rows=%d cols=%d", rows, cols);
+    if (rows == 0) return QT_OK;
+    const size_t count = (size_t)rows * cols;
+    const size_t blocks = (count + 255) / 256;
+    launch_kernel(add_bias_kernel, dim3((unsigned)(blocks < 4096 ? blocks : 4096)), dim3(256), 0, (cudaStream_t)stream, out, bias, cols, count);
+    QT_CHECK_LAUNCH("add_bias");
+    return QT_OK;
+}
+
 // ----------------------------------------------------------------------------- residual add + RMSNorm
 // One block per output row r.  src = rows ? rows[r] : r.
 //   x = residual[src] + sum_s delta[s][src]            (float)

@@ -23,6 +23,7 @@ _c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_floa
 _SIGNATURES = {
     "elementwise": {
         "qt_embedding": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+        "qt_add_bias": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_add_rmsnorm": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_float, _c_ptr, _c_int, _c_ptr, _c_int,
                            _c_int, _c_ptr],
         "qt_qk_norm_rope_write": [_c_ptr, _c_int, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
@@ -192,6 +193,15 @@ def embedding(residual: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) ->
         raise KernelError(f"embedding: table width {table.shape[1]} != stream width {hidden}")
     _call("elementwise", "qt_embedding", _ptr(residual), _ptr(table), _ptr(ids), tokens, hidden, table.shape[0],
           _code(table, "table"), _stream())
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """out [T, N] float32 += bias [N] float32, in place: the bias of a projection on its float sums."""
+    _need(out, "out", torch.float32)
+    _need(bias, "bias", torch.float32, (out.shape[-1],))
+    if out.dim() != 2:
+        raise KernelError(f"add_bias: out must be [rows, cols], got {tuple(out.shape)}")
+    _call("elementwise", "qt_add_bias", _ptr(out), _ptr(bias), out.shape[0], out.shape[1], _stream())
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: GemmOut | None, weight: torch.Tensor, eps: float,

@@ -37,6 +37,7 @@ class Attention:
         self.window = params.get("window")
         self.own_kv = bool(params.get("own_kv", True))
         self.qk_norm = bool(params.get("qk_norm", False))
+        self.bias = bool(params.get("bias", False))        # q, k, v and o projections with a bias (attention.py:38-41)
         self.eps = float(params.get("qk_norm_eps", 1e-6))
         self.names = {k: params.get(k, k) for k in ("q", "k", "v", "o", "q_norm", "k_norm")}
         if self.nq % self.nkv:
@@ -49,8 +50,8 @@ class Attention:
         self.cos_sin: torch.Tensor | None = None
         self.q_weight = self.k_weight = None
         proj_rows = (self.nq + (2 * self.nkv if self.own_kv else 0)) * self.d
-        self.qkv = Linear("attn.qkv", proj_rows, self.hidden, runtime, role="qkv")
-        self.o = Linear("attn.o", self.hidden, self.nq * self.d, runtime, role="attn_out")
+        self.qkv = Linear("attn.qkv" + (".biased" if self.bias else ""), proj_rows, self.hidden, runtime, role="qkv", bias=self.bias)
+        self.o = Linear("attn.o" + (".biased" if self.bias else ""), self.hidden, self.nq * self.d, runtime, role="attn_out", bias=self.bias)
         ws = runtime.workspace
         ws.declare("attn.q", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
         ws.declare("attn.ctx", runtime.max_step_tokens * self.nq * self.d, runtime.dtype)
@@ -70,6 +71,11 @@ class Attention:
         if own_kv:
             out[f"{prefix}.{n['k']}.weight"] = TensorSpec((nkv * d, hidden))
             out[f"{prefix}.{n['v']}.weight"] = TensorSpec((nkv * d, hidden))
+        if params.get("bias", False):
+            # the reference starts a bias at zero (models/core.py:269-270); random ones so that a bias that is skipped shows
+            for name in ("q", "o") + (("k", "v") if own_kv else ()):
+                rows = out[f"{prefix}.{n[name]}.weight"].shape[0]
+                out[f"{prefix}.{n[name]}.bias"] = TensorSpec((rows,), role="vector", init_std=0.1, init_mean=0.0)
         if params.get("qk_norm", False):
             out[f"{prefix}.{n['q_norm']}.weight"] = TensorSpec((d,), role="vector", init_std=0.1, init_mean=1.0)
             if own_kv:
@@ -83,6 +89,10 @@ class Attention:
             rows += [source(f"{p}.{n['k']}.weight"), source(f"{p}.{n['v']}.weight")]
         self.qkv.set_weight(torch.cat([r.to(self.runtime.dtype) for r in rows], dim=0))
         self.o.set_weight(source(f"{p}.{n['o']}.weight"))
+        if self.bias:
+            names = ("q", "k", "v") if self.own_kv else ("q",)
+            self.qkv.set_bias(torch.cat([source(f"{p}.{n[name]}.bias").float() for name in names], dim=0))
+            self.o.set_bias(source(f"{p}.{n['o']}.bias"))
         if self.qk_norm:
             self.q_weight = to_device(source(f"{p}.{n['q_norm']}.weight"), torch.float32, self.runtime.device)
             if self.own_kv:

@@ -84,14 +84,19 @@ def pick_pair_splits(out_features: int, in_features: int, rows: int, pairs: int)
 
 class Linear:
     def __init__(self, key: str, out_features: int, in_features: int, runtime: Runtime, max_rows: int | None = None,
-                 float_out: bool = False, role: str = "") -> None:
+                 float_out: bool = False, role: str = "", bias: bool = False) -> None:
         self.key = key
         self.role = role                   # which of the fused products of a decode step this one is, if any
         self.out_features = out_features
         self.in_features = in_features
         self.runtime = runtime
+        # a bias is added to the float sums (the first plane of a product split over K), so such a product stays float
+        # up to its consumer, and it keeps to the plain kernels: the fused products have no bias operand
+        self.has_bias = bias
+        float_out = float_out or bias
         self.float_out = float_out
         self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
         self.max_rows = runtime.max_step_tokens if max_rows is None else max_rows
         self.out_dtype = torch.float32 if float_out else runtime.dtype
         runtime.workspace.declare(f"{key}.out", self.max_rows * out_features, self.out_dtype)
@@ -124,11 +129,17 @@ class Linear:
             raise ValueError(f"{self.key}: weight {tuple(weight.shape)} is not [{self.out_features}, {self.in_features}]")
         self.weight = weight.to(device=self.runtime.device, dtype=self.runtime.dtype).contiguous()
 
+    def set_bias(self, bias: torch.Tensor) -> None:
+        if not self.has_bias or tuple(bias.shape) != (self.out_features,):
+            raise ValueError(f"{self.key}: bias {tuple(bias.shape)} for a projection "
+                             f"{'of ' + str(self.out_features) + ' features' if self.has_bias else 'built without bias'}")
+        self.bias = bias.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+
     # ------------------------------------------------------------------ the fused product of a decode step
     @property
     def fused_capable(self) -> bool:
         """Whether this product has a fused form at all (known before the weight is loaded)."""
-        return bool(self.fused_plans) and bool(self.role) and kernels.fused_enabled(self.role)
+        return bool(self.fused_plans) and bool(self.role) and kernels.fused_enabled(self.role) and not self.has_bias
 
     def fusable(self, rows: int) -> bool:
         """Whether ``rows`` tokens take the fused product (a static choice: element type, sizes, row count), in which
@@ -169,14 +180,14 @@ class Linear:
             return GemmOut(out.view(1, rows, self.out_features))
         splits = next((n for most, n in self.split_plans if rows <= most), 1)
         if out is None and splits > 1:
-            partial = self.runtime.workspace.view(f"{self.key}.partial", splits, rows, self.out_features)
-            result = GemmOut(partial)
-            kernels.gemm(x, self.weight, result)
-            return result
-        if out is None:
-            out = self.runtime.workspace.view(f"{self.key}.out", 1, rows, self.out_features)
+            result = GemmOut(self.runtime.workspace.view(f"{self.key}.partial", splits, rows, self.out_features))
+        elif out is None:
+            result = GemmOut(self.runtime.workspace.view(f"{self.key}.out", 1, rows, self.out_features))
         else:
-            out = out.view(1, rows, self.out_features)
-        result = GemmOut(out)
+            result = GemmOut(out.view(1, rows, self.out_features))
         kernels.gemm(x, self.weight, result)
+        if self.has_bias and rows:
+            if self.bias is None:
+                raise ValueError(f"{self.key}: the bias was not loaded")
+            kernels.add_bias(result.tensor[0], self.bias)
         return result

@@ -40,9 +40,13 @@ CONFIGS = {
                      rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False,
                      max_position_embeddings=128, use_sliding_window=True, sliding_window=5,
                      max_window_layers=2),
+    "golden_d": dict(model_type="qwen3", vocab_size=199, hidden_size=72, intermediate_size=88,
+                     num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3, head_dim=32,
+                     rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=True,
+                     max_position_embeddings=128, attention_bias=True),
 }
-PROMPT_LENGTHS = {"golden_a": 17, "golden_b": 31, "golden_c": 23}
-SEEDS = {"golden_a": 0, "golden_b": 1, "golden_c": 2}
+PROMPT_LENGTHS = {"golden_a": 17, "golden_b": 31, "golden_c": 23, "golden_d": 19}
+SEEDS = {"golden_a": 0, "golden_b": 1, "golden_c": 2, "golden_d": 3}
 GREEDY_PROMPT = 6
 GREEDY_NEW = 5
 
@@ -57,6 +61,8 @@ def tensor_names(raw: dict) -> list[str]:
                   f"{p}.self_attn.q_proj.weight", f"{p}.self_attn.k_proj.weight", f"{p}.self_attn.v_proj.weight",
                   f"{p}.self_attn.o_proj.weight", f"{p}.self_attn.q_norm.weight", f"{p}.self_attn.k_norm.weight",
                   f"{p}.mlp.gate_proj.weight", f"{p}.mlp.up_proj.weight", f"{p}.mlp.down_proj.weight"]
+        if raw.get("attention_bias"):
+            names += [f"{p}.self_attn.{proj}.bias" for proj in ("q_proj", "k_proj", "v_proj", "o_proj")]
     return sorted(names)
 
 
@@ -64,6 +70,8 @@ def tensor_shape(raw: dict, name: str) -> tuple[int, ...]:
     h, d = raw["hidden_size"], raw["head_dim"]
     nq, nkv, inter, vocab = raw["num_attention_heads"], raw["num_key_value_heads"], raw["intermediate_size"], raw["vocab_size"]
     leaf = name.split(".")[-2]
+    if name.endswith(".bias"):
+        return {"q_proj": (nq * d,), "k_proj": (nkv * d,), "v_proj": (nkv * d,), "o_proj": (h,)}[leaf]
     return {
         "embed_tokens": (vocab, h), "lm_head": (vocab, h), "norm": (h,),
         "input_layernorm": (h,), "post_attention_layernorm": (h,),
@@ -74,13 +82,13 @@ def tensor_shape(raw: dict, name: str) -> tuple[int, ...]:
 
 
 def golden_weights(raw: dict, seed: int) -> dict[str, torch.Tensor]:
-    """Matrices N(0, 0.05), norm weights 1 + N(0, 0.2); one generator per tensor."""
+    """Matrices N(0, 0.05), norm weights 1 + N(0, 0.2), biases N(0, 0.2); one generator per tensor."""
     out = {}
     for index, name in enumerate(tensor_names(raw)):
         generator = torch.Generator().manual_seed(seed * 1000 + index)
         shape = tensor_shape(raw, name)
         values = torch.randn(shape, generator=generator, dtype=torch.float32)
-        out[name] = 1.0 + 0.2 * values if len(shape) == 1 else 0.05 * values
+        out[name] = 0.2 * values if name.endswith(".bias") else 1.0 + 0.2 * values if len(shape) == 1 else 0.05 * values
     return out
 
 

@@ -15,8 +15,8 @@ from qwen_triton_b200.weights import Checkpoint
 # bfloat16: its bar for bfloat16 kernels (tests/test_kernels.py:150).
 TOL = {"fp32": dict(atol=1e-5, rtol=1e-4), "bf16": dict(atol=2e-2, rtol=2e-2)}
 STORE = {"fp32": torch.float32, "bf16": torch.bfloat16}
-PRESETS = ("tiny-a", "tiny-b", "tiny-c")
-SEEDS = {"tiny-a": 0, "tiny-b": 1, "tiny-c": 2}
+PRESETS = ("tiny-a", "tiny-b", "tiny-c", "tiny-d")      # tiny-d: biased attention projections, head size 64
+SEEDS = {"tiny-a": 0, "tiny-b": 1, "tiny-c": 2, "tiny-d": 3}
 _KEEP: list = []
 
 

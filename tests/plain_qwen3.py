@@ -50,6 +50,7 @@ def read_config(raw: Mapping) -> dict:
         "theta": theta, "rotary_dim": rotary_dim,
         "tied": bool(raw.get("tie_word_embeddings", text.get("tie_word_embeddings", False))),   # config.py:165
         "window": int(window) if window is not None else None, "layer_types": list(layer_types),
+        "attention_bias": bool(text.get("attention_bias", False)),              # config.py:150-151
     }
 
 
@@ -121,18 +122,24 @@ def attention_scores(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
 def attention_layer(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str, cfg: dict,
                     window: int | None) -> torch.Tensor:
     """q/k/v projections, per-head q_norm/k_norm before RoPE, attention, output projection
-    (qwen_triton/modules/attention.py:53-73,125-128)."""
+    (qwen_triton/modules/attention.py:53-73,125-128); with ``attention_bias`` all four projections have a bias
+    (attention.py:38-41), added to the product after it was rounded (modules/linear.py:31, kernels/matmul.py:99-111)."""
     seq = x.shape[0]
     d = cfg["head_dim"]
-    q = (x @ w[f"{prefix}.q_proj.weight"].T).view(seq, cfg["heads"], d)
-    k = (x @ w[f"{prefix}.k_proj.weight"].T).view(seq, cfg["kv_heads"], d)
-    v = (x @ w[f"{prefix}.v_proj.weight"].T).view(seq, cfg["kv_heads"], d)
+
+    def project(name: str, rows: torch.Tensor) -> torch.Tensor:
+        out = rows @ w[f"{prefix}.{name}.weight"].T
+        return out + w[f"{prefix}.{name}.bias"] if cfg["attention_bias"] else out
+
+    q = project("q_proj", x).view(seq, cfg["heads"], d)
+    k = project("k_proj", x).view(seq, cfg["kv_heads"], d)
+    v = project("v_proj", x).view(seq, cfg["kv_heads"], d)
     q = rms_norm(q, w[f"{prefix}.q_norm.weight"], cfg["eps"])
     k = rms_norm(k, w[f"{prefix}.k_norm.weight"], cfg["eps"])
     cos, sin = rope_tables(torch.arange(seq, device=x.device), cfg["rotary_dim"], cfg["theta"], x.dtype)
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     out = attention_scores(q, k, v, d ** -0.5, window)
-    return out.reshape(seq, cfg["heads"] * d) @ w[f"{prefix}.o_proj.weight"].T
+    return project("o_proj", out.reshape(seq, cfg["heads"] * d))
 
 
 def gated_mlp(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str) -> torch.Tensor:

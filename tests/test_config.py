@@ -56,7 +56,6 @@ def test_sliding_window_layers_from_max_window_layers():
     ({"model_type": "qwen3_moe"}, "model_type"),
     ({"num_key_value_heads": 3}, "multiple"),
     ({"hidden_act": "gelu"}, "SiLU"),
-    ({"attention_bias": True}, "attention_bias"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope scaling"),
     ({"head_dim": 15}, "even"),
     ({"layer_types": ["full_attention", "linear_attention", "full_attention"]}, "linear_attention"),
@@ -88,11 +87,12 @@ def test_round_trip_through_config_json(tmp_path):
 
 
 def test_presets_differ_in_every_size_and_option():
-    a, b, c = (load_preset(n) for n in ("tiny-a", "tiny-b", "tiny-c"))
+    a, b, c, d = (load_preset(n) for n in ("tiny-a", "tiny-b", "tiny-c", "tiny-d"))
     for field in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
                   "num_key_value_heads", "head_dim", "rope_theta", "rms_norm_eps"):
-        assert len({getattr(a, field), getattr(b, field), getattr(c, field)}) == 3, field
+        assert len({getattr(a, field), getattr(b, field), getattr(c, field), getattr(d, field)}) == 4, field
     assert a.tie_word_embeddings and not b.tie_word_embeddings
+    assert d.attention_bias and not (a.attention_bias or b.attention_bias or c.attention_bias)
     assert b.q_size != b.hidden_size and c.use_sliding_window and not a.use_sliding_window
     assert {"qwen3-0.6b", "qwen3-8b", "qwen3-32b"} <= set(preset_names())
     big = load_preset("qwen3-8b")
@@ -109,3 +109,14 @@ def test_schedule_is_data_and_is_checked():
         with pytest.raises(ValueError):
             ModelSpec(**{**fields, "schedule": bad}).validate()
     assert PartSpec("x", {"a": 1})["a"] == 1
+
+
+def test_attention_bias_adds_the_four_bias_tensors():
+    from qwen_triton_b200.engine.model import expected_tensors
+    biased, plain = (expected_tensors(load_preset(n).model_spec()) for n in ("tiny-d", "tiny-a"))
+    cfg = load_preset("tiny-d")
+    for name, rows in (("q_proj", cfg.q_size), ("k_proj", cfg.num_key_value_heads * cfg.head_dim),
+                       ("v_proj", cfg.num_key_value_heads * cfg.head_dim), ("o_proj", cfg.hidden_size)):
+        for layer in range(cfg.num_hidden_layers):
+            assert tuple(biased[f"model.layers.{layer}.self_attn.{name}.bias"].shape) == (rows,)
+    assert not any(name.endswith(".bias") for name in plain)

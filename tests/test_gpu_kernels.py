@@ -395,6 +395,16 @@ def test_kernels_refuse_what_they_cannot_run():
         kernels.gemm_simt(torch.zeros(2, 8, device=DEV), torch.zeros(4, 8, device=DEV), GemmOut(torch.zeros(2, 2, 4, device=DEV)))
 
 
+@pytest.mark.parametrize("rows, cols", [(1, 7), (5, 130), (300, 4096), (2050, 257)])
+def test_add_bias(rows, cols):
+    out, bias = rand(rows, cols, seed=130), rand(cols, seed=131)
+    expected = out + bias
+    kernels.add_bias(out, bias)
+    assert torch.equal(out, expected)
+    with pytest.raises(kernels.KernelError):
+        kernels.add_bias(out, bias[:-1].contiguous())
+
+
 # ----------------------------------------------------------------------------- tensor-core matrix product
 @pytest.mark.parametrize("m, n, k, splits, out_dtype", [
     (1, 503, 96, 1, torch.float32), (8, 640, 512, 2, torch.float32), (8, 6144, 4096, 3, torch.float32),

@@ -10,7 +10,7 @@ from qwen_triton_b200 import Engine, QwenB200ForCausalLM, StepEntry, load_preset
 
 pytestmark = pytest.mark.gpu
 DTYPES = ("fp32", "bf16")
-LENGTHS = {"tiny-a": (5, 9, 17, 70), "tiny-b": (1, 7, 12, 31, 97), "tiny-c": (3, 26, 49, 130)}
+LENGTHS = {"tiny-a": (5, 9, 17, 70), "tiny-b": (1, 7, 12, 31, 97), "tiny-c": (3, 26, 49, 130), "tiny-d": (2, 21, 66, 140)}
 
 
 @pytest.fixture(scope="module", params=[(p, d) for p in PRESETS for d in DTYPES], ids=lambda v: f"{v[0]}-{v[1]}")
@@ -280,3 +280,25 @@ def test_random_weights_are_the_same_bits_on_the_device_and_on_the_host():
     drawn = Engine.from_config(load_preset(preset), seed=SEEDS[preset], dtype=dtype, max_tokens=256)
     loaded = make_engine(preset, dtype, max_tokens=256)
     assert torch.equal(run_whole(drawn, tokens), run_whole(loaded, tokens))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_biased_projections_with_many_rows_and_with_few(dtype):
+    """tiny-d has a bias on q, k, v and o.  A prompt of 300 tokens in one step takes the products for many rows (in
+    bfloat16 the block-pair kernel, whose float result the bias is added to), a batch of five one-token steps the
+    split products for few; both against the plain implementation."""
+    preset = "tiny-d"
+    engine = make_engine(preset, dtype, max_tokens=2048)
+    long = random_tokens(preset, 300, 900)
+    assert_close(run_whole(engine, long), plain_logits(preset, dtype, long), dtype, "300 tokens in one step")
+    prompts = [random_tokens(preset, n, 910 + n) for n in (9, 33, 4, 70, 18)]
+    slots = [engine.new_sequence() for _ in prompts]
+    engine.step([StepEntry(slot, prompt, []) for slot, prompt in zip(slots, prompts)])
+    for step in range(3):
+        feed = [random_tokens(preset, 1, 950 + 10 * step + i)[0] for i in range(len(prompts))]
+        rows = engine.step([StepEntry(slot, [token], [0]) for slot, token in zip(slots, feed)])
+        for i, token in enumerate(feed):
+            prompts[i].append(token)
+            assert_close(rows[i:i + 1], plain_logits(preset, dtype, prompts[i])[-1:], dtype, f"step {step}, request {i}")
+    for slot in slots:
+        engine.release(slot)
