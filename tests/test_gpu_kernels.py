@@ -301,10 +301,11 @@ def test_one_far_key_among_hundreds_wins(dtype, mode):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("mode", ["decode", "prefill"])
-def test_window_edge(dtype, mode):
+@pytest.mark.parametrize("d", [32, 64, 128])                 # 64 and 128: the tcgen05 prefill kernel among the others
+def test_window_edge(dtype, mode, d):
     """The key just outside the window carries a huge score and a huge value: it must not be seen; the
     key just inside carries the second-largest score: it must dominate."""
-    nq, nkv, d, n, window = 2, 1, 32, 200, 37
+    nq, nkv, n, window = 2, 1, 200, 37
     k = torch.randn(n, nkv, d, generator=gen(90)) * 0.05
     v = torch.randn(n, nkv, d, generator=gen(91))
     last = n - 1
@@ -328,6 +329,41 @@ def test_window_edge(dtype, mode):
             kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
                                       torch.tensor([last], dtype=torch.int32, device=DEV), 1, nkv, PAGE, 0, window, 1.0, impl=impl)
         close(out, v[inside].expand(1, nq, d), dtype, f"window edge, {impl}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d, window, ring", [(64, 37, 0), (64, 50, 192), (128, 100, 0), (128, 90, 256), (48, 30, 0)])
+def test_both_edges_of_every_row_of_a_long_query_block(dtype, d, window, ring):
+    """130 query rows after 150 earlier tokens, so that the window's edge and the causal edge of the rows wander through
+    different 64-key tiles.  Key j carries 2 in dimension j mod d, and row i asks, with weights 30, 20 and 50, for
+    the dimensions of the key just outside its window, the key just inside it and the key just after itself: the
+    scores are 60 (must not be seen), 40 (must win: the row's output is that key's value) and 100 (must not be seen).
+    With window < d no other key that the row sees shares one of these dimensions."""
+    assert window < d - 1
+    nq, nkv, past, rows = 4, 2, 150, 130
+    if ring:
+        rows = min(rows, ring - window + 1)
+    total = past + rows
+    k = torch.zeros(total + 1, nkv, d)
+    k[torch.arange(total + 1), :, torch.arange(total + 1) % d] = 2.0
+    v = torch.randn(total + 1, nkv, d, generator=gen(95))
+    pos = torch.arange(past, past + rows)
+    query = torch.zeros(rows, nq, d)
+    query[torch.arange(rows), :, (pos - window) % d] = 30.0
+    query[torch.arange(rows), :, (pos - window + 1) % d] = 20.0
+    query[torch.arange(rows), :, (pos + 1) % d] = 50.0
+    k, v = k.to(dtype).float(), v.to(dtype).float()
+    # the cache holds the step's own keys and nothing later; the key after the last row exists only as the trap it is
+    k_cache, v_cache, table = paged([k[:total]], [v[:total]], [total], dtype, ring_tokens=ring, seed=5)
+    q = query.to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    expected = v[pos - window + 1].repeat_interleave(nq // nkv, dim=1)
+    for impl in impls_for(dtype, d, prefill=True):
+        out.fill_(float("nan"))
+        kernels.attention_prefill(q, k_cache, v_cache, out, table, torch.tensor([0, rows], dtype=torch.int32, device=DEV),
+                                  torch.tensor([past], dtype=torch.int32, device=DEV), rows, nkv, PAGE, ring, window, 1.0, impl=impl)
+        kernels.check_status(DEV)
+        close(out, expected, dtype, f"edges of every row, {impl}")
 
 
 # ----------------------------------------------------------------------------- sampling
