@@ -302,3 +302,43 @@ def test_biased_projections_with_many_rows_and_with_few(dtype):
             assert_close(rows[i:i + 1], plain_logits(preset, dtype, prompts[i])[-1:], dtype, f"step {step}, request {i}")
     for slot in slots:
         engine.release(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", [dict(hidden_size=100, intermediate_size=130, vocab_size=1001, num_attention_heads=5,
+                                         num_key_value_heads=1, head_dim=80),
+                                    dict(hidden_size=36, intermediate_size=50, vocab_size=77, num_attention_heads=3,
+                                         num_key_value_heads=3, head_dim=144),
+                                    dict(hidden_size=136, intermediate_size=264, vocab_size=515, num_attention_heads=14,
+                                         num_key_value_heads=2, head_dim=16, partial_rotary_factor=0.5)])
+def test_sizes_that_fit_no_fast_path(dtype, sizes):
+    """Widths that are no multiple of 8 (rows that the tensor-core products and the 16-byte loads do not take), an
+    intermediate size that is no multiple of 16 (no interleaved gate and up rows), head sizes beyond 128 and of 16, a
+    group of 7 heads, half of a head rotating: the model must pick kernels that take them, in a prompt of two hundred
+    tokens and in a batch of one-token steps."""
+    import dataclasses, tempfile
+    from qwen_triton_b200 import write_random_model
+    from qwen_triton_b200.weights import Checkpoint
+    base = load_preset("tiny-a")
+    config = dataclasses.replace(base, num_hidden_layers=2, layer_types=base.layer_types[:2], tie_word_embeddings=False, **sizes)
+    raw = config.to_hf_dict()
+    with tempfile.TemporaryDirectory(prefix="qt_odd_") as folder:
+        write_random_model(folder, config, seed=12, dtype={"fp32": torch.float32, "bf16": torch.bfloat16}[dtype])
+        checkpoint = Checkpoint(folder)
+        weights = {name: checkpoint.read(name).float() for name in checkpoint.names()}
+        engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=2048)
+    generator = torch.Generator().manual_seed(77)
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=generator).tolist() for n in (200, 3, 61)]
+    slots = [engine.new_sequence() for _ in prompts]
+    first = engine.step([StepEntry(slot, prompt, list(range(len(prompt)))) for slot, prompt in zip(slots, prompts)])
+    expected = torch.cat([plain.forward(raw, weights, prompt) for prompt in prompts])
+    assert_close(first, expected, dtype, "prompts")
+    for step in range(3):
+        feed = torch.randint(0, config.vocab_size, (len(prompts),), generator=generator).tolist()
+        rows = engine.step([StepEntry(slot, [token], [0]) for slot, token in zip(slots, feed)])
+        for i, token in enumerate(feed):
+            prompts[i].append(token)
+            assert_close(rows[i:i + 1], plain.forward(raw, weights, prompts[i])[-1:], dtype, f"step {step}, request {i}")
+    for slot in slots:
+        engine.release(slot)
+    engine.check_kernels()
