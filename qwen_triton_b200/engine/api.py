@@ -101,19 +101,20 @@ class QwenB200ForCausalLM:
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16, temperature: float = 0.0,
                  seed: int = 0, stop_token_ids: Sequence[int] | None = None, ignore_eos: bool = False,
-                 max_batch_size: int | None = None) -> list[GenerationResult]:
+                 max_batch_size: int | None = None, top_k: int = 0, top_p: float = 1.0) -> list[GenerationResult]:
         return generate(self.engine, prompts, max_new_tokens=max_new_tokens,
-                        sampling=SamplingParams(temperature=temperature, seed=seed), stop_token_ids=stop_token_ids,
-                        ignore_eos=ignore_eos, max_batch_size=max_batch_size, sampler=self.sampler)
+                        sampling=SamplingParams(temperature=temperature, seed=seed, top_k=top_k, top_p=top_p),
+                        stop_token_ids=stop_token_ids, ignore_eos=ignore_eos, max_batch_size=max_batch_size, sampler=self.sampler)
 
     def start_batch(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16, temperature: float = 0.0,
-                    seed: int = 0, stop_token_ids: Sequence[int] | None = None, ignore_eos: bool = False) -> BatchRun:
+                    seed: int = 0, stop_token_ids: Sequence[int] | None = None, ignore_eos: bool = False,
+                    top_k: int = 0, top_p: float = 1.0) -> BatchRun:
         """Step-by-step generation of one batch: ``run.start()`` runs the prompts and returns each request's
         first token, every ``run.advance()`` one more token per request still going; ``run.results`` collects
         them and ``run.close()`` gives the cache back.  ``generate`` is this, looped over batches."""
         results = [GenerationResult() for _ in prompts]
         return BatchRun(self.engine, self.sampler, prompts, results, range(len(prompts)), max_new_tokens=max_new_tokens,
-                        sampling=SamplingParams(temperature=temperature, seed=seed),
+                        sampling=SamplingParams(temperature=temperature, seed=seed, top_k=top_k, top_p=top_p),
                         stop=stop_set(self.engine, stop_token_ids, ignore_eos))
 
     @torch.no_grad()

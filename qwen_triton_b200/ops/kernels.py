@@ -69,7 +69,7 @@ _SIGNATURES = {
     "sampling": {
         "qt_argmax": [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
         "qt_sample": [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
-        "qt_sample_keyed": [_c_ptr, _c_float, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+        "qt_sample_keyed": [_c_ptr, _c_float, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_ptr],
         "qt_feed_tokens": [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr],
     },
 }
@@ -453,16 +453,21 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
           _stream())
 
 
-def sample_keyed(logits: torch.Tensor, temperature: float, seed: int, keys: torch.Tensor, out: torch.Tensor) -> None:
+def sample_keyed(logits: torch.Tensor, temperature: float, seed: int, keys: torch.Tensor, out: torch.Tensor,
+                 top_k: int = 0, top_p: float = 1.0) -> None:
     """Temperature sampling with the uniform number of each row made on the device from (seed, request, step);
-    ``keys`` int32 [rows, 2] holds each row's request and step number."""
+    ``keys`` int32 [rows, 2] holds each row's request and step number.  ``top_k`` > 0 keeps the k largest logits (and
+    what ties with the k-th), ``top_p`` < 1 of those the most likely tokens whose renormalised probabilities first sum
+    to it (and what ties with the last)."""
     rows = logits.shape[0]
+    if not 0.0 < top_p <= 1.0 or top_k < 0:
+        raise KernelError(f"sample: top_k={top_k} must not be negative and top_p={top_p} must lie in (0, 1]")
     _need(logits, "logits", torch.float32)
     _need(keys, "keys", torch.int32, (rows, 2))
     _need(out, "out", torch.int32, (rows,))
     seed &= (1 << 64) - 1
     _call("sampling", "qt_sample_keyed", _ptr(logits), float(temperature), seed - (1 << 64) if seed >> 63 else seed, _ptr(keys),
-          _ptr(out), rows, logits.shape[1], _stream())
+          _ptr(out), rows, logits.shape[1], int(top_k), float(top_p), _stream())
 
 
 _STATUS: dict[int, torch.Tensor] = {}

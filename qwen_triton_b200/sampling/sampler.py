@@ -4,6 +4,10 @@ The reference picks ``argmax`` of the last position and nothing else
 (qwen_triton/models/core.py:405).  Temperature sampling here draws token
 ``softmax(logits / T)`` by inverse CDF in vocabulary order with one uniform number per
 (seed, request, step), so a request's tokens do not depend on what else is in the batch.
+``top_k`` and ``top_p`` (both off by default) leave only the most likely tokens to draw from:
+the k largest logits, and of those the smallest set of the most likely whose renormalised
+probabilities sum to ``top_p``; tokens that tie with the last one kept are kept as well, so that
+the set does not depend on an order among equals.
 """
 from __future__ import annotations
 
@@ -20,10 +24,14 @@ _MASK64 = (1 << 64) - 1
 class SamplingParams:
     temperature: float = 0.0     # 0: greedy (ties go to the lowest token id)
     seed: int = 0
+    top_k: int = 0               # > 0: only the k largest logits (with temperature > 0)
+    top_p: float = 1.0           # < 1: only the most likely tokens that sum to this share (with temperature > 0)
 
     def __post_init__(self) -> None:
         if self.temperature < 0.0:
             raise ValueError("temperature must not be negative")
+        if self.top_k < 0 or not 0.0 < self.top_p <= 1.0:
+            raise ValueError("top_k must not be negative and top_p must lie in (0, 1]")
 
 
 def _mix64(value: int) -> int:
@@ -93,7 +101,8 @@ class Sampler:
         if params.temperature == 0.0:
             kernels.argmax(logits, out)
         else:
-            kernels.sample_keyed(logits, params.temperature, params.seed, self._keys_on_device(requests, steps), out)
+            kernels.sample_keyed(logits, params.temperature, params.seed, self._keys_on_device(requests, steps), out,
+                                 params.top_k, params.top_p)
         if not self._hosts or self._hosts[0].numel() < rows:
             self._hosts = [torch.empty(max(rows, 64), dtype=torch.int32, pin_memory=True) for _ in range(self._RING)]
         host = self._hosts[self._turn % self._RING]

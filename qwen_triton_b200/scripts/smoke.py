@@ -33,6 +33,8 @@ def _parse_args(argv=None) -> argparse.Namespace:
     parser.add_argument("--random-prompts", default=None, help="comma-separated lengths of prompts of uniform random token ids")
     parser.add_argument("--max-new-tokens", type=int, default=8)
     parser.add_argument("--temperature", type=float, default=0.0)
+    parser.add_argument("--top-k", type=int, default=0, help="with --temperature: draw from the k most likely tokens only")
+    parser.add_argument("--top-p", type=float, default=1.0, help="with --temperature: draw from the most likely tokens that sum to this share")
     parser.add_argument("--seed", type=int, default=0, help="seed of everything the run draws")
     parser.add_argument("--sampling-seed", type=int, default=None, help="seed of temperature sampling (default: --seed)")
     parser.add_argument("--weights-seed", type=int, default=None, help="seed of --random-weights (default: --seed)")
@@ -104,7 +106,7 @@ def main(argv=None) -> None:
     next_token = outputs.logits[:, -1].argmax(dim=-1)
     results = model.generate(prompts, max_new_tokens=args.max_new_tokens, temperature=args.temperature,
                              seed=sampling_seed, stop_token_ids=_ids(args.stop_ids, "--stop-ids"),
-                             ignore_eos=args.ignore_eos, max_batch_size=args.max_batch_size)
+                             ignore_eos=args.ignore_eos, max_batch_size=args.max_batch_size, top_k=args.top_k, top_p=args.top_p)
     print(f"backend={args.backend}")
     print(f"next_token={next_token.tolist()}")
     for prompt, result in zip(prompts, results):

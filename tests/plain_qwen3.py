@@ -229,12 +229,34 @@ def sample_temperature(logits: torch.Tensor, temperature: float, uniform: float)
     return min(index, logits.numel() - 1)
 
 
+def kept_tokens(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0) -> torch.Tensor:
+    """Which tokens top_k and top_p leave to draw from (bool [vocab]), stated with a sort: the k largest logits and
+    every logit equal to the k-th; then, with probabilities renormalised over those, the shortest run of the most
+    likely tokens that sums to top_p and every token as likely as its last."""
+    keep = torch.ones_like(logits, dtype=torch.bool)
+    if 0 < top_k < logits.numel():
+        keep &= logits >= torch.topk(logits, top_k).values[-1]
+    if top_p < 1.0:
+        scaled = logits.double() / temperature
+        weights = torch.where(keep, torch.exp(scaled - scaled.max()), torch.zeros_like(scaled))
+        ordered, order = torch.sort(weights, descending=True)
+        reached = int(torch.searchsorted(torch.cumsum(ordered, dim=0), top_p * weights.sum()))
+        keep &= logits >= logits[order[min(reached, logits.numel() - 1)]]
+    return keep
+
+
 def choice_is_consistent(logits: torch.Tensor, temperature: float, uniform: float, token: int,
-                         slack: float = 1e-4) -> bool:
+                         slack: float = 1e-4, top_k: int = 0, top_p: float = 1.0) -> bool:
     """Whether ``token`` is the inverse-CDF choice for ``uniform`` up to float32 rounding of the
-    cumulative weights: the target mass lies in the token's interval widened by ``slack`` of the total."""
+    cumulative weights: the target mass lies in the token's interval widened by ``slack`` of the total.  With
+    ``top_k`` / ``top_p`` only the tokens of ``kept_tokens`` have weight."""
     scaled = logits.double() / temperature
     weights = torch.exp(scaled - scaled.max())
+    if top_k or top_p < 1.0:
+        keep = kept_tokens(logits, temperature, top_k, top_p)
+        if not bool(keep[token]):
+            return False
+        weights = torch.where(keep, weights, torch.zeros_like(weights))
     cumulative = torch.cumsum(weights, dim=0)
     total = float(cumulative[-1])
     target = uniform * total

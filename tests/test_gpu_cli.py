@@ -62,6 +62,16 @@ def test_temperature_sampling_and_stop_ids():
             row = plain.forward(raw, weights, sequence)[-1]
             assert plain.choice_is_consistent(row, 0.8, plain.uniform_for(11, index, step), token), (index, step)
             sequence.append(token)
+    # drawing from the single most likely token is the greedy choice, whatever the temperature
+    results = generated(run_cli(*common, "--max-new-tokens", "6", "--temperature", "0.9", "--top-k", "1"))
+    assert results == [(plain.greedy_generate(raw, weights, p, 6), "length") for p in prompts]
+    results = generated(run_cli(*common, "--max-new-tokens", "5", "--temperature", "0.9", "--top-p", "0.6", "--seed", "3"))
+    for index, (prompt, (tokens, _)) in enumerate(zip(prompts, results)):
+        sequence = list(prompt)
+        for step, token in enumerate(tokens):
+            row = plain.forward(raw, weights, sequence)[-1]
+            assert plain.choice_is_consistent(row, 0.9, plain.uniform_for(3, index, step), token, top_p=0.6), (index, step)
+            sequence.append(token)
     # a stop token ends its request early and is the last token printed for it
     free_run = [plain.greedy_generate(raw, weights, p, 8) for p in prompts]
     stop = free_run[0][3]

@@ -419,6 +419,84 @@ def test_sample_draws_its_uniform_number_from_seed_request_and_step():
     assert all(abs(int(out[r]) - expected[r]) <= 1 for r in range(rows)), (out.tolist(), expected)
 
 
+def _draws(logits_row, temperature, top_k, top_p, count=4000, seed=77):
+    """``count`` draws from one row of logits, each with a request number of its own."""
+    logits = logits_row.repeat(count, 1).contiguous()
+    keys = torch.stack([torch.arange(count), torch.zeros(count, dtype=torch.long)], dim=1).int().to(DEV)
+    out = torch.empty(count, dtype=torch.int32, device=DEV)
+    kernels.sample_keyed(logits, temperature, seed, keys, out, top_k, top_p)
+    return out.cpu().long()
+
+
+@pytest.mark.parametrize("vocab, top_k, top_p", [(5003, 7, 1.0), (5003, 0, 0.6), (5003, 50, 0.8), (151936, 0, 0.9), (151936, 40, 0.95),
+                                                 (300, 299, 0.999), (64, 1, 1.0)])
+def test_sample_from_the_most_likely_tokens_only(vocab, top_k, top_p):
+    """Many draws from one row: every drawn token is one that the sorted statement of top_k / top_p keeps, every kept
+    token of some weight is drawn, and the frequencies follow the probabilities renormalised over the kept set."""
+    import plain_qwen3 as plain
+    temperature = 0.8
+    row = rand(1, vocab, seed=140, scale=3.0)
+    keep = plain.kept_tokens(row[0].cpu(), temperature, top_k, top_p)
+    assert 0 < int(keep.sum()) < vocab
+    draws = _draws(row, temperature, top_k, top_p)
+    assert bool(keep[draws].all()), f"drawn outside the kept set: {sorted(set(draws[~keep[draws]].tolist()))[:10]}"
+    probs = torch.where(keep, torch.softmax(row[0].cpu().double() / temperature, 0), torch.zeros(vocab, dtype=torch.float64))
+    probs /= probs.sum()
+    freq = torch.bincount(draws, minlength=vocab).double() / draws.numel()
+    assert float((freq - probs).abs().max()) < 0.03
+    assert bool((freq[probs > 0.01] > 0).all())
+    # the same rows again: the same tokens (masses are summed as integers, so no order of additions shows)
+    assert torch.equal(draws, _draws(row, temperature, top_k, top_p))
+
+
+@pytest.mark.parametrize("top_k, top_p", [(300, 1.0), (0, 0.5), (12000, 0.3)])
+def test_rows_of_nearly_equal_logits_are_cut_at_the_same_threshold(top_k, top_p):
+    """20,000 logits within a few hundredths of each other: the threshold's neighbourhood holds more tokens than the
+    kernel's short list, so it walks the whole row digit by digit instead; the kept set is the sorted statement's."""
+    import plain_qwen3 as plain
+    row = rand(1, 20000, seed=143, scale=0.01)
+    keep = plain.kept_tokens(row[0].cpu(), 1.0, top_k, top_p)
+    draws = _draws(row, 1.0, top_k, top_p, count=6000)
+    assert bool(keep[draws].all())
+    edge = row[0].cpu()[keep].min()                       # the least likely kept tokens are drawn as well
+    near_edge = keep & (row[0].cpu() < edge + 0.002)
+    assert int(near_edge.sum()) > 20 and bool(near_edge[draws].any())
+
+
+def test_tokens_that_tie_with_the_last_kept_one_are_kept():
+    """Ten tokens share the largest logit and top_k asks for four: all ten are drawn from.  Two tokens share the
+    probability at which top_p is reached: both are kept."""
+    row = rand(1, 700, seed=141, scale=0.5)
+    tied = torch.tensor([3, 64, 65, 128, 300, 301, 511, 512, 640, 699])
+    row[0, tied] = 6.0
+    draws = _draws(row, 1.0, 4, 1.0, count=2000)
+    assert sorted(set(draws.tolist())) == tied.tolist()
+    row = torch.full((1, 500), -30.0, device=DEV)
+    row[0, 10], row[0, 20], row[0, 400], row[0, 450] = 2.0, 1.0, 1.0, 0.0        # shares 0.55, 0.20, 0.20, 0.07 of the mass
+    draws = _draws(row, 1.0, 0, 0.7, count=2000)                                   # 0.55 + 0.20 reaches 0.7: the other 0.20 ties
+    assert sorted(set(draws.tolist())) == [10, 20, 400]
+    draws = _draws(row, 1.0, 0, 0.5, count=500)
+    assert set(draws.tolist()) == {10}
+
+
+def test_sample_of_distinct_rows_with_top_k_and_top_p():
+    """64 different rows of the full vocabulary, each with the uniform number of its (request, step): the chosen token
+    is the inverse-CDF choice over the kept set."""
+    import plain_qwen3 as plain
+    rows, vocab, seed = 64, 151936, 99
+    logits = rand(rows, vocab, seed=142, scale=2.5)
+    keys = torch.stack([torch.arange(rows) + 5, torch.arange(rows) % 3], dim=1).int()
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    for top_k, top_p in ((0, 0.9), (100, 1.0), (1000, 0.7)):
+        kernels.sample_keyed(logits, 0.7, seed, keys.to(DEV), out, top_k, top_p)
+        host = logits.cpu()
+        for r in range(rows):
+            uniform = plain.uniform_for(seed, int(keys[r, 0]), int(keys[r, 1]))
+            assert plain.choice_is_consistent(host[r], 0.7, uniform, int(out[r]), top_k=top_k, top_p=top_p), (top_k, top_p, r)
+    with pytest.raises(kernels.KernelError, match="top_p"):
+        kernels.sample_keyed(logits, 0.7, seed, keys.to(DEV), out, 0, 0.0)
+
+
 def test_kernels_refuse_what_they_cannot_run():
     with pytest.raises(kernels.KernelError, match="CUDA tensor"):
         kernels.argmax(torch.zeros(1, 4), torch.zeros(1, dtype=torch.int32))
