@@ -271,3 +271,12 @@ def test_uniform_stream_matches_the_plain_reference():
     assert SamplingParams().temperature == 0.0
     with pytest.raises(ValueError):
         SamplingParams(temperature=-1.0)
+
+
+def test_sampling_parameters_are_checked():
+    import pytest
+    from qwen_triton_b200.sampling import SamplingParams
+    assert SamplingParams().top_k == 0 and SamplingParams().top_p == 1.0
+    for bad in (dict(temperature=-0.1), dict(top_k=-1), dict(top_p=0.0), dict(top_p=1.5)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
