@@ -129,7 +129,7 @@ def attention_layer(x: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str,
 
     def project(name: str, rows: torch.Tensor) -> torch.Tensor:
         out = rows @ w[f"{prefix}.{name}.weight"].T
-        return out + w[f"{prefix}.{name}.bias"] if cfg["attention_bias"] else out
+        return out + w[f"{prefix}.{name}.bias"] if cfg.get("attention_bias", False) else out
 
     q = project("q_proj", x).view(seq, cfg["heads"], d)
     k = project("k_proj", x).view(seq, cfg["kv_heads"], d)
