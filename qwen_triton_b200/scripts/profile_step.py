@@ -3,6 +3,7 @@
 
     python -m qwen_triton_b200.scripts.profile_step --mode decode --batch 8 --context 2048 --layers 4
     python -m qwen_triton_b200.scripts.profile_step --mode prefill --tokens 2048 --layers 4
+    python -m qwen_triton_b200.scripts.profile_step --mode sampling --batch 8 --top-p 0.9
 
 Random weights of the given preset (optionally fewer layers, to keep a capture small), random token
 ids.  Prints the mean step time measured with CUDA events; under a profiler that number is not a
@@ -17,7 +18,11 @@ import dataclasses
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--preset", default="qwen3-8b")
-    parser.add_argument("--mode", choices=["decode", "prefill"], default="decode")
+    parser.add_argument("--mode", choices=["decode", "prefill", "sampling"], default="decode",
+                        help="'sampling': the choice of the next token alone, on random logits of the preset's vocabulary")
+    parser.add_argument("--temperature", type=float, default=0.8)
+    parser.add_argument("--top-k", type=int, default=0)
+    parser.add_argument("--top-p", type=float, default=1.0)
     parser.add_argument("--dtype", default="bf16")
     parser.add_argument("--layers", type=int, default=0)
     parser.add_argument("--batch", type=int, default=8)
@@ -34,6 +39,26 @@ def main(argv=None) -> None:
     from qwen_triton_b200 import QwenB200ForCausalLM, StepEntry, load_preset
 
     full = load_preset(args.preset)
+    if args.mode == "sampling":
+        from qwen_triton_b200.ops import kernels
+        generator = torch.Generator(device="cuda").manual_seed(3)
+        logits = torch.randn(args.batch, full.vocab_size, generator=generator, device="cuda") * 2.5
+        keys = torch.stack([torch.arange(args.batch), torch.zeros(args.batch, dtype=torch.long)], dim=1).int().cuda()
+        out = torch.empty(args.batch, dtype=torch.int32, device="cuda")
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for name, run in (("argmax", lambda: kernels.argmax(logits, out)),
+                          (f"temperature {args.temperature}, top_k {args.top_k}, top_p {args.top_p}",
+                           lambda: kernels.sample_keyed(logits, args.temperature, 1, keys, out, args.top_k, args.top_p))):
+            for _ in range(args.warmup):
+                run()
+            torch.cuda.synchronize()
+            begin.record()
+            for _ in range(args.steps):
+                run()
+            end.record()
+            torch.cuda.synchronize()
+            print(f"{name}: {begin.elapsed_time(end) / args.steps * 1e3:.1f} us for {args.batch} rows of {full.vocab_size}")
+        return
     layers = args.layers or full.num_hidden_layers
     config = dataclasses.replace(full, num_hidden_layers=layers, layer_types=full.layer_types[:layers])
     span = (args.context if args.mode == "decode" else args.tokens) + args.steps + args.warmup + 64
