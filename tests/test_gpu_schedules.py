@@ -3,11 +3,16 @@ steps with 8, 17 and 64 live rows, more rows than are captured in a CUDA graph, 
 across position 1,024, where a one-token step's context bucket, page-table width and split counts change.  Every
 row is compared with the plain implementation.  The models have their q/k norm weights raised so that a few keys
 carry each softmax: a missed or misplaced key then shows in bfloat16 too."""
+import dataclasses
+import tempfile
+
 import pytest
 import torch
 
-from gpu_util import assert_close, folder_logits, peaky_folder, random_tokens
-from qwen_triton_b200 import Engine, StepEntry
+import plain_qwen3 as plain
+from gpu_util import STORE, assert_close, folder_logits, peaky_folder, random_tokens
+from qwen_triton_b200 import Engine, StepEntry, load_preset, write_random_model
+from qwen_triton_b200.weights import Checkpoint, write_safetensors
 
 pytestmark = pytest.mark.gpu
 DTYPES = ("fp32", "bf16")
@@ -78,3 +83,38 @@ def test_decoding_across_position_1024(dtype):
     assert buckets == {1024, 2048}, buckets
     for i, (tokens, n) in enumerate(zip(requests, prompt_lengths)):
         assert_close(got[i], folder_logits(folder, preset, tuple(tokens))[n - 1:], dtype, f"row {i} (from {n} tokens)")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_contexts_of_several_thousand_tokens(dtype):
+    """Prompts of 5,000, 4,100 and 70 tokens (the long ones in two passes of a step), then one-token steps: the keys
+    of a sequence are cut into 32 ranges, more than a cluster merges, so the partial results go through scratch memory
+    and the combine kernel, over page tables of 80 pages.  Raised q/k norm weights let single far keys matter.  The
+    plain implementation runs on the device (float32 products, no reduced-precision mode) to keep the test short."""
+    base = load_preset("tiny-b")
+    config = dataclasses.replace(base, max_position_embeddings=8192)
+    raw = config.to_hf_dict()
+    with tempfile.TemporaryDirectory(prefix="qt_long_") as folder:
+        write_random_model(folder, config, seed=21, dtype=STORE[dtype])
+        checkpoint = Checkpoint(folder)
+        tensors = {}
+        for name in checkpoint.names():
+            tensor = checkpoint.read(name)
+            if name.endswith(("q_norm.weight", "k_norm.weight")):
+                tensor = (tensor.float() * 1.5).to(tensor.dtype)
+            tensors[name] = tensor
+        write_safetensors(f"{folder}/model.safetensors", tensors)
+        engine = Engine.from_pretrained(folder, dtype=dtype, max_tokens=3 * 5120, max_seq_len=5120, max_step_tokens=4096)
+    assert not torch.backends.cuda.matmul.allow_tf32
+    weights = {name: tensor.float().cuda() for name, tensor in tensors.items()}
+    steps = 6
+    prompt_lengths = [5000, 4100, 70]
+    generator = torch.Generator().manual_seed(31)
+    requests = [torch.randint(0, config.vocab_size, (n + steps,), generator=generator).tolist() for n in prompt_lengths]
+    got = decode_together(engine, requests, prompt_lengths, steps)
+    for i, (tokens, n) in enumerate(zip(requests, prompt_lengths)):
+        expected = plain.forward(raw, weights, tokens)[n - 1:].cpu()
+        assert_close(got[i], expected, dtype, f"row {i} (from {n} tokens)")
+    # alone, a sequence's keys are cut as finely as the scratch allows
+    alone = decode_together(engine, requests[:1], prompt_lengths[:1], 3)
+    assert_close(alone[0], plain.forward(raw, weights, requests[0])[prompt_lengths[0] - 1:prompt_lengths[0] + 3].cpu(), dtype, "alone")
