@@ -25,18 +25,25 @@ _FUSED_ROWS = int(os.environ.get("QT_B200_FUSED_ROWS", "16"))
 # first weight tiles while this one drains; up to 64 rows two blocks with deeper rings measured better.  Up to 256
 # rows (a large decode batch, a short prompt) the weight still bounds the product: blocks of 128 tokens, split
 # (alone, 256 rows of the 8B shapes: 16.6 us against 54 us for q/k/v, 32 against 158 us for the down projection).
-_SPLIT_PLANS = ((16, 4), (64, 2), (128, 2), (256, 2))      # (most rows, blocks per SM)
+# 17 to 32 rows take the 32-token tile, which keeps four blocks per SM like the 16-token one: a plan of their own
+# (in the model, batch 24 / 32 of the 8B shape: 5.23 / 5.33 ms a step against 5.36 / 5.44 with the 64-row plan).
+_SPLIT_PLANS = ((16, 4), (32, 4), (64, 2), (128, 2), (256, 2))      # (most rows, blocks per SM)
 
 
 def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: int = 16, most: int = _MAX_SPLITS,
-                partial_cost: float = 2.0) -> int:
+                partial_cost: float = 2.0, sms: int = 0) -> int:
     """Split count for a product with few rows, by a cost in bytes: the weight, read at the rate its blocks
     (128-row weight tiles x token tiles of at most 128 x splits) keep ``target_blocks`` slots busy (a second token
     tile reads it again, from L2), plus the float partial sums of ``rows`` rows, written once and read once.  Each split keeps at least four 64-wide K blocks; fewer splits win near-ties.
     (Filling waves alone would cut a product that already has blocks for several waves into many splits, whose
     partial sums then cost more than the weight: 14 splits for a 51,200 x 5,120 weight at 64 rows.)
     ``partial_cost`` is 2 for partial sums written to and read from global memory, 1 for the fused product, whose
-    blocks (at most ``most`` = 8 of a cluster) park them in shared memory and read each other's."""
+    blocks (at most ``most`` = 8 of a cluster) park them in shared memory and read each other's.
+    A weight whose tiles alone give every one of the ``sms`` SMs a block is not cut beyond the ``target_blocks`` that
+    are resident at once: its blocks already draw what the memory gives, and a second wave of them only adds a ramp
+    and partial sums (the gated product of the 8B shape at 64 rows, alone: 39.1 us unsplit, 43.1 / 41.2 us in two /
+    three ranges; in the model at batch 48 / 64 / 96 / 128: 3 % shorter steps; the 32B shape's gated product, 400
+    tiles, at batch 8: 16 layers and the head in 3.22 ms against 3.53 ms with eight ranges)."""
     token_tiles = -(-rows // kernels.TC_MAX_BLOCK_TOKENS)
     tiles = -(-out_features // 128) * token_tiles
     blocks_k = -(-in_features // 64)
@@ -47,6 +54,8 @@ def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: i
             break
         if kernels.tc_normalise_splits(in_features, splits) != splits:
             continue
+        if splits > 1 and sms and tiles >= sms and tiles * splits > target_blocks:
+            break
         waves = tiles * splits / target_blocks
         fill = waves if waves <= 1.0 else waves / (waves + 0.35)     # under one wave: idle slots; over: a tail of about a third of a wave
         partial_bytes = partial_cost * 4 * splits * rows * out_features if splits > 1 else 0.0
@@ -106,9 +115,9 @@ class Linear:
         self.split_plans: list[tuple[int, int]] = []          # (most rows, splits), fewest rows first
         self.fused_plans: list[tuple[int, int]] = []          # the same for the fused product (its blocks add up in shared memory)
         if runtime.dtype == torch.bfloat16 and in_features % 8 == 0:
-            self.split_plans = [(rows, pick_splits(out_features, in_features, per_sm * sms, rows)) for rows, per_sm in _SPLIT_PLANS]
+            self.split_plans = [(rows, pick_splits(out_features, in_features, per_sm * sms, rows, sms=sms)) for rows, per_sm in _SPLIT_PLANS]
             self.fused_plans = [(rows, pick_splits(out_features, in_features, (3 if role == "gate" else per_sm) * sms, rows,
-                                                   kernels.FUSED_MAX_SPLITS, 1.0))
+                                                   kernels.FUSED_MAX_SPLITS, 1.0, sms=sms))
                                 for rows, per_sm in _SPLIT_PLANS if rows <= kernels.FUSED_MAX_ROWS]
             # a few hundred rows: the pair kernel with split K where its tiles alone would not fill the TPCs
             if not float_out and self.max_rows > _PAIR_TILE:
