@@ -41,11 +41,15 @@ __device__ __forceinline__ void tile_coords(int t, int w_tiles, int x_tiles, int
     x = r / width;
 }
 
-template <int BX, typename TO>
+// GATED: the weight's rows alternate 16 of a gate projection and 16 of an up projection; the 32 accumulator lanes of
+// an epilogue warp are then the gate rows (lanes 0..15) and the up rows (16..31) of the same 16 features, and the
+// kernel stores act(gate) * up, [M, N / 2] (one K range only).  Of every two tokens the lower lanes finish the first
+// and the upper lanes the second: one exchange gives each half the value it lacks, and all 32 lanes compute and store.
+template <int BX, typename TO, bool GATED>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, TO* __restrict__ out,
                                                           int M, int N, int kb_total, int kb_per_split,
-                                                          size_t split_stride, int stages, int* status) {
+                                                          size_t split_stride, int stages, int act, int* status) {
     constexpr uint32_t X_BYTES = BX * BK * 2;
     constexpr uint32_t STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr uint32_t TMEM_COLS = BX < 32 ? 32 : BX;
@@ -139,7 +143,19 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             for (int c = 0; c < BX; c += 16) {
                 uint32_t v[16];
                 tmem_load16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
-                if (n < N) {
+                if (GATED) {
+                    const int features = N >> 1, feature = ((n - lane) >> 1) + (lane & 15);
+                    const bool upper = (lane & 16) != 0;
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const float mine0 = __uint_as_float(v[j]), mine1 = __uint_as_float(v[j + 1]);
+                        const float got = __shfl_xor_sync(0xffffffffu, upper ? mine0 : mine1, 16);
+                        const float g = upper ? got : mine0;          // lower lanes: token j (their gate, the partner's up)
+                        const float u = upper ? mine1 : got;          // upper lanes: token j + 1 (the partner's gate, their up)
+                        const int m = x0 + c + j + (upper ? 1 : 0);
+                        if (feature < features && m < M) dst[(size_t)m * features + feature] = from_float<TO>(gate_activation<true>(g, act) * u);
+                    }
+                } else if (n < N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int m = x0 + c + j;
@@ -639,9 +655,9 @@ int launch_pair(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int
 }
 
 // ----------------------------------------------------------------------------- host side
-template <int BX, typename TO>
+template <int BX, typename TO, bool GATED>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-           size_t split_stride, int stages, int* status, cudaStream_t stream) {
+           size_t split_stride, int stages, int act, int* status, cudaStream_t stream) {
     constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
     // Up to 32 tokens a block streams weights through a three-stage ring (54 KB), so that four blocks share an SM and
     // the next product's blocks can move in beside this one's last blocks and fetch their first weight tiles early
@@ -658,27 +674,27 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, i
     const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 16;
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BX, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BX, TO, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (err != cudaSuccess) QT_FAIL(QT_ERR_LAUNCH, "gemm_tc: cannot raise shared memory: %s", cudaGetErrorString(err));
         configured = true;
     }
     const int kb_per_split = (kb_total + splits - 1) / splits;
     dim3 grid(((N + BW - 1) / BW) * ((M + BX - 1) / BX), 1, splits);
-    launch_kernel(gemm_tc_kernel<BX, TO>, dim3(grid), dim3(THREADS), smem, stream, map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, status);
+    launch_kernel(gemm_tc_kernel<BX, TO, GATED>, dim3(grid), dim3(THREADS), smem, stream, map_w, map_x, out, M, N, kb_total, kb_per_split, split_stride, stages, act, status);
     QT_CHECK_LAUNCH("gemm_tc");
     return QT_OK;
 }
 
 
-template <typename TO>
+template <typename TO, bool GATED>
 int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
-                  size_t split_stride, int stages, int* status, cudaStream_t stream) {
+                  size_t split_stride, int stages, int act, int* status, cudaStream_t stream) {
     switch (bx) {
-        case 16: return launch<16, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
-        case 32: return launch<32, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
-        case 64: return launch<64, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
-        case 128: return launch<128, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
-        case 256: return launch<256, TO>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, status, stream);
+        case 16: return launch<16, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
+        case 32: return launch<32, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
+        case 64: return launch<64, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
+        case 128: return launch<128, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
+        case 256: return launch<256, TO, GATED>(map_w, map_x, out, M, N, kb_total, splits, split_stride, stages, act, status, stream);
     }
     QT_FAIL(QT_ERR_ARG, "gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", bx);
 }
@@ -690,8 +706,12 @@ int dispatch_tile(int bx, const CUtensorMap& map_w, const CUtensorMap& map_x, TO
 // blocks: (splits - 1) * ceil(ceil(K/64) / splits) < ceil(K/64).  `status` is a device int that stays
 // 0 unless a wait inside the kernel ran out (1 = producer, 2 = MMA issuer, 3 = epilogue).
 // `stages` > 0 overrides the depth of the shared-memory ring (a tuning knob; 0 picks the default).
+// With `gated` the weight's rows alternate 16 of a gate and 16 of an up projection and `out` is [M, N / 2] bfloat16 =
+// act(gate) * up (`act`: one of QT_ACT_*; one K range only).
 extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int token_tile,
-                          int splits, long long split_stride, int stages, int* status, void* stream) {
+                          int splits, long long split_stride, int stages, int gated, int act, int* status, void* stream) {
+    QT_REQUIRE(!gated || (splits == 1 && out_dtype == QT_BF16 && N % 32 == 0 && act >= 0 && act < QT_ACT_COUNT),
+               "gemm_tc: the gated epilogue writes bfloat16 from one K range of gate and up rows in groups of 16 (N=%d, splits=%d)", N, splits);
     QT_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     QT_REQUIRE(K % 8 == 0, "gemm_tc: K=%d must be a multiple of 8 (rows must start on 16-byte boundaries for TMA)", K);
     QT_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
@@ -708,10 +728,12 @@ extern "C" int qt_gemm_tc(const void* x, const void* w, void* out, int out_dtype
     rc = tensor_map(&map_x, x, (uint64_t)M, (uint64_t)K, (uint32_t)token_tile);
     if (rc) return rc;
     cudaStream_t s = (cudaStream_t)stream;
+    if (gated)
+        return dispatch_tile<__nv_bfloat16, true>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, 1, 0, stages, act, status, s);
     if (out_dtype == QT_BF16)
-        return dispatch_tile<__nv_bfloat16>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, stages, status, s);
+        return dispatch_tile<__nv_bfloat16, false>(token_tile, map_w, map_x, (__nv_bfloat16*)out, M, N, kb_total, splits, (size_t)split_stride, stages, 0, status, s);
     if (out_dtype == QT_F32)
-        return dispatch_tile<float>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, stages, status, s);
+        return dispatch_tile<float, false>(token_tile, map_w, map_x, (float*)out, M, N, kb_total, splits, (size_t)split_stride, stages, 0, status, s);
     QT_FAIL(QT_ERR_ARG, "gemm_tc: unknown output type %d", out_dtype);
 }
 

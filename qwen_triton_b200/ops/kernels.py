@@ -53,7 +53,7 @@ _SIGNATURES = {
         "qt_gemm_simt": [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     },
     "gemm_tc": {
-        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr],
+        "qt_gemm_tc": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
         "qt_gemm_tc_pair": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_ptr,
                             _c_ptr, _c_int, _c_ptr, _c_ptr],
         "qt_gemm_tc_pair_slots": [],
@@ -533,15 +533,20 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | None = None, stages: int = 0) -> None:
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | None = None, stages: int = 0,
+            swiglu: bool = False, activation: str = "silu") -> None:
     """out = a [M, K] @ w [N, K]^T on the tcgen05 tensor cores; bfloat16 inputs, K a multiple of 8.
 
-    ``out`` is [1, M, N] bfloat16 or float, or [splits, M, N] float for split-K partial sums.
+    ``out`` is [1, M, N] bfloat16 or float, or [splits, M, N] float for split-K partial sums.  With ``swiglu`` the
+    rows of ``w`` alternate SWIGLU_GROUP of a gate and of an up projection and ``out`` [1, M, N / 2] (bfloat16)
+    receives act(gate) * up from the epilogue.
     """
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     rows, k = a.shape
-    if k != w.shape[1] or (out.rows, out.cols) != (rows, w.shape[0]):
+    cols = w.shape[0] // 2 if swiglu else w.shape[0]
+    if k != w.shape[1] or (out.rows, out.cols) != (rows, cols) or (swiglu and (out.n_splits != 1 or w.shape[0] % (2 * SWIGLU_GROUP)
+                                                                                   or out.tensor.dtype != torch.bfloat16)):
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.tensor.shape)} do not fit")
     if rows == 0:
         return
@@ -549,7 +554,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: GemmOut, token_tile: int | No
         raise KernelError("gemm_tc: the output must be a bfloat16 or float32 CUDA tensor")
     tile = token_tile or tc_token_tile(rows)
     _call("gemm_tc", "qt_gemm_tc", _ptr(a), _ptr(w), _ptr(out.tensor), _code(out.tensor, "out"), rows, w.shape[0], k, tile,
-          out.n_splits, out.split_stride, int(stages), _ptr(_status_word(a.device)), _stream())
+          out.n_splits, out.split_stride, int(stages), 1 if swiglu else 0, activation_code(activation) if swiglu else 0,
+          _ptr(_status_word(a.device)), _stream())
 
 
 _PAIR_TAIL: dict[int, tuple[torch.Tensor, torch.Tensor, int]] = {}

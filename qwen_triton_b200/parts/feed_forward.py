@@ -60,6 +60,9 @@ class GatedMLP:
             self.gate_up.into_swiglu(x, act, self.activation)
         elif self.group and kernels.gemm_uses_pairs(x, self.gate_up.weight):
             kernels.gemm_tc_pair(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
+        elif self.group and kernels.gemm_tc_supported(x, self.gate_up.weight) and self.gate_up.plan_splits(tokens) == 1:
+            # a weight whose tiles fill the machine unsplit: the gate in the plain product's epilogue
+            kernels.gemm_tc(x, self.gate_up.weight, GemmOut(act.view(1, tokens, self.inter)), swiglu=True, activation=self.activation)
         else:
             kernels.swiglu(self.gate_up(x), act, self.group, self.activation)
         # few tokens: the down projection is left to the norm behind it, which launches it with the residual addition

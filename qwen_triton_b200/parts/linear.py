@@ -179,6 +179,10 @@ class Linear:
     def into_qkv(self, x, *args, **kwargs) -> None:
         kernels.gemm_fused_qkv(x, self.weight, *args, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(), **kwargs)
 
+    def plan_splits(self, rows: int) -> int:
+        """The number of K ranges that ``rows`` tokens are cut into by the plain products."""
+        return next((n for most, n in self.split_plans if rows <= most), 1)
+
     def __call__(self, x, out: torch.Tensor | None = None) -> GemmOut:
         rows = x.shape[0]
         if isinstance(x, ScaledRows):
@@ -187,7 +191,7 @@ class Linear:
                 out = self.runtime.workspace.view(f"{self.key}.wide", rows, self.out_features)
             kernels.gemm_fused_store(x, self.weight, out.view(rows, self.out_features), splits=self._fused_splits(rows))
             return GemmOut(out.view(1, rows, self.out_features))
-        splits = next((n for most, n in self.split_plans if rows <= most), 1)
+        splits = self.plan_splits(rows)
         if out is None and splits > 1:
             result = GemmOut(self.runtime.workspace.view(f"{self.key}.partial", splits, rows, self.out_features))
         elif out is None:

@@ -622,6 +622,23 @@ def test_gemm_block_pairs_last_wave_by_k_ranges(m, n, k, out_dtype, swiglu):
     close(out[0], expected, out_dtype, "whole tiles")
 
 
+@pytest.mark.parametrize("m, inter, k", [(64, 1552, 256), (100, 560, 1024), (5, 48, 72), (33, 4096, 64), (200, 304, 448)])
+def test_gemm_tensor_cores_with_the_gate_in_the_epilogue(m, inter, k):
+    """The single-block product with gate and up rows interleaved in groups of 16: it stores act(x G^T) * (x U^T)."""
+    a = rand(m, k, seed=160, dtype=torch.bfloat16)
+    gate, up = rand(inter, k, seed=161, scale=0.1, dtype=torch.bfloat16), rand(inter, k, seed=162, scale=0.1, dtype=torch.bfloat16)
+    w = kernels.interleave_gate_up(gate, up, kernels.SWIGLU_GROUP).contiguous()
+    out = torch.full((1, m, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(a, w, GemmOut(out), swiglu=True)
+    kernels.check_status(DEV)
+    g, u = a.double() @ gate.double().T, a.double() @ up.double().T
+    close(out[0], torch.nn.functional.silu(g) * u, torch.bfloat16, f"{m} tokens, {inter} features, K={k}")
+    kernels.gemm_tc(a, w, GemmOut(out), swiglu=True, activation="relu")
+    close(out[0], torch.relu(g) * u, torch.bfloat16, "relu")
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tc(a, w, GemmOut(torch.empty(2, m, inter, dtype=torch.float32, device=DEV)), swiglu=True)
+
+
 @pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
 def test_gemm_tensor_cores_every_token_tile(tile):
     m, n, k = 70, 384, 448
