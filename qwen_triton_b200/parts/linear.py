@@ -34,7 +34,7 @@ def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: i
                 partial_cost: float = 2.0, sms: int = 0) -> int:
     """Split count for a product with few rows, by a cost in bytes: the weight, read at the rate its blocks
     (128-row weight tiles x token tiles of at most 128 x splits) keep ``target_blocks`` slots busy (a second token
-    tile reads it again, from L2), plus the float partial sums of ``rows`` rows, written once and read once.  Each split keeps at least four 64-wide K blocks; fewer splits win near-ties.
+    tile reads it again, from L2), plus the float partial sums of ``rows`` rows, written once and read once.  Each split keeps at least four 64-wide K blocks (two in the fused product, whose sums never leave the chip: the 0.6B shape at batch 8, 1.18 ms a step against 1.21); fewer splits win near-ties.
     (Filling waves alone would cut a product that already has blocks for several waves into many splits, whose
     partial sums then cost more than the weight: 14 splits for a 51,200 x 5,120 weight at 64 rows.)
     ``partial_cost`` is 2 for partial sums written to and read from global memory, 1 for the fused product, whose
@@ -49,11 +49,14 @@ def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: i
     blocks_k = -(-in_features // 64)
     weight_bytes = 2.0 * out_features * in_features * (1.0 + 0.3 * (token_tiles - 1))
     best, best_cost = 1, float("inf")
+    clustered = most <= kernels.FUSED_MAX_SPLITS         # the fused product: the K ranges of a tile are a thread-block cluster
     for splits in range(1, most + 1):
-        if splits > 1 and blocks_k // splits < 4:
+        if splits > 1 and blocks_k // splits < (2 if clustered else 4):
             break
         if kernels.tc_normalise_splits(in_features, splits) != splits:
             continue
+        if clustered and splits == 7:
+            continue            # clusters of seven pack the SMs of a GPC worst (32B q/k/v at batch 8: 3.23 ms a step against 3.15 with 4, 5, 6 or 8)
         if splits > 1 and sms and tiles >= sms and tiles * splits > target_blocks:
             break
         waves = tiles * splits / target_blocks
