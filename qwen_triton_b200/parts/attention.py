@@ -111,9 +111,10 @@ class Attention:
     def _splits(self, ctx, cache) -> tuple[int, int]:
         """How a one-token step cuts the keys of each sequence: (blocks per sequence and kv head, warps per block).
 
-        The tensor-core kernel gives every warp a key range of its own.  Measured on the B200: with few
-        (sequence, kv head) pairs, about one block of four warps per SM and as few partial results as that
-        allows; with blocks for two per SM, three warps each and no cut at all.  Every range keeps at least
+        The tensor-core kernel gives every warp a key range of its own.  Measured on the B200: with a moderate
+        number of (sequence, kv head) pairs, about one block of four warps per SM and as few partial results as that
+        allows; with very few pairs, blocks of six warps and a count weighed against the cost of merging them (below);
+        with blocks for two per SM, three warps each and no cut at all.  Every range keeps at least
         two tiles of 32 keys.  The generic kernel (other element types and head sizes) takes one range per
         block: the count whose blocks fill whole waves of three blocks per SM nearly as well as the best one.
         """
@@ -126,6 +127,28 @@ class Attention:
             sms = self.runtime.sm_count
             splits = max(1, min(sms // pairs, most))
             warps = 3 if pairs * splits >= 3 * sms else 4
+            if splits >= 4:
+                # Few pairs (batch 1 to 4 with eight kv heads): blocks of six warps, and as many of them per pair as
+                # pays: a block draws about 80 GB/s of keys and values, a merge through a cluster of up to four blocks
+                # costs about 1.5 us, of six 3 us, and more blocks than a cluster holds (scratch memory and the combine
+                # kernel) 13 us.  Clusters of five and seven, and more than eight clusters of eight, are left out: they
+                # pack the SMs of a GPC badly beside the next product's clusters (batch 2, cache 8,192: 3.80 ms a step
+                # with eight blocks per pair, 3.57 with five, 3.51 with six).  Timed in the model, 8B shape, batch 1: cache 2,048: 3.09 ms a step
+                # with four blocks against 3.15 with eight; 8,192: 3.32 against 3.54 with four; 32,768: 3.99 with
+                # eighteen against 4.23 with eight and 5.26 with four.
+                warps = kernels.DECODE_WARPS_MAX
+                pair_bytes = 4.0 * span * self.d                      # keys and values of one pair, bfloat16
+                best = None
+                for count in range(1, splits + 1):
+                    if count > 1 and count * warps * 2 > tiles:
+                        break
+                    if count in (5, 7) or (count == 8 and pairs > 8):        # eight clusters of eight still find a GPC each
+                        continue
+                    merge = 0.0 if count == 1 else 1.5e-6 if count <= 4 else 3e-6 if count <= 8 else 13e-6
+                    cost = merge + pair_bytes / (count * 80e9)
+                    if best is None or cost < best[0]:
+                        best = (cost, count)
+                splits = best[1]
             while splits > 1 and splits * warps * 2 > tiles:
                 splits -= 1
             while warps > 1 and splits * warps * 2 > tiles:
