@@ -126,7 +126,10 @@ class Attention:
             tiles = math.ceil(span / 32)
             sms = self.runtime.sm_count
             splits = max(1, min(sms // pairs, most))
-            warps = 3 if pairs * splits >= 3 * sms else 4
+            # blocks of four warps are one to an SM, of three two: three where that makes one wave of what would be two
+            # with a nearly empty second one (160-192 blocks: 2-5 % shorter steps at batch 20-24 of the 8B shape), and
+            # where there are blocks for three waves and more (batch 56-64: 6 %)
+            warps = 3 if pairs * splits >= 3 * sms or sms < pairs * splits <= 2 * sms else 4
             if splits >= 4:
                 # Few pairs (batch 1 to 4 with eight kv heads): blocks of six warps, and as many of them per pair as
                 # pays: a block draws about 80 GB/s of keys and values, a merge through a cluster of up to four blocks
