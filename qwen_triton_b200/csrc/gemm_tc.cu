@@ -659,11 +659,13 @@ template <int BX, typename TO, bool GATED>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_x, TO* out, int M, int N, int kb_total, int splits,
            size_t split_stride, int stages, int act, int* status, cudaStream_t stream) {
     constexpr uint32_t STAGE_BYTES = W_BYTES + BX * BK * 2;
-    // Up to 32 tokens a block streams weights through a three-stage ring (54 KB), so that four blocks share an SM and
+    // Up to 16 tokens a block streams weights through a three-stage ring (54 KB), so that four blocks share an SM and
     // the next product's blocks can move in beside this one's last blocks and fetch their first weight tiles early
-    // (measured 3-4 % on a decode step against two blocks with six stages).  Larger tiles: two blocks per SM, which
-    // overlap each other's epilogue and keep two MMA issuers feeding the tensor pipe.
-    const int budget = (BX <= 32 ? 56 : 110) * 1024;
+    // (measured 3-4 % on a decode step against two blocks with six stages).  Larger tiles: two blocks per SM with
+    // rings of 110 KB, which overlap each other's epilogue and keep two MMA issuers feeding the tensor pipe.  (The
+    // 32-token tile used to share the small budget, which is two stages of its 20 KB: a decode step at batch 20 / 32 of
+    // the 8B shape took 4.91 / 5.40 ms with that, 4.50 / 4.99 ms with five stages and two blocks.)
+    const int budget = (BX <= 16 ? 56 : 110) * 1024;
     const int most = (224 * 1024) / (int)STAGE_BYTES;
     if (stages <= 0) {
         stages = (budget - 2048) / (int)STAGE_BYTES;

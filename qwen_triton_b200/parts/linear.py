@@ -25,9 +25,7 @@ _FUSED_ROWS = int(os.environ.get("QT_B200_FUSED_ROWS", "16"))
 # first weight tiles while this one drains; up to 64 rows two blocks with deeper rings measured better.  Up to 256
 # rows (a large decode batch, a short prompt) the weight still bounds the product: blocks of 128 tokens, split
 # (alone, 256 rows of the 8B shapes: 16.6 us against 54 us for q/k/v, 32 against 158 us for the down projection).
-# 17 to 32 rows take the 32-token tile, which keeps four blocks per SM like the 16-token one: a plan of their own
-# (in the model, batch 24 / 32 of the 8B shape: 5.23 / 5.33 ms a step against 5.36 / 5.44 with the 64-row plan).
-_SPLIT_PLANS = ((16, 4), (32, 4), (64, 2), (128, 2), (256, 2))      # (most rows, blocks per SM)
+_SPLIT_PLANS = ((16, 4), (64, 2), (128, 2), (256, 2))      # (most rows, blocks per SM)
 
 
 def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: int = 16, most: int = _MAX_SPLITS,

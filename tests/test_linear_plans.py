@@ -40,10 +40,10 @@ def test_every_split_count_leaves_no_split_without_k_blocks(out_features, in_fea
 
 
 def test_a_weight_whose_tiles_fill_the_machine_is_not_cut_into_a_second_wave():
-    """192 tiles of the 8B shape's gate/up weight: three ranges at 16 and 32 rows (576 blocks of 592 resident), none at
-    64 rows and more (two blocks per SM: 384 blocks would be a second wave); the fused form (three blocks per SM for
-    this product) keeps two ranges there and gives the 32B shape's 400 tiles none."""
-    assert [linear.pick_splits(24576, 4096, per_sm * 148, rows, sms=148) for rows, per_sm in linear._SPLIT_PLANS] == [3, 3, 1, 1, 1]
+    """192 tiles of the 8B shape's gate/up weight: three ranges up to 16 rows (576 blocks of 592 resident), none beyond
+    (two blocks per SM: 384 blocks would be a second wave); the fused form (three blocks per SM for this product)
+    keeps two ranges there and gives the 32B shape's 400 tiles none."""
+    assert [linear.pick_splits(24576, 4096, per_sm * 148, rows, sms=148) for rows, per_sm in linear._SPLIT_PLANS] == [3, 1, 1, 1]
     assert linear.pick_splits(24576, 4096, 3 * 148, 16, kernels.FUSED_MAX_SPLITS, 1.0, sms=148) == 2
     assert linear.pick_splits(51200, 5120, 3 * 148, 16, kernels.FUSED_MAX_SPLITS, 1.0, sms=148) == 1
     # a weight with fewer tiles than SMs is cut as before
