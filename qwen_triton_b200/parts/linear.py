@@ -16,6 +16,10 @@ from .base import Runtime
 
 
 _MAX_SPLITS = 16
+# Ring depths of the fused product that are tried in turn, deepest first (see Linear._fused_stages), and the blocks of
+# the 16-token tile that share an SM at each depth (18 KB a stage).
+_FUSED_STAGES = {"qkv": (4,), "attn_out": (4,), "gate": (4,), "mlp_out": (5, 4)}
+_FUSED_BLOCKS_PER_SM = {3: 4, 4: 3, 5: 2}
 # Most rows that take the fused product.  What a fused launch adds to the plain product is its tail (park, cluster
 # barrier, the peers' sums); it grows with the rows, and beyond 16 it costs more than the small kernels it replaces
 # (8B shapes, 64 rows, replayed alone: q/k/v 15.8 us fused against 10.4 + 2.7 us, down 23.0 against 19.9 + 3.5 us).
@@ -161,24 +165,33 @@ class Linear:
     def _fused_splits(self, rows: int) -> int:
         return next(n for most, n in self.fused_plans if rows <= most)
 
-    def _fused_stages(self) -> int:
-        """Depth of the fused product's ring (0: the kernel's default of three stages, four blocks per SM).  The
-        gated product has blocks for every slot of the machine at two or three splits; with four stages three of them
-        share an SM and the next product's blocks find room beside them (measured at the 8B shape, 8 rows: 33.4 us
-        against 39.6 us with the default)."""
-        return 4 if self.role == "gate" else 0
+    def _fused_stages(self, rows: int) -> int:
+        """Depth of the fused product's ring (0: the kernel's default of three stages, four blocks per SM): the deepest of
+        this product's candidates at which all its blocks are still resident at once.  Timed in the model (8B shape,
+        batch 8, 36 layers): 3.55 ms a step with three stages for q/k/v, o and down, 3.43 ms with four for each (three
+        blocks per SM), 3.41 ms with five for down (whose K is the longest); two stages or five for q/k/v are slower
+        (3.56, 3.58 ms).  Where the deeper ring would push blocks into a second wave it costs more than it brings (32B
+        shape, 16 layers at batch 8: 3.35 ms with four stages for the 480 blocks of q/k/v against 3.13 ms with three).
+        The gated product has blocks for every slot of the machine at two or three splits; with four stages three of
+        them share an SM and the next product's blocks find room beside them (alone, 8 rows: 33.4 us against 39.6 us
+        with three; five or six in the model: 3.72 ms)."""
+        blocks = -(-self.out_features // 128) * self._fused_splits(rows)
+        for stages in _FUSED_STAGES.get(self.role, ()):
+            if self.role == "gate" or blocks <= _FUSED_BLOCKS_PER_SM[stages] * self.runtime.sm_count:
+                return stages
+        return 0
 
     def into_residual(self, x: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor | None = None, eps: float = 0.0,
                       xw: torch.Tensor | None = None, sq: torch.Tensor | None = None) -> "ScaledRows | None":
         """residual += x W^T, and the norm behind it prepared (see ``kernels.gemm_fused_residual``)."""
-        return kernels.gemm_fused_residual(x, self.weight, residual, norm_weight, eps, xw, sq, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages())
+        return kernels.gemm_fused_residual(x, self.weight, residual, norm_weight, eps, xw, sq, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(x.shape[0]))
 
     def into_swiglu(self, x, out: torch.Tensor, activation: str = "silu") -> None:
-        kernels.gemm_fused_swiglu(x, self.weight, out, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(),
+        kernels.gemm_fused_swiglu(x, self.weight, out, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(x.shape[0]),
                                   activation=activation)
 
     def into_qkv(self, x, *args, **kwargs) -> None:
-        kernels.gemm_fused_qkv(x, self.weight, *args, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(), **kwargs)
+        kernels.gemm_fused_qkv(x, self.weight, *args, splits=self._fused_splits(x.shape[0]), stages=self._fused_stages(x.shape[0]), **kwargs)
 
     def plan_splits(self, rows: int) -> int:
         """The number of K ranges that ``rows`` tokens are cut into by the plain products."""

@@ -69,3 +69,14 @@ def test_plans_are_sorted_and_the_partial_buffer_holds_every_plan(max_rows):
     # float32 models and rows that TMA cannot address take no split plan at all
     assert linear.Linear("y", 4096, 12288, _Runtime(torch.float32, max_rows)).split_plans == []
     assert linear.Linear("z", 4096, 12284, _Runtime(torch.bfloat16, max_rows)).split_plans == []
+
+
+def test_the_fused_ring_is_as_deep_as_keeps_every_block_resident():
+    """8B shapes: four stages for q/k/v and o (384 and 256 blocks of the 444 that three to an SM give), five for down
+    (256 of 296); the 32B shape's q/k/v has 480 blocks and keeps the default three stages, its down takes four."""
+    runtime = _Runtime(torch.bfloat16, 64)
+    def stages(out_features, in_features, role):
+        return linear.Linear(f"t.{role}.{out_features}", out_features, in_features, runtime, role=role)._fused_stages(8)
+    assert [stages(6144, 4096, "qkv"), stages(4096, 4096, "attn_out"), stages(24576, 4096, "gate"), stages(4096, 12288, "mlp_out")] == [4, 4, 4, 5]
+    assert [stages(10240, 5120, "qkv"), stages(5120, 8192, "attn_out"), stages(5120, 25600, "mlp_out")] == [0, 4, 4]
+    assert stages(4096, 4096, "") == 0
