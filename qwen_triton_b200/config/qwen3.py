@@ -215,6 +215,7 @@ class Qwen3Config:
             "use_sliding_window": self.use_sliding_window,
             "sliding_window": self.sliding_window,
             "max_window_layers": self.max_window_layers,
+            "layer_types": list(self.layer_types),
         }
         if self.partial_rotary_factor != 1.0:
             out["partial_rotary_factor"] = self.partial_rotary_factor

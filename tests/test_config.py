@@ -84,6 +84,11 @@ def test_round_trip_through_config_json(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(cfg.to_hf_dict()))
     again = load_config(tmp_path)
     assert again == cfg
+    # layer types that no cutoff describes survive the trip as the list they are
+    mixed = Qwen3Config.from_hf_config({**BASE, "sliding_window": 16,
+                                        "layer_types": ["sliding_attention", "full_attention", "sliding_attention"]})
+    (tmp_path / "config.json").write_text(json.dumps(mixed.to_hf_dict()))
+    assert load_config(tmp_path).layer_types == ("sliding_attention", "full_attention", "sliding_attention")
 
 
 def test_presets_differ_in_every_size_and_option():
