@@ -96,3 +96,75 @@ def test_a_random_configuration(case):
     for slot in slots:
         engine.release(slot)
     engine.check_kernels()
+
+
+LONG_CASES = 16
+
+
+def draw_long(case: int):
+    """Prompts of thousands of tokens at the head sizes of the tensor-core attention and at others: they arrive whole
+    or in steps of 700 or 2,048 tokens, a step takes 1,024 to 4,096 tokens in a pass, and logits are wanted anywhere."""
+    rng = random.Random(9000 + case)
+    kv, group = rng.choice([1, 2, 3]), rng.choice([1, 2, 4, 5, 8])
+    layers = rng.choice([1, 2])
+    window = rng.choice([None, None, 100, 257, 1024, 3000])
+    kinds = tuple(rng.choice(["full_attention", "sliding_attention"]) if window else "full_attention" for _ in range(layers))
+    if window and "sliding_attention" not in kinds:
+        kinds = kinds[:-1] + ("sliding_attention",)
+    lengths = [rng.choice([1, 65, 1500, 2047, 2048, 2049, 3000, 4097, 6000]) for _ in range(rng.choice([1, 1, 2, 3]))]
+    if max(lengths) > 3000 and kv * group > 8:
+        group = max(1, 8 // kv)                              # the plain implementation holds every head's whole score matrix
+    sizes = dict(
+        hidden_size=rng.choice([64, 128, 200, 256, 512]), intermediate_size=rng.choice([88, 256, 512, 1000]),
+        vocab_size=rng.choice([199, 1001]), num_attention_heads=kv * group, num_key_value_heads=kv,
+        head_dim=rng.choice([64, 64, 128, 128, 128, 32, 96, 256]), num_hidden_layers=layers, layer_types=kinds,
+        sliding_window=window, use_sliding_window=bool(window), max_window_layers=None,
+        tie_word_embeddings=rng.random() < 0.4, attention_bias=rng.random() < 0.3, rms_norm_eps=1e-6,
+        rope_theta=rng.choice([1e4, 1e6]), partial_rotary_factor=rng.choice([1.0, 1.0, 0.5]), max_position_embeddings=8192)
+    return sizes, ("bf16", "fp32")[case % 2], lengths, rng.choice([None, None, 700, 2048]), rng.choice([4096, 1024, 2048]), rng.choice([1, 3, 66]), rng
+
+
+@pytest.mark.parametrize("case", range(LONG_CASES))
+def test_a_random_long_prompt(case):
+    sizes, dtype, lengths, piece, pass_tokens, steps, rng = draw_long(case)
+    config = dataclasses.replace(load_preset("tiny-a"), **sizes)
+    config.validate()
+    raw = config.to_hf_dict()
+    with tempfile.TemporaryDirectory(prefix="qt_random_") as folder:
+        write_random_model(folder, config, seed=case, dtype=STORE[dtype])
+        checkpoint = Checkpoint(folder)
+        weights = {name: checkpoint.read(name).float() for name in checkpoint.names()}
+        engine = Engine.from_pretrained(folder, dtype=dtype, max_step_tokens=pass_tokens,
+                                        max_tokens=64 * sum((n + steps + 63) // 64 for n in lengths) + 64)
+    generator = torch.Generator().manual_seed(case)
+    prompts = [torch.randint(0, config.vocab_size, (n,), generator=generator).tolist() for n in lengths]
+    whole = [plain.forward(raw, weights, prompt) for prompt in prompts]
+    what = f"{dtype}, lengths {lengths} in steps of {piece}, passes of {pass_tokens}, " + ", ".join(f"{k}={v}" for k, v in sizes.items())
+    slots = [engine.new_sequence() for _ in prompts]
+    fed = [0] * len(prompts)
+    piece = piece or max(lengths)
+    while any(f < n for f, n in zip(fed, lengths)):
+        entries, places = [], []
+        for i, (slot, prompt) in enumerate(zip(slots, prompts)):
+            part = prompt[fed[i]:fed[i] + piece]
+            if part:
+                want = sorted(set(rng.sample(range(len(part)), min(len(part), 4))) | {0, len(part) - 1})
+                entries.append(StepEntry(slot, part, want))
+                places += [(i, fed[i] + w) for w in want]
+                fed[i] += len(part)
+        rows = engine.step(entries)
+        expected = torch.stack([whole[i][place] for i, place in places])
+        try:
+            assert_close(rows, expected, dtype, f"prompt tokens up to {fed} ({what})")
+        except AssertionError:
+            compare(rows, [prompts[i][:place + 1] for i, place in places], raw, weights, dtype, what)
+    for step in range(steps):
+        feed = torch.randint(0, config.vocab_size, (len(prompts),), generator=generator).tolist()
+        rows = engine.step([StepEntry(slot, [token], [0]) for slot, token in zip(slots, feed)])
+        for prompt, token in zip(prompts, feed):
+            prompt.append(token)
+        if step in (0, steps - 1):
+            compare(rows, prompts, raw, weights, dtype, f"one-token step {step} ({what})")
+    for slot in slots:
+        engine.release(slot)
+    engine.check_kernels()
