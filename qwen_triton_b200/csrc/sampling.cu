@@ -77,9 +77,11 @@ extern "C" int qt_argmax(const float* logits, int* out, int rows, int vocab, voi
     return QT_OK;
 }
 
-// Floats as unsigned integers of the same order (every key of a negative number below every key of a positive one).
+// Floats as unsigned integers of the same order (every key of a negative number below every key of a positive one;
+// the two zeros, which compare equal, share the key of +0).
 __device__ __forceinline__ unsigned int ordered_key(float x) {
-    const unsigned int bits = __float_as_uint(x);
+    unsigned int bits = __float_as_uint(x);
+    if (bits == 0x80000000u) bits = 0u;
     return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
 }
 

@@ -477,6 +477,12 @@ def test_tokens_that_tie_with_the_last_kept_one_are_kept():
     assert sorted(set(draws.tolist())) == [10, 20, 400]
     draws = _draws(row, 1.0, 0, 0.5, count=500)
     assert set(draws.tolist()) == {10}
+    # the two zeros are one value: a row of them is a row of ties, whatever their sign bits
+    zeros = torch.zeros(1, 40, device=DEV)
+    zeros[0, ::3] = -0.0
+    for top_k, top_p in ((2, 1.0), (0, 0.1), (5, 0.5)):
+        draws = _draws(zeros, 0.7, top_k, top_p, count=2000)
+        assert sorted(set(draws.tolist())) == list(range(40)), (top_k, top_p)
 
 
 def test_sample_of_distinct_rows_with_top_k_and_top_p():
