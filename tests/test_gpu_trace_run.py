@@ -92,3 +92,55 @@ def test_trace_replay_three_ways(tmp_path, dtype, name):
     for number, rows in owner.items():
         expected = torch.stack([plain_logits(PRESET, name, requests[k])[at] for k, at in rows])
         assert_close(out[number], expected, name, f"batched step {number}")
+
+
+@pytest.mark.parametrize("dtype, name", [("float32", "fp32"), ("bfloat16", "bf16")])
+def test_two_batches_live_at_once(tmp_path, dtype, name):
+    """A second batch starts while the first still holds its cache, and their one-token steps alternate; requests
+    end at different steps, some steps want nothing from a request, and --max-tokens is exactly what the live
+    requests hold at the fullest moment (each rounded up to 64)."""
+    totals = {"a0": 70, "a1": 33, "a2": 5, "b0": 66, "b1": 2, "b2": 130}
+    prompts = {"a0": 60, "a1": 33, "a2": 1, "b0": 3, "b1": 1, "b2": 126}
+    requests = {key: random_tokens(PRESET, n, 700 + i) for i, (key, n) in enumerate(totals.items())}
+    at, held, steps, owner, peak = {}, {}, [], {}, 0
+
+    def add(entries, own):
+        nonlocal peak
+        number = len(steps)
+        for entry in entries:
+            key = entry["id"]
+            at[key] = at.get(key, 0) + len(entry["tokens"])
+            held[key] = at[key]
+        peak = max(peak, sum(-(-n // 64) * 64 for n in held.values()))
+        end = [entry["id"] for entry in entries if at[entry["id"]] == totals[entry["id"]]]
+        for key in end:
+            del held[key]
+        steps.append({"step": number, "entries": entries, "end": end})
+        if own:
+            owner[number] = own
+
+    def start(batch):
+        entries = [{"id": k, "tokens": requests[k][:prompts[k]], "want": [0, prompts[k] - 1] if prompts[k] > 1 else [0]} for k in batch]
+        add(entries, [(e["id"], w) for e in entries for w in e["want"]])
+
+    def advance(batch, quiet=()):
+        active = [k for k in batch if at[k] < totals[k]]
+        entries = [{"id": k, "tokens": [requests[k][at[k]]], "want": [] if k in quiet else [0]} for k in active]
+        add(entries, [(k, at[k]) for k in active if k not in quiet])
+        return bool(active)
+
+    first, second = ["a0", "a1", "a2"], ["b0", "b1", "b2"]
+    start(first)
+    advance(first)
+    start(second)
+    turn = 0
+    while any(at[k] < totals[k] for k in first + second):
+        batch = (first, second)[turn % 2]
+        if any(at[k] < totals[k] for k in batch):
+            advance(batch, quiet=("a0",) if turn % 3 == 0 else ())
+        turn += 1
+    assert peak == 64 * 6 and len(steps) == 75            # the schedule itself: six pages at the fullest moment
+    out = replay(model_folder(PRESET, name), dtype, steps, tmp_path / "two", max_tokens=peak)
+    for number, rows in owner.items():
+        expected = torch.stack([plain_logits(PRESET, name, requests[k])[place] for k, place in rows])
+        assert_close(out[number], expected, name, f"step {number}: {rows}")
