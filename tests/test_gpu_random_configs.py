@@ -69,9 +69,13 @@ def compare(rows, prompts, raw, weights, dtype, what):
             raise
 
 
-@pytest.mark.parametrize("case", range(CASES))
-def test_a_random_configuration(case):
+@pytest.mark.parametrize("case, head_dim", [(case, None) for case in range(CASES)] +
+                         [(100 + i, d) for i, d in enumerate((2, 6, 10, 24, 40, 50, 72, 100, 250))])
+def test_a_random_configuration(case, head_dim):
+    """``head_dim`` set: a head size between the steps of 16, which only the kernels for any size take."""
     sizes, dtype, lengths, steps, checked = draw(case)
+    if head_dim is not None:
+        sizes["head_dim"] = head_dim
     config = dataclasses.replace(load_preset("tiny-a"), **sizes)
     config.validate()
     raw = config.to_hf_dict()
@@ -168,3 +172,13 @@ def test_a_random_long_prompt(case):
     for slot in slots:
         engine.release(slot)
     engine.check_kernels()
+
+
+def test_a_head_size_beyond_the_kernels_is_refused_in_words():
+    sizes = draw(0)[0]
+    sizes["head_dim"] = 258
+    config = dataclasses.replace(load_preset("tiny-a"), **sizes)
+    with tempfile.TemporaryDirectory(prefix="qt_random_") as folder:
+        write_random_model(folder, config, seed=0, dtype=torch.float32)
+        with pytest.raises(ValueError, match="head_dim=258 is beyond what the attention kernels take"):
+            Engine.from_pretrained(folder, dtype="fp32", max_tokens=256)
