@@ -36,7 +36,9 @@ def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: i
                 partial_cost: float = 2.0, sms: int = 0) -> int:
     """Split count for a product with few rows, by a cost in bytes: the weight, read at the rate its blocks
     (128-row weight tiles x token tiles of at most 128 x splits) keep ``target_blocks`` slots busy (a second token
-    tile reads it again, from L2), plus the float partial sums of ``rows`` rows, written once and read once.  Each split keeps at least four 64-wide K blocks (two in the fused product, whose sums never leave the chip: the 0.6B shape at batch 8, 1.18 ms a step against 1.21); fewer splits win near-ties.
+    tile reads it again, from L2), plus the float partial sums of ``rows`` rows, written once and read once.  Each
+    split keeps at least four 64-wide K blocks (two in the fused product, whose sums never leave the chip: the 0.6B
+    shape at batch 8, 1.18 ms a step against 1.21); fewer splits win near-ties.
     (Filling waves alone would cut a product that already has blocks for several waves into many splits, whose
     partial sums then cost more than the weight: 14 splits for a 51,200 x 5,120 weight at 64 rows.)
     ``partial_cost`` is 2 for partial sums written to and read from global memory, 1 for the fused product, whose
@@ -58,7 +60,8 @@ def pick_splits(out_features: int, in_features: int, target_blocks: int, rows: i
         if kernels.tc_normalise_splits(in_features, splits) != splits:
             continue
         if clustered and splits == 7:
-            continue            # clusters of seven pack the SMs of a GPC worst (32B q/k/v at batch 8: 3.23 ms a step against 3.15 with 4, 5, 6 or 8)
+            continue            # clusters of seven pack the SMs of a GPC worst (32B q/k/v at batch 8: 3.23 ms a step
+                                # against 3.15 with 4, 5, 6 or 8)
         if splits > 1 and sms and tiles >= sms and tiles * splits > target_blocks:
             break
         waves = tiles * splits / target_blocks
@@ -75,9 +78,10 @@ _PAIR_TILE = 256                       # weight rows and tokens of one pair tile
 
 def pick_pair_splits(out_features: int, in_features: int, rows: int, pairs: int) -> int:
     """Split count for a product of a few hundred rows by the pair kernel, whose 256 x 256 tiles alone leave TPCs
-    idle or end in a nearly empty wave: waves of work items (tiles x splits over ``pairs`` resident pairs, one per TPC) times the time of one item at the pair's share of the
-    tensor throughput plus a fixed cost per item, plus the float partial sums written and read once (they stay
-    in L2); the constants are fitted to products of 300 to 768 rows timed alone.  Every split keeps at least eight 64-wide K blocks; fewer splits win near-ties."""
+    idle or end in a nearly empty wave: waves of work items (tiles x splits over ``pairs`` resident pairs, one per
+    TPC) times the time of one item at the pair's share of the tensor throughput plus a fixed cost per item, plus
+    the float partial sums written and read once (they stay in L2); the constants are fitted to products of 300 to
+    768 rows timed alone.  Every split keeps at least eight 64-wide K blocks; fewer splits win near-ties."""
     tiles = -(-out_features // _PAIR_TILE) * -(-rows // _PAIR_TILE)
     blocks_k = -(-in_features // 64)
     pair_flops, first_overhead, later_overhead, partial_rate = 1.45e15 / pairs, 2e-6, 0.5e-6, 2e13
